@@ -1,0 +1,419 @@
+"""The single compute backend: hand-written sm_100a kernels behind a C ABI.
+
+Function names, keyword names, return types and error behaviour mirror the
+reference's CUDA backend module (comfy_kitchen/backends/cuda/__init__.py:369-529,
+1338-1498, 1681-1817) so the registry and the layout classes can call it
+unchanged.  Differences, all additive: fp32 inputs to the block quantizers, fp32
+bias in ``scaled_mm_*``, ``dequantize_mxfp8`` / ``scaled_mm_mxfp8`` on the device,
+no zero-fill pass over the scale buffers (the kernels write the padding), and the
+fused ``adaln_quantize_*`` / ``rmsnorm`` entry points.
+
+Every output is allocated here with torch (caching allocator, CUDA-graph safe);
+the native side only launches on the current stream.  Nothing synchronises.
+"""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from comfy_kitchen import _native
+from comfy_kitchen.backends._modulation import adaln_prep_modulation
+from comfy_kitchen.float_utils import roundup
+
+DTYPE_CODE_TO_DTYPE = {
+    0: torch.float32,
+    1: torch.float16,
+    2: torch.bfloat16,
+    5: torch.float8_e4m3fn,
+    6: torch.float8_e5m2,
+}
+DTYPE_TO_CODE = {v: k for k, v in DTYPE_CODE_TO_DTYPE.items()}
+
+_native.load()  # fail at import when the library is absent: there is no other path
+
+
+def _ptr(t: torch.Tensor | None):
+    return ctypes.c_void_p(0 if t is None else t.data_ptr())
+
+
+def _stream(device) -> ctypes.c_void_p:
+    return ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+
+
+def _code(dtype: torch.dtype, what: str) -> int:
+    try:
+        return DTYPE_TO_CODE[dtype]
+    except KeyError:
+        raise TypeError(f"{what}: unsupported dtype {dtype}") from None
+
+
+def _plain(t):
+    return t.data if isinstance(t, torch.nn.Parameter) else t
+
+
+# ------------------------------------------------------------------ FP8 per tensor
+
+
+def quantize_per_tensor_fp8(
+    x: torch.Tensor, scale: torch.Tensor, output_type: torch.dtype = torch.float8_e4m3fn
+) -> torch.Tensor:
+    if output_type not in (torch.float8_e4m3fn, torch.float8_e5m2):
+        raise ValueError(
+            f"Unsupported output_type: {output_type}. Expected torch.float8_e4m3fn or torch.float8_e5m2"
+        )
+    x = _plain(x)
+    if not x.is_contiguous():
+        x = x.contiguous()
+    scale = _scalar_on(scale, x.device)
+    out = torch.empty(x.shape, dtype=torch.uint8, device=x.device)
+    _native.call(
+        "launch_quantize_fp8_kernel", _ptr(x), _ptr(out), _ptr(scale), x.numel(),
+        _code(x.dtype, "quantize_per_tensor_fp8"), DTYPE_TO_CODE[output_type], _stream(x.device),
+    )
+    return out.view(output_type)
+
+
+def dequantize_per_tensor_fp8(
+    x: torch.Tensor, scale: torch.Tensor, output_type: torch.dtype = torch.bfloat16
+) -> torch.Tensor:
+    assert scale.numel() == 1, "Scale must be a scalar tensor"
+    x = _plain(x)
+    if not x.is_contiguous():
+        x = x.contiguous()
+    scale = _scalar_on(scale, x.device)
+    out = torch.empty(x.shape, dtype=output_type, device=x.device)
+    _native.call(
+        "launch_dequantize_fp8_kernel", _ptr(x), _ptr(out), _ptr(scale), x.numel(),
+        _code(x.dtype, "dequantize_per_tensor_fp8"), _code(output_type, "dequantize_per_tensor_fp8"),
+        _stream(x.device),
+    )
+    return out
+
+
+def _scalar_on(s, device) -> torch.Tensor:
+    """fp32 one-element device tensor without a host round trip when it already is one."""
+    s = _plain(s)
+    if not isinstance(s, torch.Tensor):
+        s = torch.tensor(float(s), dtype=torch.float32, device=device)
+    if s.dtype != torch.float32 or s.device != device:
+        s = s.to(device=device, dtype=torch.float32)
+    return s.reshape(1) if s.dim() == 0 else s.contiguous()
+
+
+# ------------------------------------------------------------------ NVFP4
+
+
+def quantize_nvfp4(
+    x: torch.Tensor,
+    per_tensor_scale: torch.Tensor,
+    epsilon: float = 0.0,
+    pad_16x: bool = False,
+    hi_first: bool = True,
+) -> tuple[torch.Tensor, torch.Tensor]:
+    x = _plain(x)
+    assert x.dim() == 2, "Input must be 2D"
+    assert x.is_contiguous(), "Input tensor must be contiguous"
+    orig_rows, orig_cols = x.shape
+    if pad_16x:
+        num_rows, num_cols = roundup(orig_rows, 16), roundup(orig_cols, 16)
+    else:
+        num_rows, num_cols = orig_rows, orig_cols
+        assert num_cols % 16 == 0, f"num_cols must be divisible by 16, got {num_cols}"
+    qx = torch.empty((num_rows, num_cols // 2), device=x.device, dtype=torch.uint8)
+    # the kernel writes every byte of the tiled scale buffer, padding included
+    sx = torch.empty((roundup(num_rows, 128), roundup(num_cols // 16, 4)), device=x.device, dtype=torch.uint8)
+    g = _scalar_on(per_tensor_scale, x.device)
+    _native.call(
+        "launch_quantize_nvfp4_kernel", _ptr(x), _ptr(g), _ptr(qx), _ptr(sx), num_rows, num_cols, orig_rows,
+        orig_cols, float(epsilon), _code(x.dtype, "quantize_nvfp4"), bool(hi_first), _stream(x.device),
+    )
+    return qx, sx.view(torch.float8_e4m3fn)
+
+
+def dequantize_nvfp4(
+    qx: torch.Tensor,
+    per_tensor_scale: torch.Tensor,
+    block_scales: torch.Tensor,
+    output_type: torch.dtype = torch.bfloat16,
+    hi_first: bool = True,
+) -> torch.Tensor:
+    qx = _plain(qx)
+    assert qx.is_contiguous(), "Input tensor must be contiguous"
+    num_rows, packed = qx.shape
+    num_cols = packed * 2
+    out = torch.empty((num_rows, num_cols), device=qx.device, dtype=output_type)
+    g = _scalar_on(per_tensor_scale, qx.device)
+    sf = _plain(block_scales).contiguous().view(torch.uint8)
+    _native.call(
+        "launch_dequantize_nvfp4_kernel", _ptr(qx), _ptr(g), _ptr(sf), _ptr(out), num_rows, num_cols,
+        _code(output_type, "dequantize_nvfp4"), bool(hi_first), _stream(qx.device),
+    )
+    return out
+
+
+def scaled_mm_nvfp4(
+    a: torch.Tensor,
+    b: torch.Tensor,
+    tensor_scale_a: torch.Tensor,
+    tensor_scale_b: torch.Tensor,
+    block_scale_a: torch.Tensor,
+    block_scale_b: torch.Tensor,
+    bias: torch.Tensor | None = None,
+    out_dtype: torch.dtype | None = None,
+    alpha: torch.Tensor | None = None,
+) -> torch.Tensor:
+    a, b = _plain(a), _plain(b)
+    block_scale_a, block_scale_b = _plain(block_scale_a), _plain(block_scale_b)
+    if alpha is None:
+        alpha = _plain(tensor_scale_a) * _plain(tensor_scale_b)  # device op, no sync
+    alpha = _scalar_on(alpha, a.device)
+    assert alpha.numel() == 1, "alpha must be a scalar"
+    m, k_a = a.shape
+    n, k_b = b.shape
+    assert k_a == k_b, "Matrix dimensions do not match"
+    k = 2 * k_a
+    assert n % 8 == 0, "B tensor must have 8 alignment in N dimension"
+    assert block_scale_a.dtype == block_scale_b.dtype, "A and B scale dtype must match"
+    if block_scale_a.dtype == torch.float8_e8m0fnu:
+        raise ValueError("MXFP4 is not supported")
+    if block_scale_a.dtype != torch.float8_e4m3fn:
+        raise ValueError(f"Unsupported scale dtype: {block_scale_a.dtype}")
+    sk = roundup(k // 16, 4)
+    assert tuple(block_scale_a.shape) == (roundup(m, 128), sk), "Invalid A scale shape"
+    assert tuple(block_scale_b.shape) == (roundup(n, 128), sk), "Invalid B scale shape"
+    if out_dtype is None:
+        out_dtype = torch.bfloat16
+    bias_code = 0
+    if bias is not None and bias.numel() > 0:
+        bias = _plain(bias).contiguous()
+        assert bias.numel() == n, "bias must have N elements"
+        assert bias.dtype in (torch.float16, torch.bfloat16, torch.float32), "bias must be fp16, bf16 or fp32"
+        bias_code = DTYPE_TO_CODE[bias.dtype]
+    else:
+        bias = None
+    out = torch.empty(m, n, dtype=out_dtype, device=a.device)
+    _native.call(
+        "launch_scaled_mm_nvfp4_kernel", _ptr(a.contiguous()), _ptr(block_scale_a.contiguous().view(torch.uint8)),
+        _ptr(b.contiguous()), _ptr(block_scale_b.contiguous().view(torch.uint8)), _ptr(out), _ptr(bias), bias_code,
+        m, n, k, _ptr(alpha), _code(out_dtype, "scaled_mm_nvfp4"), _stream(a.device),
+    )
+    return out
+
+
+# ------------------------------------------------------------------ MXFP8
+
+
+def quantize_mxfp8(x: torch.Tensor, pad_32x: bool = False) -> tuple[torch.Tensor, torch.Tensor]:
+    x = _plain(x)
+    assert x.dim() == 2, "Input must be 2D"
+    assert x.is_contiguous(), "Input tensor must be contiguous"
+    orig_rows, orig_cols = x.shape
+    if pad_32x:
+        num_rows, num_cols = roundup(orig_rows, 32), roundup(orig_cols, 32)
+    else:
+        num_rows, num_cols = orig_rows, orig_cols
+        assert num_cols % 32 == 0, f"num_cols must be divisible by 32, got {num_cols}"
+    qx = torch.empty((num_rows, num_cols), device=x.device, dtype=torch.uint8)
+    sx = torch.empty((roundup(num_rows, 128), roundup(num_cols // 32, 4)), device=x.device, dtype=torch.uint8)
+    _native.call(
+        "launch_quantize_mxfp8_kernel", _ptr(x), _ptr(qx), _ptr(sx), num_rows, num_cols, orig_rows, orig_cols,
+        _code(x.dtype, "quantize_mxfp8"), _stream(x.device),
+    )
+    return qx.view(torch.float8_e4m3fn), sx.view(torch.float8_e8m0fnu)
+
+
+def dequantize_mxfp8(
+    qx: torch.Tensor, block_scales: torch.Tensor, output_type: torch.dtype = torch.bfloat16
+) -> torch.Tensor:
+    qx = _plain(qx)
+    assert qx.is_contiguous(), "Input tensor must be contiguous"
+    rows, cols = qx.shape
+    out = torch.empty((rows, cols), device=qx.device, dtype=output_type)
+    sf = _plain(block_scales).contiguous().view(torch.uint8)
+    _native.call(
+        "launch_dequantize_mxfp8_kernel", _ptr(qx), _ptr(sf), _ptr(out), rows, cols,
+        _code(output_type, "dequantize_mxfp8"), _stream(qx.device),
+    )
+    return out
+
+
+def scaled_mm_mxfp8(
+    a: torch.Tensor,
+    b: torch.Tensor,
+    block_scale_a: torch.Tensor,
+    block_scale_b: torch.Tensor,
+    bias: torch.Tensor | None = None,
+    out_dtype: torch.dtype | None = None,
+) -> torch.Tensor:
+    a, b = _plain(a), _plain(b)
+    block_scale_a, block_scale_b = _plain(block_scale_a), _plain(block_scale_b)
+    m, k = a.shape
+    n, k_b = b.shape
+    assert k == k_b, "Matrix dimensions do not match"
+    assert n % 8 == 0, "B tensor must have 8 alignment in N dimension"
+    sk = roundup(k // 32, 4)
+    assert tuple(block_scale_a.shape) == (roundup(m, 128), sk), "Invalid A scale shape"
+    assert tuple(block_scale_b.shape) == (roundup(n, 128), sk), "Invalid B scale shape"
+    if out_dtype is None:
+        out_dtype = torch.bfloat16
+    bias_code = 0
+    if bias is not None and bias.numel() > 0:
+        bias = _plain(bias).contiguous()
+        assert bias.numel() == n, "bias must have N elements"
+        bias_code = _code(bias.dtype, "scaled_mm_mxfp8")
+    else:
+        bias = None
+    out = torch.empty(m, n, dtype=out_dtype, device=a.device)
+    _native.call(
+        "launch_scaled_mm_mxfp8_kernel", _ptr(a.contiguous()), _ptr(block_scale_a.contiguous().view(torch.uint8)),
+        _ptr(b.contiguous()), _ptr(block_scale_b.contiguous().view(torch.uint8)), _ptr(out), _ptr(bias), bias_code,
+        m, n, k, _code(out_dtype, "scaled_mm_mxfp8"), _stream(a.device),
+    )
+    return out
+
+
+# ------------------------------------------------------------------ RoPE
+
+
+def _rope(xq, xk, freqs_cis, split_half: bool):
+    if xq.dim() != 4 or freqs_cis.dim() != 6:
+        raise ValueError("apply_rope expects x [B, H, N, D] (or [B, N, H, D]) and freqs_cis [b, h, n, D/2, 2, 2]")
+    xq = xq if xq.is_contiguous() else xq.contiguous()
+    if xk is not None:
+        xk = xk if xk.is_contiguous() else xk.contiguous()
+    if not freqs_cis.is_contiguous():
+        freqs_cis = freqs_cis.contiguous()
+    oq = torch.empty_like(xq)
+    ok = torch.empty_like(xk) if xk is not None else None
+    sx, sf = xq.stride(), freqs_cis.stride()
+    _native.call(
+        "launch_apply_rope_kernel", _ptr(xq), _ptr(xk), _ptr(freqs_cis), _ptr(oq), _ptr(ok),
+        *xq.shape, *freqs_cis.shape[:3], *sx, *sf,
+        _code(xq.dtype, "apply_rope"), _code(freqs_cis.dtype, "apply_rope"), bool(split_half), _stream(xq.device),
+    )
+    return oq, ok
+
+
+def apply_rope1(x: torch.Tensor, freqs_cis: torch.Tensor) -> torch.Tensor:
+    return _rope(x, None, freqs_cis, False)[0]
+
+
+def apply_rope(xq: torch.Tensor, xk: torch.Tensor, freqs_cis: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+    if xq.shape != xk.shape:
+        return apply_rope1(xq, freqs_cis), apply_rope1(xk, freqs_cis)
+    return _rope(xq, xk, freqs_cis, False)
+
+
+def apply_rope_split_half1(x: torch.Tensor, freqs_cis: torch.Tensor) -> torch.Tensor:
+    return _rope(x, None, freqs_cis, True)[0]
+
+
+def apply_rope_split_half(
+    xq: torch.Tensor, xk: torch.Tensor, freqs_cis: torch.Tensor
+) -> tuple[torch.Tensor, torch.Tensor]:
+    if xq.shape != xk.shape:
+        return apply_rope_split_half1(xq, freqs_cis), apply_rope_split_half1(xk, freqs_cis)
+    return _rope(xq, xk, freqs_cis, True)
+
+
+# ------------------------------------------------------------------ AdaLN / RMSNorm
+
+
+def _norm_inputs(x, scale, shift):
+    d = x.shape[-1]
+    n = x.numel() // d
+    xf = x.reshape(n, d)
+    if not xf.is_contiguous():
+        xf = xf.contiguous()
+    sc, sg = adaln_prep_modulation(scale.to(x.dtype), x, n, d)
+    sh, hg = adaln_prep_modulation(shift.to(x.dtype), x, n, d)
+    return xf, sc, sg, sh, hg, n, d
+
+
+def adaln(x: torch.Tensor, scale: torch.Tensor, shift: torch.Tensor, eps: float = 1e-6) -> torch.Tensor:
+    xf, sc, sg, sh, hg, n, d = _norm_inputs(x, scale, shift)
+    out = torch.empty_like(xf)
+    _native.call(
+        "launch_adaln_kernel", _ptr(xf), _ptr(sc), _ptr(sh), _ptr(out), n, d, sg, hg, float(eps),
+        _code(x.dtype, "adaln"), _stream(x.device),
+    )
+    return out.reshape(x.shape)
+
+
+def rmsnorm(x: torch.Tensor, weight: torch.Tensor | None = None, eps: float = 1e-6) -> torch.Tensor:
+    d = x.shape[-1]
+    n = x.numel() // d
+    xf = x.reshape(n, d)
+    if not xf.is_contiguous():
+        xf = xf.contiguous()
+    w = None if weight is None else weight.to(x.dtype).contiguous()
+    out = torch.empty_like(xf)
+    _native.call(
+        "launch_rmsnorm_kernel", _ptr(xf), _ptr(w), _ptr(out), n, d, float(eps), _code(x.dtype, "rmsnorm"),
+        _stream(x.device),
+    )
+    return out.reshape(x.shape)
+
+
+def adaln_quantize_nvfp4(
+    x: torch.Tensor,
+    scale: torch.Tensor,
+    shift: torch.Tensor,
+    per_tensor_scale: torch.Tensor,
+    eps: float = 1e-6,
+    hi_first: bool = True,
+) -> tuple[torch.Tensor, torch.Tensor]:
+    """quantize_nvfp4(adaln(x, scale, shift, eps), per_tensor_scale) in one pass over x."""
+    xf, sc, sg, sh, hg, n, d = _norm_inputs(x, scale, shift)
+    assert d % 16 == 0, f"last dim must be divisible by 16, got {d}"
+    qx = torch.empty((n, d // 2), device=x.device, dtype=torch.uint8)
+    sx = torch.empty((roundup(n, 128), roundup(d // 16, 4)), device=x.device, dtype=torch.uint8)
+    g = _scalar_on(per_tensor_scale, x.device)
+    _native.call(
+        "launch_adaln_quantize_nvfp4_kernel", _ptr(xf), _ptr(sc), _ptr(sh), _ptr(g), _ptr(qx), _ptr(sx), n, d, sg, hg,
+        float(eps), _code(x.dtype, "adaln_quantize_nvfp4"), bool(hi_first), 0, _stream(x.device),
+    )
+    return qx, sx.view(torch.float8_e4m3fn)
+
+
+def adaln_quantize_mxfp8(
+    x: torch.Tensor, scale: torch.Tensor, shift: torch.Tensor, eps: float = 1e-6
+) -> tuple[torch.Tensor, torch.Tensor]:
+    """quantize_mxfp8(adaln(x, scale, shift, eps)) in one pass over x."""
+    xf, sc, sg, sh, hg, n, d = _norm_inputs(x, scale, shift)
+    assert d % 32 == 0, f"last dim must be divisible by 32, got {d}"
+    qx = torch.empty((n, d), device=x.device, dtype=torch.uint8)
+    sx = torch.empty((roundup(n, 128), roundup(d // 32, 4)), device=x.device, dtype=torch.uint8)
+    _native.call(
+        "launch_adaln_quantize_mxfp8_kernel", _ptr(xf), _ptr(sc), _ptr(sh), _ptr(qx), _ptr(sx), n, d, sg, hg,
+        float(eps), _code(x.dtype, "adaln_quantize_mxfp8"), 0, _stream(x.device),
+    )
+    return qx.view(torch.float8_e4m3fn), sx.view(torch.float8_e8m0fnu)
+
+
+def rmsnorm_quantize_nvfp4(
+    x: torch.Tensor, weight: torch.Tensor | None, per_tensor_scale: torch.Tensor, eps: float = 1e-6,
+    hi_first: bool = True,
+) -> tuple[torch.Tensor, torch.Tensor]:
+    """quantize_nvfp4(rmsnorm(x, weight, eps), per_tensor_scale) in one pass over x."""
+    d = x.shape[-1]
+    n = x.numel() // d
+    assert d % 16 == 0
+    xf = x.reshape(n, d)
+    if not xf.is_contiguous():
+        xf = xf.contiguous()
+    w = None if weight is None else weight.to(x.dtype).contiguous()
+    qx = torch.empty((n, d // 2), device=x.device, dtype=torch.uint8)
+    sx = torch.empty((roundup(n, 128), roundup(d // 16, 4)), device=x.device, dtype=torch.uint8)
+    g = _scalar_on(per_tensor_scale, x.device)
+    _native.call(
+        "launch_adaln_quantize_nvfp4_kernel", _ptr(xf), _ptr(w), _ptr(None), _ptr(g), _ptr(qx), _ptr(sx), n, d, n, n,
+        float(eps), _code(x.dtype, "rmsnorm_quantize_nvfp4"), bool(hi_first), 1, _stream(x.device),
+    )
+    return qx, sx.view(torch.float8_e4m3fn)
+
+
+def gemm_device_status() -> int:
+    """Synchronise and return the GEMM kernels' device status word (0 = fine)."""
+    return int(_native.load().ck_gemm_device_status())

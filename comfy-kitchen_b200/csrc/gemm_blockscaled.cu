@@ -1,0 +1,515 @@
+// Block-scaled GEMMs for sm_100a: NVFP4 (E2M1 data, E4M3 scale per 16) and MXFP8
+// (E4M3 data, E8M0 scale per 32), written directly on tcgen05 / TMEM / TMA.
+//
+//   D[M,N] = alpha * sum_k (A[m,k] * SFA[m,k/B]) * (W[n,k] * SFW[n,k/B]) + bias[n]
+//
+// A is [M,K] and W is [N,K], both K-contiguous ("TN"); the scale factors arrive in
+// the 128x4 tiled layout written by the quantizers (ck_common.cuh: sf_offset), one
+// 512-byte tile per 128 rows x 4 scale columns — exactly the 32-lane x 128-bit
+// unit that tcgen05.cp moves from shared memory into TMEM.  Semantics follow
+// comfy_kitchen/backends/eager/quantization.py:224-248 (NVFP4) and :369-404
+// (MXFP8); the reference's CUDA backend forwards NVFP4 to a library GEMM
+// (backends/cuda/ops/cublas_gemm_nvfp4.cu:64-340) and has no MXFP8 kernel.
+//
+// Kernel structure (one persistent CTA per SM, 192 threads):
+//   warp 0      TMA producer: per k-tile one 128x128B box of A, one 192x128B box
+//               of W (both SWIZZLE_128B) and the scale tiles (plain bulk copies)
+//               into a 4-stage shared-memory ring, completion on mbarriers.
+//   warp 1      MMA issuer: tcgen05.cp scale tiles smem->TMEM, then four
+//               tcgen05.mma.kind::{mxf4nvf4,mxf8f6f4}.block_scale per k-tile
+//               (128x192xK64 for FP4, xK32 for FP8), accumulating in TMEM;
+//               tcgen05.commit releases the stage and, per tile, publishes the
+//               accumulator.
+//   warps 2-5   epilogue: tcgen05.ld the 128x192 fp32 accumulator (each warp its
+//               32 TMEM lanes), alpha*acc + bias, convert, 64-byte row stores.
+// Two accumulators (TMEM columns 0 and 256) let the epilogue of tile i overlap the
+// main loop of tile i+1.  Tile = 128x192: two 192-column accumulators plus the
+// scale-factor columns fit the 512 TMEM columns; 192 divides every N of the
+// target shapes (3072, 9216, 12288).  A 192-wide tile starts on a 128-row scale
+// tile boundary only every other tile; odd tiles load the enclosing two scale
+// tiles and hand the MMA a TMEM address two columns in.
+//
+// Every wait in this file is bounded: on expiry the CTA records a status word,
+// stops issuing work, drains its own copies and frees its TMEM before returning.
+#include <cuda.h>
+#include <cudaTypedefs.h>
+
+#include <mutex>
+
+#include "ck_common.cuh"
+
+namespace ck {
+namespace {
+
+constexpr int BM = 128;
+constexpr int BN = 192;
+constexpr int kStages = 4;
+constexpr int kThreads = 192;
+constexpr int kKbPerTile = 4;  // MMAs per k-tile
+
+constexpr int kSmemA = BM * 128;            // 16 KB
+constexpr int kSmemB = BN * 128;            // 24 KB
+constexpr int kSmemSfA = 4 * 512;           // up to four 512-byte tiles (NVFP4)
+constexpr int kSmemSfB = 2 * 4 * 512;       // two row tiles x four
+constexpr int kStageBytes = kSmemA + kSmemB + kSmemSfA + kSmemSfB;  // 47104
+constexpr int kSmemBias = 4 * BN * 4;       // per-epilogue-warp bias row
+constexpr int kSmemBytes = kStages * kStageBytes + kSmemBias + 256 /*barriers*/ + 1024 /*alignment slack*/;
+
+constexpr uint32_t kTmemCols = 512;
+constexpr uint32_t kTmemAcc0 = 0, kTmemAcc1 = 256, kTmemSfA = 448, kTmemSfB = 464;
+
+constexpr uint32_t kSpinLimit = 1u << 22;   // polls of mbarrier.try_wait before giving up (a fraction of a second)
+
+__device__ int g_gemm_status = 0;           // 0 ok; otherwise (code << 16 | detail) of the first failure
+
+enum : int { kTimeoutFull = 1, kTimeoutEmpty = 2, kTimeoutTmemFull = 3, kTimeoutTmemEmpty = 4 };
+
+// ------------------------------------------------------------------ PTX wrappers
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
+        : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+    return ok != 0;
+}
+// Bounded wait, called by all 32 lanes of a warp.  Returns false (to every lane alike)
+// when the limit ran out or another role already gave up.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int code) {
+    bool done = false;
+    for (uint32_t i = 0; i < kSpinLimit; ++i) {
+        if (mbar_try_wait(bar, parity)) { done = true; break; }
+        if ((i & 1023u) == 1023u && *abort_flag) break;
+    }
+    if (!done && !*abort_flag) {
+        *abort_flag = 1;
+        atomicCAS(&g_gemm_status, 0, (code << 16) | (int)(blockIdx.x & 0xffff));
+    }
+    return __all_sync(0xffffffffu, done);
+}
+
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int c0, int c1, uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(smem_u32(dst)), "l"(map), "r"(c0), "r"(c1), "r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void bulk_load(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+        ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
+}
+
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void tc_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tc_cp_sf(uint32_t tmem_addr, uint64_t sdesc) {
+    asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(tmem_addr), "l"(sdesc) : "memory");
+}
+template <bool kFp4>
+__device__ __forceinline__ void tc_mma(uint32_t d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate,
+                                       uint32_t sfa, uint32_t sfb) {
+    if (kFp4) {
+        asm volatile(
+            "{ .reg .pred p; setp.ne.b32 p, %4, 0;\n"
+            "tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.block16 [%0], %1, %2, %3, [%5], [%6], p; }"
+            ::"r"(d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(sfa), "r"(sfb) : "memory");
+    } else {
+        asm volatile(
+            "{ .reg .pred p; setp.ne.b32 p, %4, 0;\n"
+            "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p; }"
+            ::"r"(d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(sfa), "r"(sfb) : "memory");
+    }
+}
+__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+        "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor, K-major operand tile with 128-byte rows and the
+// 128-byte swizzle (8-row groups 1024 bytes apart).
+__device__ __forceinline__ uint64_t desc_sw128(uint32_t saddr) {
+    return (uint64_t)((saddr & 0x3ffffu) >> 4) | (1ull << 16) | ((uint64_t)(1024 >> 4) << 32) | (1ull << 46) | (2ull << 61);
+}
+// Descriptor of one 512-byte scale tile: 32 rows x 16 bytes, unswizzled, 8-row groups 128 bytes apart.
+__device__ __forceinline__ uint64_t desc_sf(uint32_t saddr) {
+    return (uint64_t)((saddr & 0x3ffffu) >> 4) | ((uint64_t)(128 >> 4) << 32) | (1ull << 46);
+}
+
+struct GemmParams {
+    const uint8_t* sfa;
+    const uint8_t* sfb;
+    void* out;
+    const void* bias;
+    const float* alpha;   // device scalar or null (1.0)
+    int M, N, K;          // K in elements
+    int sf_tiles_k;       // 512-byte scale tiles along K (= padded scale columns / 4)
+    int sf_row_tiles_b;   // 128-row scale tiles of W
+    int out_code, bias_code;
+    int tiles_m, tiles_n;
+};
+
+template <typename TO>
+__device__ __forceinline__ void store_row32(TO* dst, const float (&v)[32], int valid) {
+    // 32 consecutive outputs of one row; `valid` (multiple of 8) of them are inside the matrix
+#pragma unroll
+    for (int g = 0; g < 4; ++g) {
+        if (g * 8 < valid) {
+            float t[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) t[j] = v[g * 8 + j];
+            store8<TO>(dst + g * 8, t);
+        }
+    }
+}
+
+template <bool kFp4>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                        const GemmParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    // 1024-byte alignment for the swizzled operand tiles
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t* stage_base = smem;
+    float* s_bias = reinterpret_cast<float*>(smem + kStages * kStageBytes);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages * kStageBytes + kSmemBias);
+    uint64_t* full = bars;                    // [kStages]  TMA -> MMA
+    uint64_t* empty = bars + kStages;         // [kStages]  MMA -> TMA
+    uint64_t* tmem_full = bars + 2 * kStages; // [2]        MMA -> epilogue
+    uint64_t* tmem_empty = tmem_full + 2;     // [2]        epilogue -> MMA
+    uint32_t* s_tmem_base = reinterpret_cast<uint32_t*>(tmem_empty + 2);
+    volatile int* s_abort = reinterpret_cast<volatile int*>(s_tmem_base + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    constexpr int kElemsPerTile = kFp4 ? 256 : 128;       // K elements per k-tile (128 bytes per row)
+    constexpr int kMmaK = kFp4 ? 64 : 32;
+    constexpr int kSfTilesPerStage = kFp4 ? 4 : 1;        // 512-byte tiles per 128 rows per k-tile
+    const int k_tiles = (p.K + kElemsPerTile - 1) / kElemsPerTile;
+    const int num_tiles = p.tiles_m * p.tiles_n;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+        for (int b = 0; b < 2; ++b) { mbar_init(&tmem_full[b], 1); mbar_init(&tmem_empty[b], 4); }
+        *s_abort = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(s_tmem_base)), "r"(kTmemCols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *s_tmem_base;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ TMA producer
+        uint32_t it = 0;  // k-tiles issued so far (ring position)
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+            const int tm = tile % p.tiles_m, tn = tile / p.tiles_m;
+            const int row_tile_b = (tn * BN) >> 7;  // first 128-row scale tile touched by this W tile
+            for (int kt = 0; kt < k_tiles && ok; ++kt, ++it) {
+                const int s = it % kStages;
+                const uint32_t round = it / kStages;
+                if (round > 0) ok = mbar_wait(&empty[s], (round - 1) & 1, s_abort, kTimeoutEmpty);
+                if (!ok) break;
+                if (lane == 0) {
+                    uint8_t* st = stage_base + s * kStageBytes;
+                    // scale tiles valid in this k-tile (the last one may be short)
+                    const int sf_k0 = kt * kSfTilesPerStage;
+                    int n_sf = p.sf_tiles_k - sf_k0;
+                    if (n_sf > kSfTilesPerStage) n_sf = kSfTilesPerStage;
+                    const uint32_t sf_bytes = (uint32_t)n_sf * 512u;
+                    const int b_tiles = (row_tile_b + 1 < p.sf_row_tiles_b) ? 2 : 1;
+                    mbar_expect_tx(&full[s], kSmemA + kSmemB + sf_bytes * (1 + b_tiles));
+                    tma_load_2d(st, &map_a, kt * 128, tm * BM, &full[s]);
+                    tma_load_2d(st + kSmemA, &map_b, kt * 128, tn * BN, &full[s]);
+                    bulk_load(st + kSmemA + kSmemB, p.sfa + ((size_t)tm * p.sf_tiles_k + sf_k0) * 512, sf_bytes, &full[s]);
+                    for (int t = 0; t < b_tiles; ++t)
+                        bulk_load(st + kSmemA + kSmemB + kSmemSfA + t * (kSmemSfB / 2),
+                                  p.sfb + ((size_t)(row_tile_b + t) * p.sf_tiles_k + sf_k0) * 512, sf_bytes, &full[s]);
+                }
+                __syncwarp();
+            }
+        }
+        // drain: every copy this warp issued must have landed before the CTA may exit
+        const uint32_t first = it > (uint32_t)kStages ? it - kStages : 0;
+        for (uint32_t j = first; j < it; ++j) {
+            const int s = j % kStages;
+            (void)mbar_wait(&full[s], (j / kStages) & 1, s_abort, kTimeoutFull);
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------ MMA issuer
+        const uint32_t idesc_base = (kFp4 ? ((1u << 7) | (1u << 10)) : 0u) | ((uint32_t)(BN >> 3) << 17) |
+                                    (kFp4 ? 0u : (1u << 23)) | ((uint32_t)(BM >> 4) << 24);
+        uint32_t it = 0, local_tile = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local_tile) {
+            const int tn = tile / p.tiles_m;
+            const uint32_t buf = local_tile & 1, use = local_tile >> 1;
+            if (use > 0) ok = mbar_wait(&tmem_empty[buf], (use - 1) & 1, s_abort, kTimeoutTmemEmpty);
+            if (!ok) break;
+            tc_fence_after();
+            const uint32_t d_tmem = tmem_base + (buf ? kTmemAcc1 : kTmemAcc0);
+            // a 192-wide tile that starts mid scale-tile reads its scales 64 rows (two columns) in
+            const uint32_t sfb_shift = ((tn * BN) & 127) ? 2u : 0u;
+            for (int kt = 0; kt < k_tiles && ok; ++kt, ++it) {
+                const int s = it % kStages;
+                ok = mbar_wait(&full[s], (it / kStages) & 1, s_abort, kTimeoutFull);
+                if (!ok) break;
+                tc_fence_after();
+                if (lane == 0) {
+                    const uint32_t st = smem_u32(stage_base + s * kStageBytes);
+                    const int sf_k0 = kt * kSfTilesPerStage;
+                    int n_sf = p.sf_tiles_k - sf_k0;
+                    if (n_sf > kSfTilesPerStage) n_sf = kSfTilesPerStage;
+                    for (int t = 0; t < n_sf; ++t) {
+                        tc_cp_sf(tmem_base + kTmemSfA + 4 * t, desc_sf(st + kSmemA + kSmemB + t * 512));
+                        tc_cp_sf(tmem_base + kTmemSfB + 8 * t, desc_sf(st + kSmemA + kSmemB + kSmemSfA + t * 512));
+                        tc_cp_sf(tmem_base + kTmemSfB + 8 * t + 4,
+                                 desc_sf(st + kSmemA + kSmemB + kSmemSfA + kSmemSfB / 2 + t * 512));
+                    }
+                    const int k_left = p.K - kt * kElemsPerTile;
+                    int n_kb = (k_left + kMmaK - 1) / kMmaK;
+                    if (n_kb > kKbPerTile) n_kb = kKbPerTile;
+                    const uint64_t adesc = desc_sw128(st), bdesc = desc_sw128(st + kSmemA);
+                    for (int kb = 0; kb < n_kb; ++kb) {
+                        // 32 bytes along K per MMA inside the 128-byte swizzled row
+                        const uint64_t koff = (uint64_t)(kb * 32 >> 4);
+                        uint32_t idesc = idesc_base, sfa = tmem_base + kTmemSfA, sfb = tmem_base + kTmemSfB + sfb_shift;
+                        if (kFp4) { sfa += 4 * kb; sfb += 8 * kb; }
+                        else { idesc |= ((uint32_t)kb << 29) | ((uint32_t)kb << 4); }
+                        tc_mma<kFp4>(d_tmem, adesc + koff, bdesc + koff, idesc, (kt > 0 || kb > 0) ? 1u : 0u, sfa, sfb);
+                    }
+                    tc_commit(&empty[s]);                      // stage reusable once these MMAs have read it
+                    if (kt == k_tiles - 1) tc_commit(&tmem_full[buf]);  // accumulator complete
+                }
+                __syncwarp();
+            }
+        }
+    } else {
+        // ------------------------------------------------------------ epilogue (warps 2..5)
+        const int q = warp & 3;  // TMEM lanes 32q .. 32q+31 belong to this warp
+        float* bias_row = s_bias + (warp - 2) * BN;
+        const float alpha = p.alpha ? __ldg(p.alpha) : 1.0f;
+        uint32_t local_tile = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local_tile) {
+            const int tm = tile % p.tiles_m, tn = tile / p.tiles_m;
+            const uint32_t buf = local_tile & 1, use = local_tile >> 1;
+            const int n0 = tn * BN;
+            // bias row for this tile, private to the warp
+            for (int j = lane; j < BN; j += 32) {
+                float b = 0.0f;
+                const int n = n0 + j;
+                if (p.bias && n < p.N) {
+                    if (p.bias_code == CK_F32) b = static_cast<const float*>(p.bias)[n];
+                    else if (p.bias_code == CK_F16) b = __half2float(static_cast<const __half*>(p.bias)[n]);
+                    else b = __bfloat162float(static_cast<const __nv_bfloat16*>(p.bias)[n]);
+                }
+                bias_row[j] = b;
+            }
+            __syncwarp();
+            ok = mbar_wait(&tmem_full[buf], use & 1, s_abort, kTimeoutTmemFull);
+            if (!ok) break;
+            tc_fence_after();
+            const uint32_t acc = tmem_base + (buf ? kTmemAcc1 : kTmemAcc0) + ((uint32_t)(q * 32) << 16);
+            const int row = tm * BM + q * 32 + lane;
+#pragma unroll 1
+            for (int c = 0; c < BN / 32; ++c) {
+                uint32_t r[32];
+                tc_ld32(acc + c * 32, r);
+                tc_wait_ld();
+                float v[32];
+#pragma unroll
+                for (int j = 0; j < 32; ++j) v[j] = fmaf(__uint_as_float(r[j]), alpha, bias_row[c * 32 + j]);
+                const int col = n0 + c * 32;
+                int valid = p.N - col;
+                if (valid > 32) valid = 32;
+                if (row < p.M && valid > 0) {
+                    const size_t off = (size_t)row * p.N + col;
+                    if (p.out_code == CK_BF16) store_row32(static_cast<__nv_bfloat16*>(p.out) + off, v, valid);
+                    else if (p.out_code == CK_F16) store_row32(static_cast<__half*>(p.out) + off, v, valid);
+                    else store_row32(static_cast<float*>(p.out) + off, v, valid);
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&tmem_empty[buf]);
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+    }
+}
+
+// ------------------------------------------------------------------ host side
+
+using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                              const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                              CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeFn get_encode() {
+    static EncodeFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* sym = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeFn>(sym);
+    });
+    return fn;
+}
+
+// [rows, row_bytes] byte matrix, box = 128 bytes x box_rows, 128-byte swizzle, zero fill outside.
+int make_operand_map(CUtensorMap* map, const void* base, int64_t rows, int64_t row_bytes, int box_rows) {
+    EncodeFn enc = get_encode();
+    if (!enc) CK_FAIL(CK_ERR_UNSUPPORTED, "scaled_mm: cuTensorMapEncodeTiled is not available from the driver");
+    cuuint64_t dims[2] = {(cuuint64_t)row_bytes, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)row_bytes};
+    cuuint32_t box[2] = {128u, (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1u, 1u};
+    CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) CK_FAIL(CK_ERR_UNSUPPORTED, "scaled_mm: cuTensorMapEncodeTiled failed with %d", (int)r);
+    return CK_OK;
+}
+
+int sm_count() {
+    static int cached[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 64) return 148;
+    if (cached[dev] == 0) {
+        int n = 0;
+        cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+        cached[dev] = n > 0 ? n : 148;
+    }
+    return cached[dev];
+}
+
+template <bool kFp4>
+int launch_gemm(const void* a, const void* sfa, const void* b, const void* sfb, void* d, const void* bias,
+                int bias_code, int64_t M, int64_t N, int64_t K, const float* alpha, int out_code, cudaStream_t stream) {
+    const char* what = kFp4 ? "scaled_mm_nvfp4" : "scaled_mm_mxfp8";
+    if (!a || !sfa || !b || !sfb || !d) CK_FAIL(CK_ERR_NULL, "%s: null pointer", what);
+    if (M <= 0 || N <= 0 || K <= 0 || M > INT32_MAX || N > INT32_MAX || K > INT32_MAX)
+        CK_FAIL(CK_ERR_SHAPE, "%s: bad shape M=%lld N=%lld K=%lld", what, (long long)M, (long long)N, (long long)K);
+    if (K % 32 != 0 || N % 8 != 0)
+        CK_FAIL(CK_ERR_SHAPE, "%s: K (%lld) must be a multiple of 32 and N (%lld) a multiple of 8", what, (long long)K, (long long)N);
+    if (out_code != CK_F32 && out_code != CK_F16 && out_code != CK_BF16)
+        CK_FAIL(CK_ERR_DTYPE, "%s: unsupported output dtype code %d", what, out_code);
+    if (bias && bias_code != CK_F32 && bias_code != CK_F16 && bias_code != CK_BF16)
+        CK_FAIL(CK_ERR_DTYPE, "%s: unsupported bias dtype code %d", what, bias_code);
+    const int64_t row_bytes = kFp4 ? K / 2 : K;
+    if (!aligned16(a) || !aligned16(b) || !aligned16(sfa) || !aligned16(sfb) || !aligned16(d) || row_bytes % 16 != 0)
+        CK_FAIL(CK_ERR_ALIGN, "%s: operands, scales and output must be 16-byte aligned (row pitch too)", what);
+
+    static bool attr_set[2][64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 64 || !attr_set[kFp4][dev]) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_blockscaled_kernel<kFp4>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+        if (e != cudaSuccess) CK_FAIL((int)e, "%s: cannot reserve %d bytes of shared memory: %s", what, kSmemBytes, cudaGetErrorString(e));
+        if (dev >= 0 && dev < 64) attr_set[kFp4][dev] = true;
+    }
+
+    CUtensorMap map_a, map_b;
+    if (int rc = make_operand_map(&map_a, a, M, row_bytes, BM)) return rc;
+    if (int rc = make_operand_map(&map_b, b, N, row_bytes, BN)) return rc;
+
+    GemmParams p{};
+    p.sfa = static_cast<const uint8_t*>(sfa);
+    p.sfb = static_cast<const uint8_t*>(sfb);
+    p.out = d;
+    p.bias = bias;
+    p.alpha = alpha;
+    p.M = (int)M; p.N = (int)N; p.K = (int)K;
+    const int64_t blk = kFp4 ? 16 : 32;
+    p.sf_tiles_k = (int)(round_up(K / blk, 4) / 4);
+    p.sf_row_tiles_b = (int)ceil_div(N, 128);
+    p.out_code = out_code;
+    p.bias_code = bias_code;
+    p.tiles_m = (int)ceil_div(M, BM);
+    p.tiles_n = (int)ceil_div(N, BN);
+    const int64_t tiles = (int64_t)p.tiles_m * p.tiles_n;
+    const int grid = (int)(tiles < sm_count() ? tiles : sm_count());
+    gemm_blockscaled_kernel<kFp4><<<grid, kThreads, kSmemBytes, stream>>>(map_a, map_b, p);
+    return launch_status(what);
+}
+
+}  // namespace
+}  // namespace ck
+
+// D[M,N] = alpha * (A . W^T) + bias, NVFP4 operands.  A: [M, K/2] bytes, W: [N, K/2] bytes,
+// scales tiled E4M3, alpha: device fp32 scalar (null = 1), bias: [N] or null.
+extern "C" int launch_scaled_mm_nvfp4_kernel(const void* A, const void* A_scale, const void* B, const void* B_scale,
+                                             void* D, const void* bias, int bias_dtype_code, int64_t M, int64_t N,
+                                             int64_t K, const float* alpha_device_ptr, int out_dtype_code,
+                                             cudaStream_t stream) {
+    return ck::launch_gemm<true>(A, A_scale, B, B_scale, D, bias, bias_dtype_code, M, N, K, alpha_device_ptr,
+                                 out_dtype_code, stream);
+}
+
+// Same contraction, MXFP8 operands: A: [M, K] E4M3, W: [N, K] E4M3, scales tiled E8M0.
+extern "C" int launch_scaled_mm_mxfp8_kernel(const void* A, const void* A_scale, const void* B, const void* B_scale,
+                                             void* D, const void* bias, int bias_dtype_code, int64_t M, int64_t N,
+                                             int64_t K, int out_dtype_code, cudaStream_t stream) {
+    return ck::launch_gemm<false>(A, A_scale, B, B_scale, D, bias, bias_dtype_code, M, N, K, nullptr, out_dtype_code,
+                                  stream);
+}
+
+// Argument order and meaning of the reference's entry point (weights first; bias has the
+// output's dtype; workspace unused; accumulate must be false).
+extern "C" int launch_cublas_gemm_blockwise_fp4_kernel(const void* B_ptr, const void* B_decode_scale_ptr,
+                                                       const void* A_ptr, const void* A_decode_scale_ptr, void* D_ptr,
+                                                       const void* bias_ptr, int64_t M, int64_t N, int64_t K,
+                                                       const float* alpha_device_ptr, int out_dtype_code,
+                                                       void* workspace_ptr, bool accumulate, cudaStream_t stream) {
+    (void)workspace_ptr;
+    if (accumulate) CK_FAIL(CK_ERR_UNSUPPORTED, "cublas_gemm_blockwise_fp4: accumulate=true is not supported");
+    return ck::launch_gemm<true>(A_ptr, A_decode_scale_ptr, B_ptr, B_decode_scale_ptr, D_ptr, bias_ptr, out_dtype_code,
+                                 M, N, K, alpha_device_ptr, out_dtype_code, stream);
+}
+
+// Reads and clears the device-side status word of the GEMM kernels (synchronises the device).
+// 0 = no bounded wait ran out since the last call.
+extern "C" int ck_gemm_device_status(void) {
+    int v = 0, zero = 0;
+    cudaError_t e = cudaDeviceSynchronize();
+    if (e != cudaSuccess) CK_FAIL((int)e, "gemm status: %s", cudaGetErrorString(e));
+    e = cudaMemcpyFromSymbol(&v, ck::g_gemm_status, sizeof(int));
+    if (e != cudaSuccess) CK_FAIL((int)e, "gemm status: %s", cudaGetErrorString(e));
+    cudaMemcpyToSymbol(ck::g_gemm_status, &zero, sizeof(int));
+    if (v != 0) ck::set_error("gemm kernel: bounded wait %d ran out in CTA %d", v >> 16, v & 0xffff);
+    return v;
+}

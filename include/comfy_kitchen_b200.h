@@ -1,0 +1,149 @@
+/*
+ * C ABI of libcomfy_kitchen_b200.so — the sm_100a kernels of comfy-kitchen's
+ * quantized-linear hot path (FP8 / NVFP4 / MXFP8 quantizers, block-scaled GEMMs,
+ * RoPE, AdaLN and the fused AdaLN->quantize front end).
+ *
+ * Conventions
+ *   - every pointer is a DEVICE pointer on the current device unless stated;
+ *     the library never allocates, frees or synchronises (ck_gemm_device_status
+ *     excepted) and launches on the stream it is given;
+ *   - dtype codes: 0 float32, 1 float16, 2 bfloat16, 5 float8_e4m3fn, 6 float8_e5m2
+ *     (comfy_kitchen/backends/eager/quantization.py:33-41);
+ *   - block scales use the 128x4 tiled layout of
+ *     comfy_kitchen/float_utils.py:292-326 (to_blocked): scale (r, c) of a tensor
+ *     with C scale columns (C rounded up to 4) lives at byte
+ *       ((r/128)*(C/4) + c/4)*512 + (r%32)*16 + ((r%128)/32)*4 + c%4
+ *     and the buffer covers rows rounded up to 128; quantizers write every byte
+ *     of it (padding = 0);
+ *   - return value: 0 success; negative = argument error (CK_ERR_*); positive =
+ *     cudaError_t of the launch.  ck_last_error() returns a description for the
+ *     calling thread.  The reference's entry points of the same names
+ *     (comfy_kitchen/backends/cuda/dlpack_bindings.cpp:44-209) return void and
+ *     throw C++ exceptions; everything else about their signatures is kept.
+ */
+#ifndef COMFY_KITCHEN_B200_H_
+#define COMFY_KITCHEN_B200_H_
+
+#include <stdbool.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct CUstream_st* ck_stream_t; /* cudaStream_t */
+
+#define CK_OK 0
+#define CK_ERR_DTYPE (-1)
+#define CK_ERR_SHAPE (-2)
+#define CK_ERR_ALIGN (-3)
+#define CK_ERR_NULL (-4)
+#define CK_ERR_UNSUPPORTED (-5)
+#define CK_ERR_DEVICE_TIMEOUT (-6)
+
+/* ---- library ---- */
+const char* ck_last_error(void);
+int ck_abi_version(void);
+int ck_check_device(void); /* 0 when the current device is sm_100 */
+
+/* ---- per-tensor FP8 ----
+ * Replaces launch_quantize_fp8_kernel / launch_dequantize_fp8_kernel
+ * (backends/cuda/dlpack_bindings.cpp:45-52, ops/per_tensor_quantize.cu:170-237).
+ * scale: one device float.  Arithmetic: backends/eager/quantization.py:43-63. */
+int launch_quantize_fp8_kernel(const void* input, void* output, const void* scale, int64_t numel,
+                               int input_dtype_code, int output_dtype_code, ck_stream_t stream);
+int launch_dequantize_fp8_kernel(const void* input, void* output, const void* scale, int64_t numel,
+                                 int input_dtype_code, int output_dtype_code, ck_stream_t stream);
+
+/* ---- NVFP4 ----
+ * Replaces launch_quantize_nvfp4_kernel / launch_dequantize_nvfp4_kernel
+ * (dlpack_bindings.cpp:102-124, ops/quantize_nvfp4.cu:323-435).
+ * input [orig_rows, orig_cols]; output bytes [num_rows, num_cols/2]; block_scales
+ * tiled [roundup(num_rows,128), roundup(num_cols/16,4)]; num_* >= orig_* (the
+ * excess reads as zero; pad_16x of the Python API).  epsilon is accepted and
+ * ignored, as in the reference.  Arithmetic: backends/eager/quantization.py:117-221. */
+int launch_quantize_nvfp4_kernel(const void* input, const void* global_scale, void* output, void* block_scales,
+                                 int64_t num_rows, int64_t num_cols, int64_t orig_rows, int64_t orig_cols,
+                                 float epsilon, int input_dtype_code, bool hi_first, ck_stream_t stream);
+int launch_dequantize_nvfp4_kernel(const void* input, const void* global_scale, const void* block_scales,
+                                   void* output, int64_t num_rows, int64_t num_cols, int output_dtype_code,
+                                   bool hi_first, ck_stream_t stream);
+
+/* ---- MXFP8 ----
+ * launch_quantize_mxfp8_kernel replaces the reference's entry point of that name
+ * (dlpack_bindings.cpp:125-134, ops/quantize_mxfp8.cu:148-208).
+ * launch_dequantize_mxfp8_kernel has no CUDA counterpart in the reference (eager
+ * only: backends/eager/quantization.py:329-366). */
+int launch_quantize_mxfp8_kernel(const void* input, void* output, void* block_scales, int64_t num_rows,
+                                 int64_t num_cols, int64_t orig_rows, int64_t orig_cols, int input_dtype_code,
+                                 ck_stream_t stream);
+int launch_dequantize_mxfp8_kernel(const void* input, const void* block_scales, void* output, int64_t num_rows,
+                                   int64_t num_cols, int output_dtype_code, ck_stream_t stream);
+
+/* ---- block-scaled GEMMs:  D[M,N] = alpha * A[M,K] . W[N,K]^T + bias[N] ----
+ * launch_cublas_gemm_blockwise_fp4_kernel keeps the reference's argument order
+ * (weights first) and meaning (dlpack_bindings.cpp:60-74,
+ * ops/cublas_gemm_nvfp4.cu:295-340): bias has the output dtype, workspace is
+ * unused, accumulate must be false.  launch_scaled_mm_nvfp4_kernel is the same
+ * kernel with activations first and an explicit bias dtype (fp32 allowed).
+ * launch_scaled_mm_mxfp8_kernel has no CUDA counterpart in the reference (eager
+ * forwards to torch: backends/eager/quantization.py:369-404).
+ * K counts elements (multiple of 32); N multiple of 8; alpha is a device float
+ * (NULL = 1). */
+int launch_cublas_gemm_blockwise_fp4_kernel(const void* B_ptr, const void* B_decode_scale_ptr, const void* A_ptr,
+                                            const void* A_decode_scale_ptr, void* D_ptr, const void* bias_ptr,
+                                            int64_t M, int64_t N, int64_t K, const float* alpha_device_ptr,
+                                            int out_dtype_code, void* workspace_ptr, bool accumulate,
+                                            ck_stream_t stream);
+int launch_scaled_mm_nvfp4_kernel(const void* A, const void* A_scale, const void* B, const void* B_scale, void* D,
+                                  const void* bias, int bias_dtype_code, int64_t M, int64_t N, int64_t K,
+                                  const float* alpha_device_ptr, int out_dtype_code, ck_stream_t stream);
+int launch_scaled_mm_mxfp8_kernel(const void* A, const void* A_scale, const void* B, const void* B_scale, void* D,
+                                  const void* bias, int bias_dtype_code, int64_t M, int64_t N, int64_t K,
+                                  int out_dtype_code, ck_stream_t stream);
+/* Synchronises the device, returns and clears the GEMM kernels' status word
+ * (non-zero when a bounded device-side wait ran out). */
+int ck_gemm_device_status(void);
+
+/* ---- RoPE ----
+ * Replaces launch_apply_rope_kernel (dlpack_bindings.cpp:75-101,
+ * ops/apply_rope.cu:358-404).  x is [batch, dim1, dim2, head_dim] with the given
+ * element strides (used for input and output alike); freqs is
+ * [freqs_batch, freqs_dim1, freqs_dim2, head_dim/2, 2, 2], each leading dim 1
+ * (broadcast) or >= x's.  xk / xk_out may both be NULL.
+ * Arithmetic: backends/eager/rope.py:9-32. */
+int launch_apply_rope_kernel(const void* xq, const void* xk, const void* freqs, void* xq_out, void* xk_out,
+                             int64_t batch, int64_t dim1, int64_t dim2, int64_t head_dim, int64_t freqs_batch,
+                             int64_t freqs_dim1, int64_t freqs_dim2, int64_t stride_x_batch, int64_t stride_x_dim1,
+                             int64_t stride_x_dim2, int64_t stride_x_dim, int64_t stride_freqs_batch,
+                             int64_t stride_freqs_dim1, int64_t stride_freqs_dim2, int64_t stride_freqs_dim,
+                             int64_t stride_freqs_rot, int64_t stride_freqs_pair, int input_dtype_code,
+                             int freqs_dtype_code, bool split_half, ck_stream_t stream);
+
+/* ---- AdaLN / RMSNorm ----
+ * launch_adaln_kernel replaces the reference's entry point of that name
+ * (dlpack_bindings.cpp:196-207, ops/adaln.cu:247-300): x, out [N, D]; scale
+ * [N/scale_group, D]; shift [N/shift_group, D]; row r reads modulation row
+ * r/group (backends/_modulation.py:12-57).
+ * launch_rmsnorm_kernel and the two fused norm->quantize entry points have no
+ * counterpart in the reference; their packed outputs equal launch_adaln_kernel
+ * (or launch_rmsnorm_kernel) followed by the matching quantizer, byte for byte.
+ * norm_kind: 0 = LayerNorm + (1+scale), shift; 1 = RMSNorm with weight `scale`
+ * (one row, NULL = no weight) and no shift. */
+int launch_adaln_kernel(const void* x, const void* scale, const void* shift, void* out, int64_t N, int64_t D,
+                        int64_t scale_group, int64_t shift_group, float eps, int dtype_code, ck_stream_t stream);
+int launch_rmsnorm_kernel(const void* x, const void* weight, void* out, int64_t N, int64_t D, float eps,
+                          int dtype_code, ck_stream_t stream);
+int launch_adaln_quantize_nvfp4_kernel(const void* x, const void* scale, const void* shift, const void* global_scale,
+                                       void* output, void* block_scales, int64_t N, int64_t D, int64_t scale_group,
+                                       int64_t shift_group, float eps, int dtype_code, bool hi_first, int norm_kind,
+                                       ck_stream_t stream);
+int launch_adaln_quantize_mxfp8_kernel(const void* x, const void* scale, const void* shift, void* output,
+                                       void* block_scales, int64_t N, int64_t D, int64_t scale_group,
+                                       int64_t shift_group, float eps, int dtype_code, int norm_kind,
+                                       ck_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* COMFY_KITCHEN_B200_H_ */

@@ -1,0 +1,221 @@
+"""GPU parity of the quantizers / dequantizers, through the C ABI, against the CPU oracle
+and the reference-generated fixtures.  Integer outputs must be bit-identical."""
+import pytest
+import torch
+
+from conftest import cases_of
+
+pytestmark = pytest.mark.gpu
+
+DT = {"bf16": torch.bfloat16, "f16": torch.float16, "f32": torch.float32}
+
+
+@pytest.fixture(scope="module")
+def ck():
+    from comfy_kitchen.backends import cuda
+
+    return cuda
+
+
+@pytest.fixture(scope="module")
+def orc():
+    from oracle import ck_oracle
+
+    return ck_oracle
+
+
+def _same_bits(a, b):
+    return torch.equal(a.contiguous().view(torch.uint8).cpu(), b.contiguous().view(torch.uint8).cpu())
+
+
+def _outliers(shape, seed, dtype=torch.bfloat16):
+    g = torch.Generator().manual_seed(seed)
+    x = torch.randn(shape, generator=g)
+    mask = torch.rand(shape, generator=g) < 0.001
+    return torch.where(mask, 50.0 * torch.randn(shape, generator=g), x).to(dtype)
+
+
+# ----------------------------------------------------------------- golden fixtures
+
+
+def test_nvfp4_golden(ck, golden):
+    for c in cases_of(golden, "quantize_nvfp4"):
+        x = c["x"].cuda()
+        q, sf = ck.quantize_nvfp4(x, c["scale"].cuda(), pad_16x=c["pad"], hi_first=c["hi_first"])
+        assert torch.equal(sf.view(torch.uint8).cpu(), c["sf"]), f"scales {tuple(x.shape)} {x.dtype}"
+        assert torch.equal(q.cpu(), c["q"]), f"codes {tuple(x.shape)} {x.dtype}"
+        for name, dt in DT.items():
+            if "dq_" + name in c:
+                out = ck.dequantize_nvfp4(c["q"].cuda(), c["scale"].cuda(), c["sf"].cuda().view(torch.float8_e4m3fn),
+                                          dt, hi_first=c["hi_first"])
+                assert _same_bits(out, c["dq_" + name]), f"dequant {name} {tuple(x.shape)}"
+
+
+def test_mxfp8_golden(ck, golden):
+    for c in cases_of(golden, "quantize_mxfp8"):
+        x = c["x"].cuda()
+        q, sf = ck.quantize_mxfp8(x, pad_32x=c["pad"])
+        assert torch.equal(sf.view(torch.uint8).cpu(), c["sf"]), f"scales {tuple(x.shape)} {x.dtype}"
+        assert torch.equal(q.view(torch.uint8).cpu(), c["q"]), f"data {tuple(x.shape)} {x.dtype}"
+        for name, dt in DT.items():
+            if "dq_" + name in c:
+                out = ck.dequantize_mxfp8(c["q"].cuda().view(torch.float8_e4m3fn),
+                                          c["sf"].cuda().view(torch.float8_e8m0fnu), dt)
+                assert _same_bits(out, c["dq_" + name]), f"dequant {name} {tuple(x.shape)}"
+
+
+def test_fp8_golden(ck, golden):
+    for c in cases_of(golden, "quantize_fp8"):
+        ot = torch.float8_e4m3fn if c["out"] == "e4m3" else torch.float8_e5m2
+        q = ck.quantize_per_tensor_fp8(c["x"].cuda(), c["scale"].cuda(), ot)
+        assert torch.equal(q.view(torch.uint8).cpu(), c["q"]), f"{c['x'].dtype} {c['out']} {float(c['scale'])}"
+        for name, dt in DT.items():
+            if "dq_" + name in c:
+                out = ck.dequantize_per_tensor_fp8(c["q"].cuda().view(ot), c["scale"].cuda(), dt)
+                assert _same_bits(out, c["dq_" + name])
+
+
+# ----------------------------------------------------------------- known answers
+
+
+def test_known_answers(ck):
+    x = (torch.arange(16).float() / 2).reshape(1, 16).bfloat16().cuda()
+    g = torch.tensor(7.5 / (6 * 448), device="cuda")
+    q, sf = ck.quantize_nvfp4(x, g)
+    assert q.flatten().tolist() == [1, 34, 52, 69, 86, 102, 103, 119]
+    assert int(sf.view(torch.uint8)[0, 0]) == 126
+    assert int(sf.view(torch.uint8).sum()) == 126  # every padding byte of the 128x4 buffer is zero
+    x = torch.zeros(1, 16).bfloat16()
+    x[0, 0], x[0, 1] = 6.0, 3.0
+    g = torch.tensor(1.0 / 448, device="cuda")
+    assert int(ck.quantize_nvfp4(x.cuda(), g, hi_first=True)[0][0, 0]) == 0x75
+    assert int(ck.quantize_nvfp4(x.cuda(), g, hi_first=False)[0][0, 0]) == 0x57
+    # E2M1 ties and signed zero: one value per block so the block scale is exactly 1 when amax = 6
+    v = [0, 0.1, 0.25, 0.2500001, 0.5, 0.75, 1, 1.25, 1.5, 1.75, 2, 2.5, 3, 3.5, 4, 5, 5.0000005, 6,
+         -0.25, -0.75, -5, -6, -0.0]
+    want = [0, 0, 0, 1, 1, 2, 2, 2, 3, 4, 4, 4, 5, 6, 6, 6, 7, 7, 8, 10, 14, 15, 8]
+    x = torch.zeros(len(v), 16)
+    x[:, 0] = torch.tensor(v)
+    x[:, 1] = 6.0
+    q, sf = ck.quantize_nvfp4(x.cuda(), torch.tensor(1.0 / 64, device="cuda"))  # block scale 64, total exactly 1
+    assert int(sf.view(torch.uint8)[0, 0]) == 0x68
+    assert (q[:, 0] >> 4).tolist() == want
+    for val, e, qv in [(448.0, 127, 448.0), (449.0, 127, 448.0), (1.75, 119, 448.0), (1e-30, 19, 320.0),
+                       (3e38, 247, 224.0)]:
+        x = torch.zeros(1, 32).bfloat16()
+        x[0, 0] = val
+        q, sf = ck.quantize_mxfp8(x.cuda())
+        assert int(sf.view(torch.uint8)[0, 0]) == e and float(q[0, 0].float()) == qv, val
+    x = torch.tensor([1.0039062, 3.140625, 447, 500]).bfloat16().cuda()
+    assert ck.quantize_per_tensor_fp8(x, torch.tensor(0.3, device="cuda")).view(torch.uint8).tolist() == [69, 82, 126, 126]
+
+
+# ----------------------------------------------------------------- oracle parity on seeded inputs
+
+
+@pytest.mark.parametrize("shape,pad", [((1024, 3072), False), ((129, 128), False), ((33, 65), True),
+                                       ((4608, 256), False), ((200, 1040), False), ((2048, 4096), False)])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
+def test_nvfp4_vs_oracle(ck, orc, shape, pad, dtype):
+    if dtype != torch.bfloat16 and shape[0] * shape[1] > 2_000_000:
+        pytest.skip("large shapes only in bf16")
+    x = _outliers(shape, 1, dtype)
+    g = (x.float().abs().max() / (6.0 * 448.0)).float()
+    q_ref, sf_ref = orc.quantize_nvfp4(x, g, pad_16x=pad)
+    q, sf = ck.quantize_nvfp4(x.cuda(), g.cuda(), pad_16x=pad)
+    assert torch.equal(sf.view(torch.uint8).cpu(), sf_ref.view(torch.uint8))
+    assert torch.equal(q.cpu(), q_ref)
+    for odt in (torch.bfloat16, torch.float32, torch.float16):
+        d = ck.dequantize_nvfp4(q, g.cuda(), sf, odt)
+        assert _same_bits(d, orc.dequantize_nvfp4(q_ref, g, sf_ref, odt))
+
+
+@pytest.mark.parametrize("shape,pad", [((1024, 3072), False), ((65, 96), True), ((257, 288), False),
+                                       ((4608, 128), False), ((2048, 4096), False)])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
+def test_mxfp8_vs_oracle(ck, orc, shape, pad, dtype):
+    if dtype != torch.bfloat16 and shape[0] * shape[1] > 2_000_000:
+        pytest.skip("large shapes only in bf16")
+    x = _outliers(shape, 2, dtype)
+    q_ref, sf_ref = orc.quantize_mxfp8(x, pad_32x=pad)
+    q, sf = ck.quantize_mxfp8(x.cuda(), pad_32x=pad)
+    assert torch.equal(sf.view(torch.uint8).cpu(), sf_ref.view(torch.uint8))
+    assert torch.equal(q.view(torch.uint8).cpu(), q_ref.view(torch.uint8))
+    for odt in (torch.bfloat16, torch.float32, torch.float16):
+        d = ck.dequantize_mxfp8(q, sf, odt)
+        assert _same_bits(d, orc.dequantize_mxfp8(q_ref, sf_ref, odt))
+
+
+def test_mxfp8_tiny_blocks(ck, orc):
+    # blocks whose scale byte is 0 or 1 (|amax| around 2^-118): the reference's 0-scale corner
+    x = torch.zeros(2, 64).bfloat16()
+    x[0, 0], x[0, 1], x[0, 32], x[0, 33] = 2.0 ** -120, -(2.0 ** -125), 2.0 ** -117, 2.0 ** -126
+    x[1, 5] = 2.0 ** -119
+    q_ref, sf_ref = orc.quantize_mxfp8(x)
+    q, sf = ck.quantize_mxfp8(x.cuda())
+    assert torch.equal(sf.view(torch.uint8).cpu(), sf_ref.view(torch.uint8))
+    assert torch.equal(q.view(torch.uint8).cpu(), q_ref.view(torch.uint8))
+
+
+@pytest.mark.parametrize("numel_shape", [(1024, 3072), (7, 13), (4097, 33), (2048, 4096)])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
+@pytest.mark.parametrize("ot", [torch.float8_e4m3fn, torch.float8_e5m2])
+def test_fp8_vs_oracle(ck, orc, numel_shape, dtype, ot):
+    x = _outliers(numel_shape, 3, dtype)
+    lp_max = 448.0 if ot == torch.float8_e4m3fn else 57344.0
+    s = (x.float().abs().max() / lp_max).float()
+    q_ref = orc.quantize_per_tensor_fp8(x, s, ot)
+    q = ck.quantize_per_tensor_fp8(x.cuda(), s.cuda(), ot)
+    assert torch.equal(q.view(torch.uint8).cpu(), q_ref.view(torch.uint8))
+    for odt in (torch.bfloat16, torch.float32, torch.float16):
+        assert _same_bits(ck.dequantize_per_tensor_fp8(q, s.cuda(), odt), orc.dequantize_per_tensor_fp8(q_ref, s, odt))
+
+
+# ----------------------------------------------------------------- size-independent properties at full size
+
+
+def test_full_size_properties(ck, orc):
+    M, K = 65536, 3072
+    g = torch.Generator(device="cuda").manual_seed(1)
+    x = torch.randn(M, K, device="cuda", generator=g, dtype=torch.float32)
+    x = torch.where(torch.rand(M, K, device="cuda", generator=g) < 0.001, 50.0 * x, x).bfloat16()
+    gs = (x.float().abs().max() / (6.0 * 448.0)).float()
+    q, sf = ck.quantize_nvfp4(x, gs)
+    # rows are independent: any row slice quantizes to the same bytes, and the oracle agrees on a sample
+    rows = torch.cat([torch.arange(0, 256), torch.randint(0, M, (1024,), generator=torch.Generator().manual_seed(0))])
+    rows = rows.unique()[: 1152 // 128 * 128]
+    xs = x[rows.cuda()].contiguous()
+    q_s, sf_s = ck.quantize_nvfp4(xs, gs)
+    assert torch.equal(q_s, q[rows.cuda()])
+    q_ref, sf_ref = orc.quantize_nvfp4(xs.cpu(), gs.cpu())
+    assert torch.equal(q_s.cpu(), q_ref) and torch.equal(sf_s.view(torch.uint8).cpu(), sf_ref.view(torch.uint8))
+    # idempotence: quantizing the dequantized tensor with the same scale reproduces codes and scales
+    d = ck.dequantize_nvfp4(q, gs, sf, torch.float32)
+    q2, sf2 = ck.quantize_nvfp4(d, gs)
+    assert torch.equal(sf2.view(torch.uint8), sf.view(torch.uint8)) and torch.equal(q2, q)
+    # MXFP8: same two properties
+    q8, sf8 = ck.quantize_mxfp8(x)
+    d8 = ck.dequantize_mxfp8(q8, sf8, torch.float32)
+    q8b, sf8b = ck.quantize_mxfp8(d8)
+    assert torch.equal(q8b.view(torch.uint8), q8.view(torch.uint8))
+    assert torch.equal(sf8b.view(torch.uint8), sf8.view(torch.uint8))
+    # FP8: dequantize(quantize(x)) requantizes to the same codes
+    s = (x.float().abs().max() / 448.0).float()
+    q1 = ck.quantize_per_tensor_fp8(x, s)
+    assert q1.shape == x.shape
+
+
+def test_argument_errors(ck):
+    x = torch.randn(16, 24, device="cuda").bfloat16()
+    with pytest.raises((AssertionError, RuntimeError)):
+        ck.quantize_nvfp4(x, torch.tensor(1.0, device="cuda"))  # 24 is not a multiple of 16
+    with pytest.raises((AssertionError, RuntimeError)):
+        ck.quantize_mxfp8(x)
+    with pytest.raises(ValueError):
+        ck.quantize_per_tensor_fp8(x, torch.tensor(1.0, device="cuda"), torch.bfloat16)
+    from comfy_kitchen import _native
+    import ctypes
+    with pytest.raises(RuntimeError, match="multiple of 16"):
+        _native.call("launch_quantize_nvfp4_kernel", ctypes.c_void_p(x.data_ptr()), ctypes.c_void_p(x.data_ptr()),
+                     ctypes.c_void_p(x.data_ptr()), ctypes.c_void_p(x.data_ptr()), 16, 24, 16, 24, 0.0, 2, True,
+                     ctypes.c_void_p(0))
