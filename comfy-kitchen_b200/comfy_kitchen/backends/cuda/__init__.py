@@ -414,6 +414,11 @@ def rmsnorm_quantize_nvfp4(
     return qx, sx.view(torch.float8_e4m3fn)
 
 
+def set_option(name: str, value: int) -> None:
+    """Process-wide library option (see ``ck_set_option`` in the C header)."""
+    _native.call("ck_set_option", name.encode(), int(value))
+
+
 def gemm_device_status() -> int:
     """Synchronise and return the GEMM kernels' device status word (0 = fine)."""
     return int(_native.load().ck_gemm_device_status())

@@ -1,6 +1,7 @@
 // Library-level entry points of the C ABI: error text, version, device check.
 #include <cstdarg>
 #include <cstdio>
+#include <cstring>
 
 #include "ck_common.cuh"
 
@@ -20,6 +21,15 @@ void set_error(const char* fmt, ...) {
 extern "C" const char* ck_last_error(void) { return ck::g_error; }
 
 extern "C" int ck_abi_version(void) { return 1; }
+
+namespace ck { int g_nvfp4_exact_div = 0; }
+
+// Library options.  "nvfp4_exact_div": 1 makes the NVFP4 quantizer use plain IEEE divisions
+// instead of the shared-reciprocal sequence (same bytes, slower); used by the tests.
+extern "C" int ck_set_option(const char* name, int value) {
+    if (name && !strcmp(name, "nvfp4_exact_div")) { ck::g_nvfp4_exact_div = value ? 1 : 0; return CK_OK; }
+    CK_FAIL(CK_ERR_UNSUPPORTED, "ck_set_option: unknown option '%s'", name ? name : "(null)");
+}
 
 // 0 when the current device can run this library (compute capability 10.x), else a status.
 extern "C" int ck_check_device(void) {

@@ -97,7 +97,7 @@ norm_warp_kernel(const NormArgs a) {
 
     const T* __restrict__ sc = a.scale ? static_cast<const T*>(a.scale) + (row / a.scale_group) * D : nullptr;
     const T* __restrict__ sh = a.shift ? static_cast<const T*>(a.shift) + (row / a.shift_group) * D : nullptr;
-    const float g = kMode == kOutNvfp4 ? __ldg(a.global_scale) : 0.0f;
+    const Nvfp4Ctx ctx = nvfp4_ctx(kMode == kOutNvfp4 ? __ldg(a.global_scale) : 1.0f);
 
 #pragma unroll
     for (int i = 0; i < kNV; ++i) {
@@ -126,7 +126,7 @@ norm_warp_kernel(const NormArgs a) {
             for (int j = 0; j < 8; ++j) y[j] = Elem<T>::round(y[j]);
             if (kMode == kOutNvfp4) {
                 uint32_t s8;
-                const uint32_t packed = nvfp4_encode_half_block(y, g, a.hi_first != 0, s8);
+                const uint32_t packed = nvfp4_encode_half_block(y, ctx, a.hi_first != 0, s8);
                 if (!ok) s8 = 0u;
                 // four scale bytes (lanes L, L+2, L+4, L+6) leave as one 32-bit store
                 uint32_t w = s8;

@@ -252,29 +252,258 @@ __device__ __forceinline__ void unpack8(const Raw8<float>& r, float (&v)[8]) {
 
 // ------------------------------------------------------------ block encoders
 
-// NVFP4: this lane holds 8 of the 16 elements of a block (its partner is lane^1).
-// Returns 4 bytes of E2M1 codes and the block's E4M3 scale byte.  Must be called
-// by all 32 lanes.  Arithmetic order: see quant_nvfp4.cu.
-__device__ __forceinline__ uint32_t nvfp4_encode_half_block(const float (&v)[8], float g, bool hi_first, uint32_t& s8) {
+// ---- NVFP4 block arithmetic --------------------------------------------------------------
+// The reference divides three times per block/element with IEEE fp32 division:
+//   bs = amax / 6;  sbs = bs / g;  q = x / tot   (tot = g * e4m3(sbs)).
+// A correctly rounded quotient a/b can also be had from the correctly rounded reciprocal
+// r = RN(1/b):  q0 = RN(a*r);  rem = a - b*q0 (exact, one FMA);  q = RN(q0 + rem*r)
+// (Markstein's sequence; it needs b's significand not to be all ones and no under/overflow
+// in q0 and rem).  r is shared by every element of a block (1/tot) or of the tensor (1/g),
+// so the per-element cost drops from a full division to three FMAs.  Wherever the conditions
+// are not met the code below takes the plain IEEE division, so results are bit-identical by
+// construction; where a tiny operand makes `rem` inexact the quotient is far below the
+// smallest rounding boundary that matters (2^-10 for the E4M3 scale, 0.25 for E2M1 codes).
+struct Nvfp4Ctx {
+    float g;    // per-tensor scale
+    float rg;   // RN(1/g)
+    bool fast;  // g admits the reciprocal sequence
+};
+
+__device__ __forceinline__ Nvfp4Ctx nvfp4_ctx(float g) {
+    Nvfp4Ctx c;
+    c.g = g;
+    c.rg = __frcp_rn(g);
+    const uint32_t u = __float_as_uint(g), e = (u >> 23) & 0xffu;
+    c.fast = (u >> 31) == 0u && e >= 40u && e <= 214u && (u & 0x7fffffu) != 0x7fffffu;  // 2^-87 <= g < 2^88
+    return c;
+}
+
+__device__ __forceinline__ float div_by_reciprocal(float a, float b, float r) {
+    const float q0 = __fmul_rn(a, r);
+    return __fmaf_rn(__fmaf_rn(-b, q0, a), r, q0);
+}
+
+struct Nvfp4Block {
+    uint32_t s8;  // E4M3 scale byte
+    float tot;    // g * float(s8)
+    float rtot;   // RN(1/tot) when `fast`
+    bool fast;    // per-element quotients may use the reciprocal sequence
+};
+
+// amax of a 16-element block -> its scale byte and the divisor of its elements.
+template <bool kExactDiv>
+__device__ __forceinline__ Nvfp4Block nvfp4_block_scale(float amax, const Nvfp4Ctx& c) {
+    float sbs;
+    if (!kExactDiv && c.fast) {
+        // exact for every amax >= 2^-125; below that sbs < 2^-38 rounds to scale 0 either way
+        const float bs = div_by_reciprocal(amax, 6.0f, 0.16666667163372040f /* RN(1/6) */);
+        // an overflowing quotient turns into NaN here and fminf returns the other operand, 448
+        sbs = div_by_reciprocal(bs, c.g, c.rg);
+    } else {
+        sbs = __fdiv_rn(__fdiv_rn(amax, 6.0f), c.g);
+    }
+    sbs = fminf(sbs, 448.0f);
+    Nvfp4Block b;
+    b.s8 = cvt_e4m3x2(0.0f, sbs) & 0xffu;
+    b.tot = __fmul_rn(c.g, e4m3_to_f32(b.s8));
+    const uint32_t u = __float_as_uint(b.tot), e = (u >> 23) & 0xffu;
+    // 2^-64 <= tot < 2^65, significand not all ones, |x| <= amax < 2^60 (no overflow in x * rtot)
+    b.fast = !kExactDiv && e >= 63u && e <= 191u && (u & 0x7fffffu) != 0x7fffffu &&
+             ((__float_as_uint(amax) >> 23) & 0xffu) < 187u;
+    b.rtot = b.fast ? __frcp_rn(b.tot) : 0.0f;
+    return b;
+}
+
+// Eight elements of a block -> four bytes of E2M1 codes (element 2i and 2i+1 share byte i).
+__device__ __forceinline__ uint32_t nvfp4_codes8(const float (&v)[8], const Nvfp4Block& b, bool hi_first) {
+    if (b.tot == 0.0f) return 0u;
+    float q[8];
+    if (b.fast) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i)  // the quotient's sign is x's (tot > 0); the FMA pair loses it for x = -0
+            q[i] = copysignf(div_by_reciprocal(v[i], b.tot, b.rtot), v[i]);
+    } else {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) q[i] = __fdiv_rn(v[i], b.tot);
+    }
+    uint32_t out;
+    if (hi_first) {
+        asm("{ .reg .b8 t0, t1, t2, t3;\n"
+            "cvt.rn.satfinite.e2m1x2.f32 t0, %1, %2; cvt.rn.satfinite.e2m1x2.f32 t1, %3, %4;\n"
+            "cvt.rn.satfinite.e2m1x2.f32 t2, %5, %6; cvt.rn.satfinite.e2m1x2.f32 t3, %7, %8;\n"
+            "mov.b32 %0, {t0, t1, t2, t3}; }"
+            : "=r"(out) : "f"(q[0]), "f"(q[1]), "f"(q[2]), "f"(q[3]), "f"(q[4]), "f"(q[5]), "f"(q[6]), "f"(q[7]));
+    } else {
+        asm("{ .reg .b8 t0, t1, t2, t3;\n"
+            "cvt.rn.satfinite.e2m1x2.f32 t0, %2, %1; cvt.rn.satfinite.e2m1x2.f32 t1, %4, %3;\n"
+            "cvt.rn.satfinite.e2m1x2.f32 t2, %6, %5; cvt.rn.satfinite.e2m1x2.f32 t3, %8, %7;\n"
+            "mov.b32 %0, {t0, t1, t2, t3}; }"
+            : "=r"(out) : "f"(q[0]), "f"(q[1]), "f"(q[2]), "f"(q[3]), "f"(q[4]), "f"(q[5]), "f"(q[6]), "f"(q[7]));
+    }
+    return out;
+}
+
+// This lane holds 8 of the 16 elements of a block (its partner is lane^1).  Returns 4 bytes of
+// codes and the block's scale byte.  Must be called by all 32 lanes.
+template <bool kExactDiv = false>
+__device__ __forceinline__ uint32_t nvfp4_encode_half_block(const float (&v)[8], const Nvfp4Ctx& c, bool hi_first,
+                                                            uint32_t& s8) {
     float amax = 0.0f;
 #pragma unroll
     for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
     amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
-    const float bs = __fdiv_rn(amax, 6.0f);
-    const float sbs = fminf(__fdiv_rn(bs, g), 448.0f);
-    s8 = cvt_e4m3x2(0.0f, sbs) & 0xffu;
-    const float tot = __fmul_rn(g, e4m3_to_f32(s8));
-    uint32_t packed = 0;
-    if (tot != 0.0f) {
+    const Nvfp4Block b = nvfp4_block_scale<kExactDiv>(amax, c);
+    s8 = b.s8;
+    return nvfp4_codes8(v, b, hi_first);
+}
+
+// A whole 16-element block held by one thread -> 8 bytes of codes and the scale byte.
+template <bool kExactDiv = false>
+__device__ __forceinline__ uint2 nvfp4_encode_block(const float (&v)[16], const Nvfp4Ctx& c, bool hi_first, uint32_t& s8) {
+    float amax = 0.0f;
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const float a = __fdiv_rn(v[2 * i], tot);
-            const float b = __fdiv_rn(v[2 * i + 1], tot);
-            const uint32_t byte = hi_first ? cvt_e2m1x2(a, b) : cvt_e2m1x2(b, a);
-            packed |= (byte & 0xffu) << (8 * i);
-        }
+    for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(v[i]));
+    const Nvfp4Block b = nvfp4_block_scale<kExactDiv>(amax, c);
+    s8 = b.s8;
+    float lo[8], hi[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) { lo[i] = v[i]; hi[i] = v[8 + i]; }
+    return make_uint2(nvfp4_codes8(lo, b, hi_first), nvfp4_codes8(hi, b, hi_first));
+}
+
+// ---- 256-bit global accesses (sm_100) -------------------------------------------------------
+__device__ __forceinline__ void ldg256(const void* p, uint32_t (&r)[8]) {
+    asm volatile("ld.global.nc.L1::no_allocate.v8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+                 : "l"(p));
+}
+__device__ __forceinline__ void stg256(void* p, const uint32_t (&r)[8]) {
+    asm volatile("st.global.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};"
+                 ::"l"(p), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
+                 : "memory");
+}
+
+// 16 consecutive elements (32-byte aligned) as fp32.
+template <typename T>
+__device__ __forceinline__ void load16(const T* __restrict__ p, float (&v)[16]);
+template <>
+__device__ __forceinline__ void load16<__nv_bfloat16>(const __nv_bfloat16* __restrict__ p, float (&v)[16]) {
+    uint32_t w[8];
+    ldg256(p, w);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        v[2 * i] = __uint_as_float(w[i] << 16);
+        v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
     }
-    return packed;
+}
+template <>
+__device__ __forceinline__ void load16<__half>(const __half* __restrict__ p, float (&v)[16]) {
+    uint32_t w[8];
+    ldg256(p, w);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
+        v[2 * i] = f.x;
+        v[2 * i + 1] = f.y;
+    }
+}
+template <>
+__device__ __forceinline__ void load16<float>(const float* __restrict__ p, float (&v)[16]) {
+    uint32_t w[8];
+    ldg256(p, w);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(w[i]);
+    ldg256(p + 8, w);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) v[8 + i] = __uint_as_float(w[i]);
+}
+
+// 16 consecutive elements kept packed in registers (8 registers for 16-bit types, 16 for fp32).
+template <typename T> struct Raw16 { uint32_t w[8]; };
+template <> struct Raw16<float> { uint32_t w[16]; };
+
+template <typename T>
+__device__ __forceinline__ void load_raw16(const T* __restrict__ p, Raw16<T>& r) { ldg256(p, r.w); }
+template <>
+__device__ __forceinline__ void load_raw16<float>(const float* __restrict__ p, Raw16<float>& r) {
+    uint32_t a[8], b[8];
+    ldg256(p, a);
+    ldg256(p + 8, b);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) { r.w[i] = a[i]; r.w[8 + i] = b[i]; }
+}
+template <typename T>
+__device__ __forceinline__ void zero_raw16(Raw16<T>& r) {
+#pragma unroll
+    for (int i = 0; i < (int)(sizeof(r.w) / 4); ++i) r.w[i] = 0u;
+}
+__device__ __forceinline__ void unpack16(const Raw16<__nv_bfloat16>& r, float (&v)[16]) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        v[2 * i] = __uint_as_float(r.w[i] << 16);
+        v[2 * i + 1] = __uint_as_float(r.w[i] & 0xffff0000u);
+    }
+}
+__device__ __forceinline__ void unpack16(const Raw16<__half>& r, float (&v)[16]) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&r.w[i]));
+        v[2 * i] = f.x;
+        v[2 * i + 1] = f.y;
+    }
+}
+__device__ __forceinline__ void unpack16(const Raw16<float>& r, float (&v)[16]) {
+#pragma unroll
+    for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r.w[i]);
+}
+
+// 16 consecutive fp32 values rounded to T and stored (32-byte aligned).
+template <typename T>
+__device__ __forceinline__ void store16(T* __restrict__ p, const float (&v)[16]);
+template <>
+__device__ __forceinline__ void store16<__nv_bfloat16>(__nv_bfloat16* __restrict__ p, const float (&v)[16]) {
+    uint32_t w[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+        w[i] = *reinterpret_cast<const uint32_t*>(&h);
+    }
+    stg256(p, w);
+}
+template <>
+__device__ __forceinline__ void store16<__half>(__half* __restrict__ p, const float (&v)[16]) {
+    uint32_t w[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const __half2 h = __floats2half2_rn(v[2 * i], v[2 * i + 1]);
+        w[i] = *reinterpret_cast<const uint32_t*>(&h);
+    }
+    stg256(p, w);
+}
+template <>
+__device__ __forceinline__ void store16<float>(float* __restrict__ p, const float (&v)[16]) {
+    uint32_t w[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) w[i] = __float_as_uint(v[i]);
+    stg256(p, w);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) w[i] = __float_as_uint(v[8 + i]);
+    stg256(p + 8, w);
+}
+
+// Four bytes of E2M1 codes -> eight fp32 values in element order.
+__device__ __forceinline__ void e2m1x8_to_f32(uint32_t codes, bool hi_first, float (&v)[8]) {
+    uint32_t h[4];
+    asm("{ .reg .b8 t0, t1, t2, t3; mov.b32 {t0, t1, t2, t3}, %4;\n"
+        "cvt.rn.f16x2.e2m1x2 %0, t0; cvt.rn.f16x2.e2m1x2 %1, t1;\n"
+        "cvt.rn.f16x2.e2m1x2 %2, t2; cvt.rn.f16x2.e2m1x2 %3, t3; }"
+        : "=r"(h[0]), "=r"(h[1]), "=r"(h[2]), "=r"(h[3]) : "r"(codes));
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&h[i]));  // x = low nibble, y = high nibble
+        v[2 * i] = hi_first ? f.y : f.x;
+        v[2 * i + 1] = hi_first ? f.x : f.y;
+    }
 }
 
 // E8M0 byte for a block amax: clamp(ceil(log2(max(amax/448, 2^-127))) + 127, 0, 254),

@@ -58,6 +58,10 @@ constexpr int kSmemBytes = kStages * kStageBytes + kSmemBias + 256 /*barriers*/ 
 constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kTmemAcc0 = 0, kTmemAcc1 = 256, kTmemSfA = 448, kTmemSfB = 464;
 
+#ifndef CK_GEMM_PROBE
+#define CK_GEMM_PROBE 0   // timing experiments only: 1 = no scale copies, 2 = no TMA payload, 4 = no MMA
+#endif
+
 constexpr uint32_t kSpinLimit = 1u << 22;   // polls of mbarrier.try_wait before giving up (a fraction of a second)
 
 __device__ int g_gemm_status = 0;           // 0 ok; otherwise (code << 16 | detail) of the first failure
@@ -99,6 +103,14 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
     return __all_sync(0xffffffffu, done);
 }
 
+// One lane of a converged warp, chosen by the hardware.  Code that wraps a single asm statement in
+// `if (elect_one())` stays warp-uniform, so its operands can live in uniform registers.
+__device__ __forceinline__ bool elect_one() {
+    uint32_t pred;
+    asm volatile("{ .reg .pred p; elect.sync _|p, 0xffffffff; selp.u32 %0, 1, 0, p; }" : "=r"(pred));
+    return pred != 0;
+}
+
 __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int c0, int c1, uint64_t* bar) {
     asm volatile(
         "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
@@ -113,25 +125,47 @@ __device__ __forceinline__ void bulk_load(void* dst, const void* src, uint32_t b
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 
+// The tcgen05 issue wrappers below are called by all 32 lanes of the issuing warp with identical
+// arguments; one elected lane executes the instruction.
 __device__ __forceinline__ void tc_commit(uint64_t* bar) {
+    if (elect_one())
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
-__device__ __forceinline__ void tc_cp_sf(uint32_t tmem_addr, uint64_t sdesc) {
-    asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(tmem_addr), "l"(sdesc) : "memory");
+// Shared-memory descriptors are built from a 32-bit low word (start address >> 4, plus the
+// leading-offset field for the swizzled form) and a constant high word:
+//   operand tiles: K-major, 128-byte rows, 128-byte swizzle, 8-row groups 1024 bytes apart
+//                  -> hi = SBO 64 | version 1 (bit 46) | layout SWIZZLE_128B (bits 61-63)
+//   scale tiles:   32 rows x 16 bytes, unswizzled, 8-row groups 128 bytes apart
+//                  -> hi = SBO 8 | version 1
+constexpr uint32_t kDescHiOperand = 64u | (1u << 14) | (2u << 29);
+constexpr uint32_t kDescHiScale = 8u | (1u << 14);
+constexpr uint32_t kDescLoLbo1 = 1u << 16;
+
+__device__ __forceinline__ void tc_cp_sf(uint32_t tmem_addr, uint32_t desc_lo) {
+    if (CK_GEMM_PROBE & 1) return;
+    if (elect_one())
+    asm volatile(
+        "{ .reg .b64 d; mov.b64 d, {%1, %2};\n"
+        "tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], d; }"
+        ::"r"(tmem_addr), "r"(desc_lo), "n"(kDescHiScale) : "memory");
 }
 template <bool kFp4>
-__device__ __forceinline__ void tc_mma(uint32_t d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate,
+__device__ __forceinline__ void tc_mma(uint32_t d, uint32_t a_lo, uint32_t b_lo, uint32_t idesc, uint32_t accumulate,
                                        uint32_t sfa, uint32_t sfb) {
+    if (CK_GEMM_PROBE & 4) return;
+    if (!elect_one()) return;
     if (kFp4) {
         asm volatile(
-            "{ .reg .pred p; setp.ne.b32 p, %4, 0;\n"
-            "tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.block16 [%0], %1, %2, %3, [%5], [%6], p; }"
-            ::"r"(d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(sfa), "r"(sfb) : "memory");
+            "{ .reg .pred p; .reg .b64 da, db; setp.ne.b32 p, %4, 0;\n"
+            "mov.b64 da, {%1, %7}; mov.b64 db, {%2, %7};\n"
+            "tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.block16 [%0], da, db, %3, [%5], [%6], p; }"
+            ::"r"(d), "r"(a_lo), "r"(b_lo), "r"(idesc), "r"(accumulate), "r"(sfa), "r"(sfb), "n"(kDescHiOperand) : "memory");
     } else {
         asm volatile(
-            "{ .reg .pred p; setp.ne.b32 p, %4, 0;\n"
-            "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p; }"
-            ::"r"(d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(sfa), "r"(sfb) : "memory");
+            "{ .reg .pred p; .reg .b64 da, db; setp.ne.b32 p, %4, 0;\n"
+            "mov.b64 da, {%1, %7}; mov.b64 db, {%2, %7};\n"
+            "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale [%0], da, db, %3, [%5], [%6], p; }"
+            ::"r"(d), "r"(a_lo), "r"(b_lo), "r"(idesc), "r"(accumulate), "r"(sfa), "r"(sfb), "n"(kDescHiOperand) : "memory");
     }
 }
 __device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
@@ -146,16 +180,6 @@ __device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
         : "r"(taddr) : "memory");
 }
 __device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-
-// Shared-memory matrix descriptor, K-major operand tile with 128-byte rows and the
-// 128-byte swizzle (8-row groups 1024 bytes apart).
-__device__ __forceinline__ uint64_t desc_sw128(uint32_t saddr) {
-    return (uint64_t)((saddr & 0x3ffffu) >> 4) | (1ull << 16) | ((uint64_t)(1024 >> 4) << 32) | (1ull << 46) | (2ull << 61);
-}
-// Descriptor of one 512-byte scale tile: 32 rows x 16 bytes, unswizzled, 8-row groups 128 bytes apart.
-__device__ __forceinline__ uint64_t desc_sf(uint32_t saddr) {
-    return (uint64_t)((saddr & 0x3ffffu) >> 4) | ((uint64_t)(128 >> 4) << 32) | (1ull << 46);
-}
 
 struct GemmParams {
     const uint8_t* sfa;
@@ -231,26 +255,35 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
         for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
             const int tm = tile % p.tiles_m, tn = tile / p.tiles_m;
             const int row_tile_b = (tn * BN) >> 7;  // first 128-row scale tile touched by this W tile
+            const int b_tiles = (row_tile_b + 1 < p.sf_row_tiles_b) ? 2 : 1;
+            const size_t sf_row_pitch = (size_t)p.sf_tiles_k * 512;
+            const uint8_t* sfa_src = p.sfa + (size_t)tm * sf_row_pitch;
+            const uint8_t* sfb_src = p.sfb + (size_t)row_tile_b * sf_row_pitch;
             for (int kt = 0; kt < k_tiles && ok; ++kt, ++it) {
                 const int s = it % kStages;
                 const uint32_t round = it / kStages;
                 if (round > 0) ok = mbar_wait(&empty[s], (round - 1) & 1, s_abort, kTimeoutEmpty);
                 if (!ok) break;
-                if (lane == 0) {
-                    uint8_t* st = stage_base + s * kStageBytes;
-                    // scale tiles valid in this k-tile (the last one may be short)
-                    const int sf_k0 = kt * kSfTilesPerStage;
-                    int n_sf = p.sf_tiles_k - sf_k0;
-                    if (n_sf > kSfTilesPerStage) n_sf = kSfTilesPerStage;
-                    const uint32_t sf_bytes = (uint32_t)n_sf * 512u;
-                    const int b_tiles = (row_tile_b + 1 < p.sf_row_tiles_b) ? 2 : 1;
-                    mbar_expect_tx(&full[s], kSmemA + kSmemB + sf_bytes * (1 + b_tiles));
-                    tma_load_2d(st, &map_a, kt * 128, tm * BM, &full[s]);
-                    tma_load_2d(st + kSmemA, &map_b, kt * 128, tn * BN, &full[s]);
-                    bulk_load(st + kSmemA + kSmemB, p.sfa + ((size_t)tm * p.sf_tiles_k + sf_k0) * 512, sf_bytes, &full[s]);
-                    for (int t = 0; t < b_tiles; ++t)
-                        bulk_load(st + kSmemA + kSmemB + kSmemSfA + t * (kSmemSfB / 2),
-                                  p.sfb + ((size_t)(row_tile_b + t) * p.sf_tiles_k + sf_k0) * 512, sf_bytes, &full[s]);
+                // operands are computed by the whole warp; one elected lane issues the copies
+                uint8_t* st = stage_base + s * kStageBytes;
+                int n_sf = p.sf_tiles_k - kt * kSfTilesPerStage;  // scale tiles valid in this k-tile (the last may be short)
+                if (n_sf > kSfTilesPerStage) n_sf = kSfTilesPerStage;
+                const uint32_t sf_bytes = (uint32_t)n_sf * 512u;
+                const size_t sf_off = (size_t)kt * (kSfTilesPerStage * 512);
+                const uint32_t tx_bytes = kSmemA + kSmemB + sf_bytes * (1 + b_tiles);
+                if (elect_one()) {
+                    if (CK_GEMM_PROBE & 2) {
+                        mbar_arrive(&full[s]);
+                    } else {
+                        mbar_expect_tx(&full[s], tx_bytes);
+                        tma_load_2d(st, &map_a, kt * 128, tm * BM, &full[s]);
+                        tma_load_2d(st + kSmemA, &map_b, kt * 128, tn * BN, &full[s]);
+                        bulk_load(st + kSmemA + kSmemB, sfa_src + sf_off, sf_bytes, &full[s]);
+                        bulk_load(st + kSmemA + kSmemB + kSmemSfA, sfb_src + sf_off, sf_bytes, &full[s]);
+                        if (b_tiles == 2)
+                            bulk_load(st + kSmemA + kSmemB + kSmemSfA + kSmemSfB / 2, sfb_src + sf_row_pitch + sf_off,
+                                      sf_bytes, &full[s]);
+                    }
                 }
                 __syncwarp();
             }
@@ -263,8 +296,15 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------ MMA issuer
-        const uint32_t idesc_base = (kFp4 ? ((1u << 7) | (1u << 10)) : 0u) | ((uint32_t)(BN >> 3) << 17) |
+#ifdef CK_PROBE_N
+        constexpr int kInstrN = CK_PROBE_N;   // timing experiment: instruction N differs from the tile (wrong results)
+#else
+        constexpr int kInstrN = BN;
+#endif
+        const uint32_t idesc_base = (kFp4 ? ((1u << 7) | (1u << 10)) : 0u) | ((uint32_t)(kInstrN >> 3) << 17) |
                                     (kFp4 ? 0u : (1u << 23)) | ((uint32_t)(BM >> 4) << 24);
+        const uint32_t smem16 = (smem_u32(stage_base) & 0x3ffffu) >> 4;
+        const bool tail_full = (p.K % kElemsPerTile) == 0;
         uint32_t it = 0, local_tile = 0;
         bool ok = true;
         for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local_tile) {
@@ -281,28 +321,45 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
                 ok = mbar_wait(&full[s], (it / kStages) & 1, s_abort, kTimeoutFull);
                 if (!ok) break;
                 tc_fence_after();
-                if (lane == 0) {
-                    const uint32_t st = smem_u32(stage_base + s * kStageBytes);
-                    const int sf_k0 = kt * kSfTilesPerStage;
-                    int n_sf = p.sf_tiles_k - sf_k0;
-                    if (n_sf > kSfTilesPerStage) n_sf = kSfTilesPerStage;
-                    for (int t = 0; t < n_sf; ++t) {
-                        tc_cp_sf(tmem_base + kTmemSfA + 4 * t, desc_sf(st + kSmemA + kSmemB + t * 512));
-                        tc_cp_sf(tmem_base + kTmemSfB + 8 * t, desc_sf(st + kSmemA + kSmemB + kSmemSfA + t * 512));
-                        tc_cp_sf(tmem_base + kTmemSfB + 8 * t + 4,
-                                 desc_sf(st + kSmemA + kSmemB + kSmemSfA + kSmemSfB / 2 + t * 512));
-                    }
-                    const int k_left = p.K - kt * kElemsPerTile;
-                    int n_kb = (k_left + kMmaK - 1) / kMmaK;
-                    if (n_kb > kKbPerTile) n_kb = kKbPerTile;
-                    const uint64_t adesc = desc_sw128(st), bdesc = desc_sw128(st + kSmemA);
-                    for (int kb = 0; kb < n_kb; ++kb) {
-                        // 32 bytes along K per MMA inside the 128-byte swizzled row
-                        const uint64_t koff = (uint64_t)(kb * 32 >> 4);
-                        uint32_t idesc = idesc_base, sfa = tmem_base + kTmemSfA, sfb = tmem_base + kTmemSfB + sfb_shift;
-                        if (kFp4) { sfa += 4 * kb; sfb += 8 * kb; }
-                        else { idesc |= ((uint32_t)kb << 29) | ((uint32_t)kb << 4); }
-                        tc_mma<kFp4>(d_tmem, adesc + koff, bdesc + koff, idesc, (kt > 0 || kb > 0) ? 1u : 0u, sfa, sfb);
+                {
+                    // every descriptor of this stage is "stage start >> 4" plus a constant
+                    const uint32_t st16 = smem16 + (uint32_t)s * (kStageBytes >> 4);
+                    const uint32_t a_lo = st16 | kDescLoLbo1, b_lo = (st16 + (kSmemA >> 4)) | kDescLoLbo1;
+                    const uint32_t sfa16 = st16 + ((kSmemA + kSmemB) >> 4), sfb16 = sfa16 + (kSmemSfA >> 4);
+                    const uint32_t t_sfa = tmem_base + kTmemSfA, t_sfb = tmem_base + kTmemSfB;
+                    if (kt + 1 < k_tiles || tail_full) {
+                        // full k-tile: all scale tiles and four MMAs, fully unrolled
+#pragma unroll
+                        for (int t = 0; t < kSfTilesPerStage; ++t) {
+                            tc_cp_sf(t_sfa + 4 * t, sfa16 + t * 32);
+                            tc_cp_sf(t_sfb + 8 * t, sfb16 + t * 32);
+                            tc_cp_sf(t_sfb + 8 * t + 4, sfb16 + (kSmemSfB >> 5) + t * 32);
+                        }
+#pragma unroll
+                        for (int kb = 0; kb < kKbPerTile; ++kb) {
+                            // 32 bytes along K per MMA inside the 128-byte swizzled row
+                            uint32_t idesc = idesc_base, sfa = t_sfa, sfb = t_sfb + sfb_shift;
+                            if (kFp4) { sfa += 4 * kb; sfb += 8 * kb; }
+                            else { idesc |= ((uint32_t)kb << 29) | ((uint32_t)kb << 4); }
+                            tc_mma<kFp4>(d_tmem, a_lo + 2 * kb, b_lo + 2 * kb, idesc, (kt > 0 || kb > 0) ? 1u : 0u, sfa, sfb);
+                        }
+                    } else {
+                        // last, short k-tile
+                        int n_sf = p.sf_tiles_k - kt * kSfTilesPerStage;
+                        if (n_sf > kSfTilesPerStage) n_sf = kSfTilesPerStage;
+                        for (int t = 0; t < n_sf; ++t) {
+                            tc_cp_sf(t_sfa + 4 * t, sfa16 + t * 32);
+                            tc_cp_sf(t_sfb + 8 * t, sfb16 + t * 32);
+                            tc_cp_sf(t_sfb + 8 * t + 4, sfb16 + (kSmemSfB >> 5) + t * 32);
+                        }
+                        const int k_left = p.K - kt * kElemsPerTile;
+                        const int n_kb = (k_left + kMmaK - 1) / kMmaK;
+                        for (int kb = 0; kb < n_kb; ++kb) {
+                            uint32_t idesc = idesc_base, sfa = t_sfa, sfb = t_sfb + sfb_shift;
+                            if (kFp4) { sfa += 4 * kb; sfb += 8 * kb; }
+                            else { idesc |= ((uint32_t)kb << 29) | ((uint32_t)kb << 4); }
+                            tc_mma<kFp4>(d_tmem, a_lo + 2 * kb, b_lo + 2 * kb, idesc, (kt > 0 || kb > 0) ? 1u : 0u, sfa, sfb);
+                        }
                     }
                     tc_commit(&empty[s]);                      // stage reusable once these MMAs have read it
                     if (kt == k_tiles - 1) tc_commit(&tmem_full[buf]);  // accumulator complete

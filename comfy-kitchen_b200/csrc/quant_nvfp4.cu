@@ -6,85 +6,86 @@
 // bit-identical (comfy_kitchen/backends/eager/quantization.py:117-221):
 //   amax -> bs = amax/6 -> sbs = min(bs/g, 448) -> s8 = e4m3_rne(sbs)
 //   tot = g*float(s8);  tot == 0 -> codes 0;  else code = e2m1_rne(clamp(x/tot, +-6))
-// All divisions are IEEE (this file is compiled without fast-math).
+// The divisions are IEEE-exact (ck_common.cuh: "NVFP4 block arithmetic"); this file
+// is compiled without fast-math.
 //
 // Work decomposition (HBM-bound, 2.5625 algorithmic bytes per element for bf16):
-// one CTA of 256 threads owns a tile of 128 rows x 256 columns.  A warp reads one
-// 512-byte row segment per step with one 128-bit load per lane (8 elements = half
-// a block; the two lanes of a block combine their amax with one shuffle), and
-// writes 4 bytes of codes per lane.  The tile's block scales are staged in shared
-// memory in the GEMM's 128x4 tiled order and leave as 16-byte stores, so every
-// byte of the padded scale buffer is written by exactly one CTA (no memset pass).
+// one CTA of 256 threads owns a tile of 128 rows x 256 columns.  A thread owns whole
+// 16-element blocks: one 256-bit load in (two for fp32), 8 bytes of codes out; a
+// warp covers two 512-byte row segments per step.  The tile's block scales are
+// staged in shared memory in the GEMM's 128x4 tiled order and leave as 16-byte
+// stores, so every byte of the padded scale buffer is written by exactly one CTA
+// (no memset pass).
 #include "ck_common.cuh"
 
 namespace ck {
+
+// 0 = reciprocal-sequence divisions (default), 1 = plain IEEE divisions everywhere.
+// Both produce the same bytes; the switch exists so tests can check that on the device.
+extern int g_nvfp4_exact_div;
+
 namespace {
 
 constexpr int kTileRows = 128;
 constexpr int kTileCols = 256;
 constexpr int kThreads = 256;
-constexpr int kWarps = kThreads / 32;
-constexpr int kSfTiles = kTileCols / 64;  // 512-byte scale tiles per CTA tile
+constexpr int kRowsPerStep = kThreads / 16;  // 16 threads (one block each) cover a 256-column row segment
+constexpr int kSfTiles = kTileCols / 64;     // 512-byte scale tiles per CTA tile
 
-// Scalar tail loader: 8 elements with bounds checks, zero beyond the source.
+// Scalar loader: 16 elements with bounds checks, zero beyond the source.
 template <typename T>
-__device__ __forceinline__ void load8_guarded(const T* __restrict__ x, int64_t row, int64_t col, int64_t orig_rows,
-                                              int64_t orig_cols, float (&v)[8]) {
+__device__ __forceinline__ void load16_guarded(const T* __restrict__ x, int64_t row, int64_t col, int64_t orig_rows,
+                                               int64_t orig_cols, float (&v)[16]) {
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
+    for (int i = 0; i < 16; ++i) {
         int64_t c = col + i;
         v[i] = (row < orig_rows && c < orig_cols) ? Elem<T>::to_f32(x[row * orig_cols + c]) : 0.0f;
     }
 }
 
-template <typename T, bool kVec>
+template <typename T, bool kVec, bool kExactDiv>
 __global__ void __launch_bounds__(kThreads)
 quantize_nvfp4_kernel(const T* __restrict__ x, const float* __restrict__ global_scale, uint8_t* __restrict__ q,
                       uint8_t* __restrict__ sf, int64_t rows, int64_t cols, int64_t orig_rows, int64_t orig_cols,
                       int64_t sf_cpad, bool hi_first) {
     __shared__ __align__(16) uint8_t s_sf[kSfTiles * 512];
 
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int tid = threadIdx.x;
+    const int blk = tid & 15;          // block index inside the 256-column tile
+    const int sub = tid >> 4;          // row inside one step
     const int64_t row0 = (int64_t)blockIdx.y * kTileRows;
-    const int64_t col0 = (int64_t)blockIdx.x * kTileCols;
-    const float g = __ldg(global_scale);
+    const int64_t col = (int64_t)blockIdx.x * kTileCols + blk * 16;
+    const Nvfp4Ctx ctx = nvfp4_ctx(__ldg(global_scale));
 
     // scale bytes of rows/columns outside the tensor must read as zero
     reinterpret_cast<uint2*>(s_sf)[tid] = make_uint2(0u, 0u);
     __syncthreads();
 
-    const int64_t col = col0 + lane * 8;
     const bool col_ok = col < cols;
-    const int blk_in_tile = lane >> 1;  // 16-element block index inside the 256-column tile
-
     constexpr int kUnroll = 4;
 #pragma unroll 1
-    for (int it = 0; it < kTileRows / kWarps; it += kUnroll) {
-        float v[kUnroll][8];
+    for (int it = 0; it < kTileRows / kRowsPerStep; it += kUnroll) {
+        Raw16<T> raw[kUnroll];
 #pragma unroll
         for (int u = 0; u < kUnroll; ++u) {
-            const int64_t row = row0 + (it + u) * kWarps + warp;
+            const int64_t row = row0 + (it + u) * kRowsPerStep + sub;
             if (kVec) {
-                if (col < orig_cols && row < orig_rows) {
-                    load8<T>(x + row * orig_cols + col, v[u]);
-                } else {
-#pragma unroll
-                    for (int i = 0; i < 8; ++i) v[u][i] = 0.0f;
-                }
-            } else {
-                load8_guarded<T>(x, row, col, orig_rows, orig_cols, v[u]);
+                if (col < orig_cols && row < orig_rows) load_raw16<T>(x + row * orig_cols + col, raw[u]);
+                else zero_raw16<T>(raw[u]);
             }
         }
 #pragma unroll
         for (int u = 0; u < kUnroll; ++u) {
-            const int r_in_tile = (it + u) * kWarps + warp;
+            const int r_in_tile = (it + u) * kRowsPerStep + sub;
             const int64_t row = row0 + r_in_tile;
+            float v[16];
+            if (kVec) unpack16(raw[u], v);
+            else load16_guarded<T>(x, row, col, orig_rows, orig_cols, v);
             uint32_t s8;
-            const uint32_t packed = nvfp4_encode_half_block(v[u], g, hi_first, s8);
+            const uint2 packed = nvfp4_encode_block<kExactDiv>(v, ctx, hi_first, s8);
             if (col_ok && row < rows) {
-                *reinterpret_cast<uint32_t*>(q + row * (cols >> 1) + (col >> 1)) = packed;
-                if ((lane & 1) == 0)
-                    s_sf[(blk_in_tile >> 2) * 512 + sf_tile_offset(r_in_tile, blk_in_tile & 3)] = (uint8_t)s8;
+                *reinterpret_cast<uint2*>(q + row * (cols >> 1) + (col >> 1)) = packed;
+                s_sf[(blk >> 2) * 512 + sf_tile_offset(r_in_tile, blk & 3)] = (uint8_t)s8;
             }
         }
     }
@@ -93,7 +94,7 @@ quantize_nvfp4_kernel(const T* __restrict__ x, const float* __restrict__ global_
     // 2 KB of staged scales -> 128 x 16-byte stores; tiles past the padded width are skipped
     if (tid < kSfTiles * 32) {
         const int t = tid >> 5;
-        const int64_t tile_col = (col0 >> 6) + t;
+        const int64_t tile_col = ((int64_t)blockIdx.x * kTileCols >> 6) + t;
         if (tile_col < (sf_cpad >> 2)) {
             uint8_t* dst = sf + ((int64_t)blockIdx.y * (sf_cpad >> 2) + tile_col) * 512 + (tid & 31) * 16;
             *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(s_sf + t * 512 + (tid & 31) * 16);
@@ -102,14 +103,16 @@ quantize_nvfp4_kernel(const T* __restrict__ x, const float* __restrict__ global_
 }
 
 // Dequantize: lut[code] * (g * s8), each product rounded to the output dtype as
-// the eager reference does (backends/eager/quantization.py:213-219).
-template <typename T>
+// the eager reference does (backends/eager/quantization.py:213-219).  Same tiling
+// as the quantizer: a thread expands one block (8 bytes in, one 256-bit store out).
+template <typename T, bool kVec>
 __global__ void __launch_bounds__(kThreads)
 dequantize_nvfp4_kernel(const uint8_t* __restrict__ q, const float* __restrict__ global_scale,
                         const uint8_t* __restrict__ sf, T* __restrict__ out, int64_t rows, int64_t cols,
                         int64_t sf_cpad, bool hi_first) {
     __shared__ __align__(16) uint8_t s_sf[kSfTiles * 512];
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int tid = threadIdx.x;
+    const int blk = tid & 15, sub = tid >> 4;
     const int64_t row0 = (int64_t)blockIdx.y * kTileRows;
     const int64_t col0 = (int64_t)blockIdx.x * kTileCols;
 
@@ -125,43 +128,52 @@ dequantize_nvfp4_kernel(const uint8_t* __restrict__ q, const float* __restrict__
     __syncthreads();
 
     const float g = Elem<T>::round(__ldg(global_scale));
-    const int64_t col = col0 + lane * 8;
+    const int64_t col = col0 + blk * 16;
     if (col >= cols) return;
-    const int blk_in_tile = lane >> 1;
 
 #pragma unroll 4
-    for (int it = 0; it < kTileRows / kWarps; ++it) {
-        const int r_in_tile = it * kWarps + warp;
+    for (int it = 0; it < kTileRows / kRowsPerStep; ++it) {
+        const int r_in_tile = it * kRowsPerStep + sub;
         const int64_t row = row0 + r_in_tile;
         if (row >= rows) break;
-        const uint32_t codes = *reinterpret_cast<const uint32_t*>(q + row * (cols >> 1) + (col >> 1));
-        const uint32_t s8 = s_sf[(blk_in_tile >> 2) * 512 + sf_tile_offset(r_in_tile, blk_in_tile & 3)];
+        const uint2 codes = *reinterpret_cast<const uint2*>(q + row * (cols >> 1) + (col >> 1));
+        const uint32_t s8 = s_sf[(blk >> 2) * 512 + sf_tile_offset(r_in_tile, blk & 3)];
         const float tot = Elem<T>::round(__fmul_rn(g, e4m3_to_f32(s8)));
-        float v[8];
+        float lo[8], hi[8], v[16];
+        e2m1x8_to_f32(codes.x, hi_first, lo);
+        e2m1x8_to_f32(codes.y, hi_first, hi);
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const uint32_t byte = (codes >> (8 * i)) & 0xffu;
-            const uint32_t first = hi_first ? (byte >> 4) : (byte & 0xfu);
-            const uint32_t second = hi_first ? (byte & 0xfu) : (byte >> 4);
-            v[2 * i] = __fmul_rn(e2m1_value(first), tot);
-            v[2 * i + 1] = __fmul_rn(e2m1_value(second), tot);
+        for (int i = 0; i < 8; ++i) {
+            v[i] = __fmul_rn(lo[i], tot);
+            v[8 + i] = __fmul_rn(hi[i], tot);
         }
-        store8<T>(out + row * cols + col, v);
+        T* dst = out + row * cols + col;
+        if (kVec) {
+            store16<T>(dst, v);
+        } else {
+            float a[8], b[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) { a[i] = v[i]; b[i] = v[8 + i]; }
+            store8<T>(dst, a);
+            store8<T>(dst + 8, b);
+        }
     }
 }
+
+inline bool aligned32(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 31u) == 0; }
 
 template <typename T>
 int launch_quantize(const void* x, const float* g, uint8_t* q, uint8_t* sf, int64_t rows, int64_t cols,
                     int64_t orig_rows, int64_t orig_cols, bool hi_first, cudaStream_t stream) {
     const int64_t sf_cpad = round_up(cols / 16, 4);
     dim3 grid((unsigned)ceil_div(sf_cpad * 16, kTileCols), (unsigned)ceil_div(rows, kTileRows));
-    const bool vec = aligned16(x) && (orig_cols % 8 == 0);
-    if (vec)
-        quantize_nvfp4_kernel<T, true><<<grid, kThreads, 0, stream>>>((const T*)x, g, q, sf, rows, cols, orig_rows,
-                                                                      orig_cols, sf_cpad, hi_first);
-    else
-        quantize_nvfp4_kernel<T, false><<<grid, kThreads, 0, stream>>>((const T*)x, g, q, sf, rows, cols, orig_rows,
-                                                                       orig_cols, sf_cpad, hi_first);
+    const bool vec = aligned32(x) && (orig_cols % 16 == 0);
+    auto xt = static_cast<const T*>(x);
+#define CK_LAUNCH_Q(VEC, EXACT) \
+    quantize_nvfp4_kernel<T, VEC, EXACT><<<grid, kThreads, 0, stream>>>(xt, g, q, sf, rows, cols, orig_rows, orig_cols, sf_cpad, hi_first)
+    if (g_nvfp4_exact_div) { if (vec) CK_LAUNCH_Q(true, true); else CK_LAUNCH_Q(false, true); }
+    else { if (vec) CK_LAUNCH_Q(true, false); else CK_LAUNCH_Q(false, false); }
+#undef CK_LAUNCH_Q
     return launch_status("quantize_nvfp4");
 }
 
@@ -170,7 +182,10 @@ int launch_dequantize(const uint8_t* q, const float* g, const uint8_t* sf, void*
                       bool hi_first, cudaStream_t stream) {
     const int64_t sf_cpad = round_up(cols / 16, 4);
     dim3 grid((unsigned)ceil_div(cols, kTileCols), (unsigned)ceil_div(rows, kTileRows));
-    dequantize_nvfp4_kernel<T><<<grid, kThreads, 0, stream>>>(q, g, sf, (T*)out, rows, cols, sf_cpad, hi_first);
+    if (aligned32(out))
+        dequantize_nvfp4_kernel<T, true><<<grid, kThreads, 0, stream>>>(q, g, sf, (T*)out, rows, cols, sf_cpad, hi_first);
+    else
+        dequantize_nvfp4_kernel<T, false><<<grid, kThreads, 0, stream>>>(q, g, sf, (T*)out, rows, cols, sf_cpad, hi_first);
     return launch_status("dequantize_nvfp4");
 }
 
@@ -189,8 +204,8 @@ extern "C" int launch_quantize_nvfp4_kernel(const void* input, const void* globa
         CK_FAIL(CK_ERR_SHAPE, "quantize_nvfp4: bad shape rows=%lld cols=%lld orig=%lldx%lld (cols must be a multiple of 16)",
                 (long long)num_rows, (long long)num_cols, (long long)orig_rows, (long long)orig_cols);
     if (ceil_div(num_rows, 128) > 65535) CK_FAIL(CK_ERR_SHAPE, "quantize_nvfp4: more than 65535*128 rows");
-    if (!aligned16(block_scales) || (reinterpret_cast<uintptr_t>(output) & 3u))
-        CK_FAIL(CK_ERR_ALIGN, "quantize_nvfp4: outputs must be 16-byte (scales) / 4-byte (codes) aligned");
+    if (!aligned16(block_scales) || (reinterpret_cast<uintptr_t>(output) & 7u))
+        CK_FAIL(CK_ERR_ALIGN, "quantize_nvfp4: outputs must be 16-byte (scales) / 8-byte (codes) aligned");
     auto* g = static_cast<const float*>(global_scale);
     auto* q = static_cast<uint8_t*>(output);
     auto* sf = static_cast<uint8_t*>(block_scales);
@@ -211,8 +226,8 @@ extern "C" int launch_dequantize_nvfp4_kernel(const void* input, const void* glo
         CK_FAIL(CK_ERR_SHAPE, "dequantize_nvfp4: bad shape %lldx%lld (cols must be a multiple of 16)",
                 (long long)num_rows, (long long)num_cols);
     if (ceil_div(num_rows, 128) > 65535) CK_FAIL(CK_ERR_SHAPE, "dequantize_nvfp4: more than 65535*128 rows");
-    if (!aligned16(block_scales) || !aligned16(output) || (reinterpret_cast<uintptr_t>(input) & 3u))
-        CK_FAIL(CK_ERR_ALIGN, "dequantize_nvfp4: scales/output must be 16-byte aligned, codes 4-byte aligned");
+    if (!aligned16(block_scales) || !aligned16(output) || (reinterpret_cast<uintptr_t>(input) & 7u))
+        CK_FAIL(CK_ERR_ALIGN, "dequantize_nvfp4: scales/output must be 16-byte aligned, codes 8-byte aligned");
     auto* q = static_cast<const uint8_t*>(input);
     auto* g = static_cast<const float*>(global_scale);
     auto* sf = static_cast<const uint8_t*>(block_scales);

@@ -45,6 +45,10 @@ typedef struct CUstream_st* ck_stream_t; /* cudaStream_t */
 const char* ck_last_error(void);
 int ck_abi_version(void);
 int ck_check_device(void); /* 0 when the current device is sm_100 */
+/* Library options (process-wide).  "nvfp4_exact_div" = 1: the NVFP4 quantizer uses plain IEEE
+ * divisions instead of the shared-reciprocal sequence; the bytes are the same either way (the
+ * tests check that on the device), only the speed differs. */
+int ck_set_option(const char* name, int value);
 
 /* ---- per-tensor FP8 ----
  * Replaces launch_quantize_fp8_kernel / launch_dequantize_fp8_kernel

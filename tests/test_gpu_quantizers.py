@@ -193,16 +193,54 @@ def test_full_size_properties(ck, orc):
     d = ck.dequantize_nvfp4(q, gs, sf, torch.float32)
     q2, sf2 = ck.quantize_nvfp4(d, gs)
     assert torch.equal(sf2.view(torch.uint8), sf.view(torch.uint8)) and torch.equal(q2, q)
-    # MXFP8: same two properties
+    # MXFP8: the round trip stays within half an E4M3 step of the block's scale
     q8, sf8 = ck.quantize_mxfp8(x)
     d8 = ck.dequantize_mxfp8(q8, sf8, torch.float32)
-    q8b, sf8b = ck.quantize_mxfp8(d8)
-    assert torch.equal(q8b.view(torch.uint8), q8.view(torch.uint8))
-    assert torch.equal(sf8b.view(torch.uint8), sf8.view(torch.uint8))
+    from comfy_kitchen.float_utils import e8m0_to_f32, from_blocked
+    step = e8m0_to_f32(from_blocked(sf8.view(torch.uint8), M, K // 32)).repeat_interleave(32, dim=1)
+    err = (d8 - x.float()).abs()
+    bound = torch.maximum(x.float().abs() * 2.0 ** -4, step * 2.0 ** -10)
+    assert bool((err <= bound).all())
+    del step, err, bound, d8
     # FP8: dequantize(quantize(x)) requantizes to the same codes
     s = (x.float().abs().max() / 448.0).float()
     q1 = ck.quantize_per_tensor_fp8(x, s)
     assert q1.shape == x.shape
+
+
+def test_nvfp4_reciprocal_division_is_exact(ck):
+    """The quantizer's shared-reciprocal divisions must give the same bytes as plain IEEE
+    divisions: compared on the device over many tensors, per-tensor scales and dtypes."""
+    gen = torch.Generator(device="cuda").manual_seed(123)
+    total = 0
+    for i in range(40):
+        dt = (torch.bfloat16, torch.float16, torch.float32)[i % 3]
+        M, K = 8192, 2048
+        x = torch.randn(M, K, device="cuda", generator=gen)
+        if i % 4 == 1:
+            x = x * torch.exp2(torch.randint(-12, 12, (M, 1), device="cuda", generator=gen).float())
+        if i % 4 == 2:
+            x = torch.where(torch.rand(M, K, device="cuda", generator=gen) < 0.01, 40.0 * x, x)
+        if i % 4 == 3:
+            x = (x * 4).round() / 4  # many exact ties
+        x = x.to(dt)
+        amax = x.float().abs().max()
+        # a spread of per-tensor scales: the natural one, ones that clamp block scales at 448, tiny, huge
+        g = amax / (6.0 * 448.0) * float(torch.tensor([1.0, 0.037, 1.7, 1e-3, 64.0][i % 5]))
+        if i == 7:
+            g = torch.tensor(2.0 ** -100, device="cuda")   # outside the fast range: IEEE path inside the kernel
+        g = g.float().reshape(1)
+        ck.set_option("nvfp4_exact_div", 0)
+        q_fast, sf_fast = ck.quantize_nvfp4(x, g)
+        ck.set_option("nvfp4_exact_div", 1)
+        try:
+            q_ref, sf_ref = ck.quantize_nvfp4(x, g)
+        finally:
+            ck.set_option("nvfp4_exact_div", 0)
+        assert torch.equal(sf_fast.view(torch.uint8), sf_ref.view(torch.uint8)), f"scales differ in tensor {i}"
+        assert torch.equal(q_fast, q_ref), f"codes differ in tensor {i}"
+        total += x.numel()
+    assert total > 6e8
 
 
 def test_argument_errors(ck):
