@@ -1,0 +1,421 @@
+"""Benchmark of the quantized-linear hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Workload (the NVFP4 linear sweep of the Flux-like MMDiT shapes): for token counts
+M = 4608 x {1, 2, 4} and layers (N, K) in {(9216,3072) QKV, (3072,3072) proj,
+(12288,3072) MLP-up, (3072,12288) MLP-down}, one "linear" = activation front end
+(fused LayerNorm+AdaLN -> NVFP4 quantize for the K=3072 layers, whose input is the
+hidden state; plain NVFP4 quantize for MLP-down, whose input is the MLP activation)
+followed by the NVFP4 block-scaled GEMM with fp32 bias and bf16 output.  One step =
+all 12 linears.  Synthetic data: activations N(0,1), weights N(0,0.02), modulation
+N(0,0.1), fixed seeds; weights are quantized once outside the timed region, as in
+inference.
+
+Printed JSON (one line, rank 0):
+  value     TFLOP/s of the whole job (2*M*N*K per linear), inputs resident in HBM
+  e2e       the same metric with the activations starting in pinned host memory and the
+            outputs read back to the host inside the timed region
+  roofline  the NVFP4 GEMM kernel against the tensor peak (see DESIGN.md for the denominator)
+  cpu_baseline  the CPU oracle (a port of the reference's eager arithmetic) on a bounded sample
+  quantizers    GB/s of the memory-bound kernels at the largest sweep shape
+With --impl reference the CPU oracle is what is timed (the reference's own path for this
+workload runs on the host cores; it cannot execute block-scaled GEMMs on a CPU, so the
+GEMM there is dequantize -> fp32 matmul, as the reference's tests do).
+
+N > 1 (torchrun): every rank runs the same sweep on its own tokens (the linears are
+independent per token: no collective in the data path); value = N x per-rank work / max time.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+for _p in (os.path.join(ROOT, "comfy-kitchen_b200"), ROOT):
+    if _p not in sys.path:
+        sys.path.insert(0, _p)
+
+import torch  # noqa: E402
+
+LAYERS = [("qkv", 9216, 3072), ("proj", 3072, 3072), ("mlp_up", 12288, 3072), ("mlp_down", 3072, 12288)]
+BATCHES = [1, 2, 4]
+TOKENS = 4608
+HIDDEN = 3072
+
+
+def step_flops() -> float:
+    return float(sum(2.0 * TOKENS * b * n * k for b in BATCHES for _, n, k in LAYERS))
+
+
+def measured_peaks() -> dict:
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            d = json.load(f)
+        d["_source"] = "measured"
+        return d
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "_source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.proc = None
+        self.lines: list[str] = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._pump, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        clocks, mx, reasons = [], None, set()
+        for line in self.lines:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 6:
+                continue
+            try:
+                clocks.append(float(parts[0]))
+                mx = float(parts[1])
+            except ValueError:
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), parts[2:6]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        clocks.sort()
+        # the median of the upper half: samples taken under load (idle samples sit at the floor)
+        load = clocks[len(clocks) // 2:] if clocks else []
+        return {"sm_mhz": load[len(load) // 2] if load else None, "sm_max_mhz": mx, "reasons": sorted(reasons),
+                "samples": len(clocks)}
+
+
+# ----------------------------------------------------------------------------- our arm
+
+
+class Workload:
+    """Device-resident tensors of the sweep plus the pinned host copies for the e2e leg."""
+
+    def __init__(self, device, seed: int):
+        from comfy_kitchen.backends import cuda as ck
+
+        self.ck = ck
+        self.device = device
+        g = torch.Generator(device=device).manual_seed(seed)
+        self.weights = {}
+        for name, n, k in LAYERS:
+            w = (0.02 * torch.randn(n, k, device=device, generator=g)).bfloat16()
+            gw = (w.float().abs().max() / (6 * 448)).float().reshape(1)
+            qw, sw = ck.quantize_nvfp4(w, gw)
+            bias = (0.02 * torch.randn(n, device=device, generator=g)).float()
+            self.weights[name] = (qw, sw, gw, bias)
+            del w
+        self.acts = {}
+        for b in BATCHES:
+            x = torch.randn(b, TOKENS, HIDDEN, device=device, generator=g).bfloat16()
+            shift = (0.1 * torch.randn(b, 1, HIDDEN, device=device, generator=g)).bfloat16()
+            scale = (0.1 * torch.randn(b, 1, HIDDEN, device=device, generator=g)).bfloat16()
+            h = torch.randn(b * TOKENS, 4 * HIDDEN, device=device, generator=g).bfloat16()
+            # static per-tensor activation scales (calibrated once, like input_scale of a checkpoint)
+            y = ck.adaln(x, scale, shift, 1e-6)
+            gx = (y.float().abs().max() / (6 * 448)).float().reshape(1)
+            gh = (h.float().abs().max() / (6 * 448)).float().reshape(1)
+            del y
+            self.acts[b] = (x, shift, scale, h, gx, gh)
+        self.alphas = {(b, name): self.acts[b][4 if k == HIDDEN else 5] * self.weights[name][2]
+                       for b in BATCHES for name, _, k in LAYERS}
+        self.gemm_events: list[tuple[torch.cuda.Event, torch.cuda.Event, float]] = []
+
+    def linear(self, b: int, name: str, x, shift, scale, h, gx, gh, record: bool):
+        ck = self.ck
+        qw, sw, gw, bias = self.weights[name]
+        n, k = qw.shape[0], qw.shape[1] * 2
+        if k == HIDDEN:
+            qa, sa = ck.adaln_quantize_nvfp4(x, scale, shift, gx, 1e-6)
+            ga = gx
+        else:
+            qa, sa = ck.quantize_nvfp4(h, gh)
+            ga = gh
+        if record:
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+        out = ck.scaled_mm_nvfp4(qa, qw, ga, gw, sa, sw, bias=bias, out_dtype=torch.bfloat16, alpha=self.alphas[(b, name)])
+        if record:
+            e1.record()
+            self.gemm_events.append((e0, e1, 2.0 * TOKENS * b * n * k))
+        return out
+
+    def step(self, record: bool = False):
+        outs = None
+        for b in BATCHES:
+            x, shift, scale, h, gx, gh = self.acts[b]
+            for name, _, _ in LAYERS:
+                outs = self.linear(b, name, x, shift, scale, h, gx, gh, record)
+        return outs
+
+    # ---- e2e: activations start in pinned host memory, outputs end there
+    def make_host(self):
+        self.host_in, self.host_out = {}, {}
+        for b in BATCHES:
+            x, shift, scale, h, gx, gh = self.acts[b]
+            self.host_in[b] = (x.cpu().pin_memory(), h.cpu().pin_memory())
+            self.host_out[b] = {name: torch.empty(b * TOKENS, n, dtype=torch.bfloat16).pin_memory() for name, n, _ in LAYERS}
+        h2d = sum(3 * xi.numel() * 2 + hi.numel() * 2 for xi, hi in self.host_in.values())
+        d2h = sum(t.numel() * 2 for d in self.host_out.values() for t in d.values())
+        return h2d, d2h
+
+    def step_e2e(self):
+        for b in BATCHES:
+            _, shift, scale, _, gx, gh = self.acts[b]
+            hx, hh = self.host_in[b]
+            for name, _, k in LAYERS:
+                # each linear is an independent call: its input crosses the bus, its output goes back
+                if k == HIDDEN:
+                    x = hx.to(self.device, non_blocking=True)
+                    out = self.linear(b, name, x, shift, scale, None, gx, gh, False)
+                else:
+                    h = hh.to(self.device, non_blocking=True)
+                    out = self.linear(b, name, None, shift, scale, h, gx, gh, False)
+                self.host_out[b][name].copy_(out, non_blocking=True)
+
+
+def quantizer_sweep(device) -> dict:
+    """GB/s of the memory-bound kernels on bf16 [65536, 12288] (algorithmic bytes / event time)."""
+    from comfy_kitchen.backends import cuda as ck
+
+    M, K = 65536, 12288
+    x = torch.randn(M, K, device=device).bfloat16()
+    n = M * K
+    g = (x.float().abs().max() / (6 * 448)).float().reshape(1)
+    s8 = (x.float().abs().max() / 448).float().reshape(1)
+
+    def t(fn, iters=5):
+        fn()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(iters):
+            fn()
+        b.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b) / iters * 1e-3
+
+    res = {}
+    res["quantize_nvfp4"] = 2.5625 * n / t(lambda: ck.quantize_nvfp4(x, g)) / 1e9
+    q, sf = ck.quantize_nvfp4(x, g)
+    res["dequantize_nvfp4"] = 2.5625 * n / t(lambda: ck.dequantize_nvfp4(q, g, sf)) / 1e9
+    del q, sf
+    res["quantize_mxfp8"] = 3.03125 * n / t(lambda: ck.quantize_mxfp8(x)) / 1e9
+    q8, sf8 = ck.quantize_mxfp8(x)
+    res["dequantize_mxfp8"] = 3.03125 * n / t(lambda: ck.dequantize_mxfp8(q8, sf8)) / 1e9
+    del q8, sf8
+    res["quantize_fp8"] = 3.0 * n / t(lambda: ck.quantize_per_tensor_fp8(x, s8)) / 1e9
+    qf = ck.quantize_per_tensor_fp8(x, s8)
+    res["dequantize_fp8"] = 3.0 * n / t(lambda: ck.dequantize_per_tensor_fp8(qf, s8)) / 1e9
+    return {k: round(v, 1) for k, v in res.items()}
+
+
+# ----------------------------------------------------------------------------- CPU arm
+
+
+def cpu_sample_step(rows: int, threads: int) -> tuple[float, float]:
+    """One pass of the same 4 layers on `rows` tokens with the CPU oracle; returns (seconds, flops)."""
+    from oracle import ck_oracle as orc
+
+    orc.set_threads(threads)
+    torch.set_num_threads(threads)
+    g = torch.Generator().manual_seed(0)
+    x = torch.randn(1, rows, HIDDEN, generator=g).bfloat16()
+    shift = (0.1 * torch.randn(1, 1, HIDDEN, generator=g)).bfloat16()
+    scale = (0.1 * torch.randn(1, 1, HIDDEN, generator=g)).bfloat16()
+    h = torch.randn(rows, 4 * HIDDEN, generator=g).bfloat16()
+    cache = getattr(cpu_sample_step, "_w", None)
+    if cache is None:
+        cache = {}
+        for name, n, k in LAYERS:
+            w = (0.02 * torch.randn(n, k, generator=g)).bfloat16()
+            gw = (w.float().abs().max() / (6 * 448)).float()
+            qw, sw = orc.quantize_nvfp4(w, gw)
+            cache[name] = (qw, sw, gw, (0.02 * torch.randn(n, generator=g)).float())
+        cpu_sample_step._w = cache
+    gx, gh = torch.tensor(0.002), torch.tensor(0.002)
+    t0 = time.perf_counter()
+    flops = 0.0
+    for name, n, k in LAYERS:
+        qw, sw, gw, bias = cache[name]
+        if k == HIDDEN:
+            y = orc.adaln(x, scale, shift, 1e-6).reshape(rows, HIDDEN)
+            qa, sa = orc.quantize_nvfp4(y, gx)
+            ga = gx
+        else:
+            qa, sa = orc.quantize_nvfp4(h, gh)
+            ga = gh
+        orc.scaled_mm_nvfp4(qa, qw, ga, gw, sa, sw, bias=bias, out_dtype=torch.bfloat16)
+        flops += 2.0 * rows * n * k
+    return time.perf_counter() - t0, flops
+
+
+def run_reference(args) -> None:
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    threads = os.cpu_count() or 1
+    rows = 512
+    for _ in range(max(1, min(args.warmup, 1))):
+        cpu_sample_step(rows, threads)
+    t_total, f_total = 0.0, 0.0
+    for _ in range(args.steps):
+        t, f = cpu_sample_step(rows, threads)
+        t_total += t
+        f_total += f
+    value = f_total / t_total / 1e12
+    sample = f"{rows} tokens x 4 layers per step (of 32256 tokens x 4 layers), CPU oracle, dequantize->fp32 matmul"
+    line = {
+        "impl": "reference", "metric": "nvfp4_linear_throughput", "value": round(value, 4), "unit": "TFLOP/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(t_total / args.steps * 1e3, 2),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "nvfp4 (e2m1 x e4m3 block scales), fp32 accumulate",
+        "data": "synthetic",
+        "config": {"workload": "NVFP4 linear sweep, Flux-like MMDiT shapes (configs[2])", "tokens": [TOKENS * b for b in BATCHES],
+                   "layers": [[n, k] for _, n, k in LAYERS], "l2": "inputs larger than L2"},
+        "cpu_baseline": {"value": round(value, 4), "unit": "TFLOP/s", "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": round(value, 4), "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line))
+
+
+# ----------------------------------------------------------------------------- main
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-extras", action="store_true", help="skip the quantizer sweep, e2e and CPU legs")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+
+    if args.impl == "reference":
+        run_reference(args)
+        return
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (the product path has no CPU fallback)")
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist  # type: ignore[no-redef]
+
+        dist.init_process_group("nccl", device_id=device)
+
+    wl = Workload(device, seed=1000 + rank)
+    for _ in range(args.warmup):
+        wl.step()
+    torch.cuda.synchronize()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    if dist is not None:
+        dist.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        wl.step(record=True)
+    e1.record()
+    torch.cuda.synchronize()
+    if dist is not None:
+        dist.barrier()
+    elapsed_ms = e0.elapsed_time(e1)
+    clocks = sampler.stop() if rank == 0 else None
+    if dist is not None:
+        t = torch.tensor([elapsed_ms], device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        elapsed_ms = float(t.item())
+    assert wl.ck.gemm_device_status() == 0, "GEMM kernel reported a device-side timeout"
+    flops = step_flops()
+    value = world * flops * args.steps / (elapsed_ms * 1e-3) / 1e12
+
+    gemm_ms = sum(a.elapsed_time(b) for a, b, _ in wl.gemm_events)
+    gemm_flops = sum(f for _, _, f in wl.gemm_events)
+    achieved = gemm_flops / (gemm_ms * 1e-3) / 1e12
+    peaks = measured_peaks()
+    # dense FP4 peak = 4 x dense bf16 peak on this part (9 vs 2.25 PFLOP/s nominal); the bf16 figure is
+    # the sustained cuBLAS measurement, because the GEMMs run back to back inside a long step
+    peak = 4.0 * float(peaks.get("bf16_tflops_sustained", peaks["bf16_tflops"]))
+
+    line = {
+        "metric": "nvfp4_linear_throughput", "value": round(value, 1), "unit": "TFLOP/s", "n_gpus": world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(elapsed_ms / args.steps, 3),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "nvfp4 (e2m1 x e4m3 block scales), fp32 accumulate", "data": "synthetic",
+        "config": {"workload": "NVFP4 linear sweep, Flux-like MMDiT shapes (configs[2]): fused LN+AdaLN->NVFP4 quantize, "
+                               "NVFP4 GEMM + fp32 bias -> bf16", "tokens": [TOKENS * b for b in BATCHES],
+                   "layers": [[n, k] for _, n, k in LAYERS], "l2": "inputs larger than L2 (1.9 GB of outputs per step)",
+                   "parallelism": f"tokens x{world}" if world > 1 else "single GPU"},
+        "gpu_launches": 24 * args.steps,
+        "clocks": clocks,
+        "roofline": {"bound": "tensor", "achieved": round(achieved, 1), "peak": round(peak, 1), "unit": "TFLOP/s",
+                     "frac": round(achieved / peak, 4), "traffic": None,
+                     "kernel": "gemm_blockscaled_kernel<fp4>", "peak_source": f"4 x bf16_tflops_sustained ({peaks['_source']})"},
+    }
+
+    if rank == 0 and not args.no_extras:
+        # ---- e2e through the public API with host buffers
+        h2d, d2h = wl.make_host()
+        wl.step_e2e()
+        torch.cuda.synchronize()
+        n_e2e = max(1, min(args.steps, 3))
+        t0 = time.perf_counter()
+        for _ in range(n_e2e):
+            wl.step_e2e()
+        torch.cuda.synchronize()
+        t_e2e = (time.perf_counter() - t0) / n_e2e
+        line["e2e"] = {"value": round(flops / t_e2e / 1e12, 2), "unit": "TFLOP/s", "h2d_bytes_per_step": int(h2d),
+                       "d2h_bytes_per_step": int(d2h), "steps": n_e2e}
+        del wl.host_in, wl.host_out
+        # ---- memory-bound kernels, largest sweep shape
+        line["quantizers"] = {"shape": [65536, 12288], "unit": "GB/s", "hbm_peak": peaks["hbm_gbs"], **quantizer_sweep(device)}
+        # ---- CPU oracle on a bounded sample
+        threads = os.cpu_count() or 1
+        cpu_sample_step(512, threads)
+        t_cpu, f_cpu = cpu_sample_step(512, threads)
+        line["cpu_baseline"] = {"value": round(f_cpu / t_cpu / 1e12, 4), "unit": "TFLOP/s", "cores": threads, "kind": "port",
+                                "sample": "512 tokens x 4 layers (of 32256 tokens x 4 layers), CPU oracle, dequantize->fp32 matmul"}
+    elif rank == 0:
+        line["e2e"] = None
+    if rank == 0:
+        print(json.dumps(line))
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

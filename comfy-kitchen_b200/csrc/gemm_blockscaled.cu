@@ -64,7 +64,10 @@ constexpr uint32_t kTmemAcc0 = 0, kTmemAcc1 = 256, kTmemSfA = 448, kTmemSfB = 46
 
 constexpr uint32_t kSpinLimit = 1u << 22;   // polls of mbarrier.try_wait before giving up (a fraction of a second)
 
-__device__ int g_gemm_status = 0;           // 0 ok; otherwise (code << 16 | detail) of the first failure
+__device__ int g_gemm_status = 0;
+#if CK_GEMM_PROBE & 8
+__device__ long long g_probe_ts[4 * 256];   // MMA warp of CTA 0, per k-tile: before wait, after wait, after issue
+#endif           // 0 ok; otherwise (code << 16 | detail) of the first failure
 
 enum : int { kTimeoutFull = 1, kTimeoutEmpty = 2, kTimeoutTmemFull = 3, kTimeoutTmemEmpty = 4 };
 
@@ -85,6 +88,15 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
     uint32_t ok;
     asm volatile(
         "{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
+        : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+    return ok != 0;
+}
+// Non-blocking look at a barrier phase (try_wait may suspend the thread for a while when the phase is
+// still pending; this never does).
+__device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{ .reg .pred p; mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
         : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
     return ok != 0;
 }
@@ -306,7 +318,7 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
         const uint32_t smem16 = (smem_u32(stage_base) & 0x3ffffu) >> 4;
         const bool tail_full = (p.K % kElemsPerTile) == 0;
         uint32_t it = 0, local_tile = 0;
-        bool ok = true;
+        bool ok = true, ready = false;
         for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local_tile) {
             const int tn = tile / p.tiles_m;
             const uint32_t buf = local_tile & 1, use = local_tile >> 1;
@@ -318,53 +330,55 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
             const uint32_t sfb_shift = ((tn * BN) & 127) ? 2u : 0u;
             for (int kt = 0; kt < k_tiles && ok; ++kt, ++it) {
                 const int s = it % kStages;
-                ok = mbar_wait(&full[s], (it / kStages) & 1, s_abort, kTimeoutFull);
+#if CK_GEMM_PROBE & 8
+                if (blockIdx.x == 0 && lane == 0 && it < 256) g_probe_ts[4 * it + 0] = clock64();
+#endif
+                // `ready` is an early look at this barrier taken while the previous k-tile was being issued
+                if (!__all_sync(0xffffffffu, ready)) ok = mbar_wait(&full[s], (it / kStages) & 1, s_abort, kTimeoutFull);
                 if (!ok) break;
                 tc_fence_after();
-                {
-                    // every descriptor of this stage is "stage start >> 4" plus a constant
-                    const uint32_t st16 = smem16 + (uint32_t)s * (kStageBytes >> 4);
-                    const uint32_t a_lo = st16 | kDescLoLbo1, b_lo = (st16 + (kSmemA >> 4)) | kDescLoLbo1;
-                    const uint32_t sfa16 = st16 + ((kSmemA + kSmemB) >> 4), sfb16 = sfa16 + (kSmemSfA >> 4);
-                    const uint32_t t_sfa = tmem_base + kTmemSfA, t_sfb = tmem_base + kTmemSfB;
-                    if (kt + 1 < k_tiles || tail_full) {
-                        // full k-tile: all scale tiles and four MMAs, fully unrolled
+#if CK_GEMM_PROBE & 8
+                if (blockIdx.x == 0 && lane == 0 && it < 256) g_probe_ts[4 * it + 1] = clock64();
+#endif
+                // every descriptor of this stage is "stage start >> 4" plus a constant
+                const uint32_t st16 = smem16 + (uint32_t)s * (kStageBytes >> 4);
+                const uint32_t a_lo = st16 | kDescLoLbo1, b_lo = (st16 + (kSmemA >> 4)) | kDescLoLbo1;
+                const uint32_t sfa16 = st16 + ((kSmemA + kSmemB) >> 4), sfb16 = sfa16 + (kSmemSfA >> 4);
+                const uint32_t t_sfa = tmem_base + kTmemSfA, t_sfb = tmem_base + kTmemSfB;
+                // The tensor pipe runs the copies and MMAs of one thread in issue order, so the scale copies of a
+                // k-tile simply precede its MMAs (issuing them as one batch measured faster than interleaving).
+                auto issue = [&](int n_sf, int n_kb) {
 #pragma unroll
-                        for (int t = 0; t < kSfTilesPerStage; ++t) {
+                    for (int t = 0; t < kSfTilesPerStage; ++t) {
+                        if (t < n_sf) {
                             tc_cp_sf(t_sfa + 4 * t, sfa16 + t * 32);
                             tc_cp_sf(t_sfb + 8 * t, sfb16 + t * 32);
                             tc_cp_sf(t_sfb + 8 * t + 4, sfb16 + (kSmemSfB >> 5) + t * 32);
                         }
+                    }
 #pragma unroll
-                        for (int kb = 0; kb < kKbPerTile; ++kb) {
+                    for (int kb = 0; kb < kKbPerTile; ++kb) {
+                        if (kb < n_kb) {
                             // 32 bytes along K per MMA inside the 128-byte swizzled row
                             uint32_t idesc = idesc_base, sfa = t_sfa, sfb = t_sfb + sfb_shift;
                             if (kFp4) { sfa += 4 * kb; sfb += 8 * kb; }
                             else { idesc |= ((uint32_t)kb << 29) | ((uint32_t)kb << 4); }
                             tc_mma<kFp4>(d_tmem, a_lo + 2 * kb, b_lo + 2 * kb, idesc, (kt > 0 || kb > 0) ? 1u : 0u, sfa, sfb);
                         }
-                    } else {
-                        // last, short k-tile
-                        int n_sf = p.sf_tiles_k - kt * kSfTilesPerStage;
-                        if (n_sf > kSfTilesPerStage) n_sf = kSfTilesPerStage;
-                        for (int t = 0; t < n_sf; ++t) {
-                            tc_cp_sf(t_sfa + 4 * t, sfa16 + t * 32);
-                            tc_cp_sf(t_sfb + 8 * t, sfb16 + t * 32);
-                            tc_cp_sf(t_sfb + 8 * t + 4, sfb16 + (kSmemSfB >> 5) + t * 32);
-                        }
-                        const int k_left = p.K - kt * kElemsPerTile;
-                        const int n_kb = (k_left + kMmaK - 1) / kMmaK;
-                        for (int kb = 0; kb < n_kb; ++kb) {
-                            uint32_t idesc = idesc_base, sfa = t_sfa, sfb = t_sfb + sfb_shift;
-                            if (kFp4) { sfa += 4 * kb; sfb += 8 * kb; }
-                            else { idesc |= ((uint32_t)kb << 29) | ((uint32_t)kb << 4); }
-                            tc_mma<kFp4>(d_tmem, a_lo + 2 * kb, b_lo + 2 * kb, idesc, (kt > 0 || kb > 0) ? 1u : 0u, sfa, sfb);
-                        }
                     }
-                    tc_commit(&empty[s]);                      // stage reusable once these MMAs have read it
-                    if (kt == k_tiles - 1) tc_commit(&tmem_full[buf]);  // accumulator complete
+                };
+                if (kt + 1 < k_tiles || tail_full) {
+                    issue(kSfTilesPerStage, kKbPerTile);
+                } else {  // last, short k-tile
+                    issue(p.sf_tiles_k - kt * kSfTilesPerStage, (p.K - kt * kElemsPerTile + kMmaK - 1) / kMmaK);
                 }
-                __syncwarp();
+                // the pipe is busy with these for a while: look at the next k-tile's barrier now
+                ready = mbar_test_wait(&full[(it + 1) % kStages], ((it + 1) / kStages) & 1);
+                tc_commit(&empty[s]);                      // stage reusable once these MMAs have read it
+                if (kt == k_tiles - 1) tc_commit(&tmem_full[buf]);  // accumulator complete
+#if CK_GEMM_PROBE & 8
+                if (blockIdx.x == 0 && lane == 0 && it < 256) g_probe_ts[4 * it + 2] = clock64();
+#endif
             }
         }
     } else {
@@ -557,6 +571,13 @@ extern "C" int launch_cublas_gemm_blockwise_fp4_kernel(const void* B_ptr, const 
     return ck::launch_gemm<true>(A_ptr, A_decode_scale_ptr, B_ptr, B_decode_scale_ptr, D_ptr, bias_ptr, out_dtype_code,
                                  M, N, K, alpha_device_ptr, out_dtype_code, stream);
 }
+
+#if CK_GEMM_PROBE & 8
+extern "C" int ck_probe_read(long long* out) {
+    cudaDeviceSynchronize();
+    return (int)cudaMemcpyFromSymbol(out, ck::g_probe_ts, sizeof(long long) * 4 * 256);
+}
+#endif
 
 // Reads and clears the device-side status word of the GEMM kernels (synchronises the device).
 // 0 = no bounded wait ran out since the last call.
