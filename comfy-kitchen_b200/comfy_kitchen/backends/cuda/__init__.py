@@ -101,6 +101,17 @@ def _scalar_on(s, device) -> torch.Tensor:
     return s.reshape(1) if s.dim() == 0 else s.contiguous()
 
 
+def _bias_for(bias: torch.Tensor, n: int) -> torch.Tensor:
+    """Bias vector for an output of n columns; a weight padded to the block multiple gets zero bias
+    on its padding columns (they are cropped by the layout handlers afterwards)."""
+    bias = bias.contiguous()
+    if bias.numel() == n:
+        return bias
+    if bias.dim() != 1 or bias.numel() > n:
+        raise RuntimeError(f"bias has {bias.numel()} elements, output has {n} columns")
+    return torch.nn.functional.pad(bias, (0, n - bias.numel()))
+
+
 # ------------------------------------------------------------------ NVFP4
 
 
@@ -186,8 +197,7 @@ def scaled_mm_nvfp4(
         out_dtype = torch.bfloat16
     bias_code = 0
     if bias is not None and bias.numel() > 0:
-        bias = _plain(bias).contiguous()
-        assert bias.numel() == n, "bias must have N elements"
+        bias = _bias_for(_plain(bias), n)
         assert bias.dtype in (torch.float16, torch.bfloat16, torch.float32), "bias must be fp16, bf16 or fp32"
         bias_code = DTYPE_TO_CODE[bias.dtype]
     else:
@@ -259,8 +269,7 @@ def scaled_mm_mxfp8(
         out_dtype = torch.bfloat16
     bias_code = 0
     if bias is not None and bias.numel() > 0:
-        bias = _plain(bias).contiguous()
-        assert bias.numel() == n, "bias must have N elements"
+        bias = _bias_for(_plain(bias), n)
         bias_code = _code(bias.dtype, "scaled_mm_mxfp8")
     else:
         bias = None
@@ -412,6 +421,57 @@ def rmsnorm_quantize_nvfp4(
         float(eps), _code(x.dtype, "rmsnorm_quantize_nvfp4"), bool(hi_first), 1, _stream(x.device),
     )
     return qx, sx.view(torch.float8_e4m3fn)
+
+
+def build_constraints() -> dict:
+    """What this backend accepts, per function (checked by the registry before dispatch)."""
+    from comfy_kitchen.constraints import DivisibleBy, ExactDims, FunctionConstraints, ParamConstraint
+
+    dev = frozenset({"cuda"})
+    floats = frozenset({torch.float32, torch.float16, torch.bfloat16})
+    fp8 = frozenset({torch.float8_e4m3fn, torch.float8_e5m2})
+    sm100 = (10, 0)
+
+    def fc(**params):
+        return FunctionConstraints(params=params, default_devices=dev, min_compute_capability=sm100)
+
+    two_d = (ExactDims(2),)
+    rope = fc(x=ParamConstraint(dtypes=floats, shape_rules=(ExactDims(4),)),
+              freqs_cis=ParamConstraint(dtypes=floats, shape_rules=(ExactDims(6),)))
+    rope2 = fc(xq=ParamConstraint(dtypes=floats, shape_rules=(ExactDims(4),)),
+               xk=ParamConstraint(dtypes=floats, shape_rules=(ExactDims(4),)),
+               freqs_cis=ParamConstraint(dtypes=floats, shape_rules=(ExactDims(6),)))
+    norm = dict(x=ParamConstraint(dtypes=floats), scale=ParamConstraint(dtypes=floats), shift=ParamConstraint(dtypes=floats))
+    return {
+        "quantize_per_tensor_fp8": fc(x=ParamConstraint(dtypes=floats), scale=ParamConstraint(dtypes=frozenset({torch.float32})),
+                                      output_type=ParamConstraint(dtypes=fp8)),
+        "dequantize_per_tensor_fp8": fc(x=ParamConstraint(dtypes=fp8), output_type=ParamConstraint(dtypes=floats)),
+        "quantize_nvfp4": fc(x=ParamConstraint(dtypes=floats, shape_rules=two_d),
+                             per_tensor_scale=ParamConstraint(dtypes=frozenset({torch.float32}))),
+        "dequantize_nvfp4": fc(qx=ParamConstraint(dtypes=frozenset({torch.uint8}), shape_rules=two_d + (DivisibleBy(1, 8),)),
+                               per_tensor_scale=ParamConstraint(dtypes=frozenset({torch.float32})),
+                               block_scales=ParamConstraint(dtypes=frozenset({torch.float8_e4m3fn})),
+                               output_type=ParamConstraint(dtypes=floats)),
+        "scaled_mm_nvfp4": fc(a=ParamConstraint(dtypes=frozenset({torch.uint8}), shape_rules=two_d + (DivisibleBy(1, 16),)),
+                              b=ParamConstraint(dtypes=frozenset({torch.uint8}), shape_rules=two_d + (DivisibleBy(1, 16), DivisibleBy(0, 8))),
+                              block_scale_a=ParamConstraint(dtypes=frozenset({torch.float8_e4m3fn})),
+                              block_scale_b=ParamConstraint(dtypes=frozenset({torch.float8_e4m3fn})),
+                              bias=ParamConstraint(dtypes=floats), out_dtype=ParamConstraint(dtypes=floats)),
+        "quantize_mxfp8": fc(x=ParamConstraint(dtypes=floats, shape_rules=two_d)),
+        "dequantize_mxfp8": fc(qx=ParamConstraint(dtypes=frozenset({torch.float8_e4m3fn}), shape_rules=two_d + (DivisibleBy(1, 32),)),
+                               block_scales=ParamConstraint(dtypes=frozenset({torch.float8_e8m0fnu})),
+                               output_type=ParamConstraint(dtypes=floats)),
+        "scaled_mm_mxfp8": fc(a=ParamConstraint(dtypes=frozenset({torch.float8_e4m3fn}), shape_rules=two_d + (DivisibleBy(1, 32),)),
+                              b=ParamConstraint(dtypes=frozenset({torch.float8_e4m3fn}), shape_rules=two_d + (DivisibleBy(1, 32), DivisibleBy(0, 8))),
+                              block_scale_a=ParamConstraint(dtypes=frozenset({torch.float8_e8m0fnu})),
+                              block_scale_b=ParamConstraint(dtypes=frozenset({torch.float8_e8m0fnu})),
+                              bias=ParamConstraint(dtypes=floats), out_dtype=ParamConstraint(dtypes=floats)),
+        "apply_rope": rope2, "apply_rope1": rope, "apply_rope_split_half": rope2, "apply_rope_split_half1": rope,
+        "adaln": fc(**norm),
+        "rmsnorm": fc(x=ParamConstraint(dtypes=floats), weight=ParamConstraint(dtypes=floats)),
+        "adaln_quantize_nvfp4": fc(**norm, per_tensor_scale=ParamConstraint(dtypes=frozenset({torch.float32}))),
+        "adaln_quantize_mxfp8": fc(**norm),
+    }
 
 
 def set_option(name: str, value: int) -> None:
