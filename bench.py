@@ -305,6 +305,66 @@ def run_reference(args) -> None:
     print(json.dumps(line))
 
 
+def run_case(args) -> None:
+    """One kernel on one shape, timed with CUDA events (small, self-contained: what the ncu captures run)."""
+    from comfy_kitchen.backends import cuda as ck
+
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    M, N, K = args.m, args.n, args.k
+    g = torch.Generator(device=dev).manual_seed(0)
+    x = torch.randn(M, K, device=dev, generator=g).bfloat16()
+    gx = (x.float().abs().max() / (6 * 448)).float().reshape(1)
+    work, unit = None, "GB/s"
+    if args.case in ("gemm_nvfp4", "gemm_mxfp8"):
+        w = (0.02 * torch.randn(N, K, device=dev, generator=g)).bfloat16()
+        bias = (0.02 * torch.randn(N, device=dev, generator=g)).float()
+        work, unit = 2.0 * M * N * K / 1e3, "TFLOP/s"
+        if args.case == "gemm_nvfp4":
+            gw = (w.float().abs().max() / (6 * 448)).float().reshape(1)
+            qx, sx = ck.quantize_nvfp4(x, gx)
+            qw, sw = ck.quantize_nvfp4(w, gw)
+            alpha = gx * gw
+            fn = lambda: ck.scaled_mm_nvfp4(qx, qw, gx, gw, sx, sw, bias=bias, out_dtype=torch.bfloat16, alpha=alpha)  # noqa: E731
+        else:
+            qx, sx = ck.quantize_mxfp8(x)
+            qw, sw = ck.quantize_mxfp8(w)
+            fn = lambda: ck.scaled_mm_mxfp8(qx, qw, sx, sw, bias=bias, out_dtype=torch.bfloat16)  # noqa: E731
+    elif args.case == "quantize_nvfp4":
+        work, fn = 2.5625 * M * K, (lambda: ck.quantize_nvfp4(x, gx))
+    elif args.case == "dequantize_nvfp4":
+        q, sf = ck.quantize_nvfp4(x, gx)
+        work, fn = 2.5625 * M * K, (lambda: ck.dequantize_nvfp4(q, gx, sf))
+    elif args.case == "quantize_mxfp8":
+        work, fn = 3.03125 * M * K, (lambda: ck.quantize_mxfp8(x))
+    elif args.case == "quantize_fp8":
+        s8 = gx * 6
+        work, fn = 3.0 * M * K, (lambda: ck.quantize_per_tensor_fp8(x, s8))
+    elif args.case == "adaln_quantize_nvfp4":
+        xs = x.view(1, M, K)
+        sc = (0.1 * torch.randn(1, 1, K, device=dev, generator=g)).bfloat16()
+        sh = (0.1 * torch.randn(1, 1, K, device=dev, generator=g)).bfloat16()
+        work, fn = 2.5625 * M * K, (lambda: ck.adaln_quantize_nvfp4(xs, sc, sh, gx, 1e-6))
+    elif args.case == "rope":
+        q = torch.randn(M // 4608 or 1, 24, 4608, 128, device=dev, generator=g).bfloat16()
+        k = torch.randn_like(q)
+        fr = torch.randn(q.shape[0], 1, 4608, 64, 2, 2, device=dev, generator=g)
+        work, fn = 8.0 * q.numel() + 4.0 * fr.numel(), (lambda: ck.apply_rope(q, k, fr))
+    else:
+        raise SystemExit(f"unknown --case {args.case}")
+    for _ in range(max(1, args.warmup)):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / args.steps
+    print(json.dumps({"case": args.case, "shape": [M, N, K], "ms": round(ms, 4), "value": round(work / ms / 1e6, 1), "unit": unit}))
+
+
 # ----------------------------------------------------------------------------- main
 
 
@@ -315,7 +375,16 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-extras", action="store_true", help="skip the quantizer sweep, e2e and CPU legs")
+    ap.add_argument("--case", default=None,
+                    help="run one kernel instead of the sweep (for profiling): gemm_nvfp4, gemm_mxfp8, quantize_nvfp4, "
+                         "dequantize_nvfp4, quantize_mxfp8, quantize_fp8, adaln_quantize_nvfp4, rope")
+    ap.add_argument("--m", type=int, default=9216)
+    ap.add_argument("--n", type=int, default=9216)
+    ap.add_argument("--k", type=int, default=3072)
     args = ap.parse_args()
+    if args.case:
+        run_case(args)
+        return
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 
     if args.impl == "reference":
