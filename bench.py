@@ -305,6 +305,20 @@ def run_reference(args) -> None:
     print(json.dumps(line))
 
 
+def max_over_ranks(elapsed_ms: float, dist, device) -> float:
+    """The slowest rank's device time: what a multi-GPU number is quoted on."""
+    if dist is None:
+        return float(elapsed_ms)
+    t = torch.tensor([elapsed_ms], device=device, dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def job_throughput(world: int, flops_per_rank_step: float, steps: int, elapsed_ms: float) -> float:
+    """Whole-job TFLOP/s when every rank does `flops_per_rank_step` per step (token-sharded, weak scaling)."""
+    return world * flops_per_rank_step * steps / (elapsed_ms * 1e-3) / 1e12
+
+
 def run_case(args) -> None:
     """One kernel on one shape, timed with CUDA events (small, self-contained: what the ncu captures run)."""
     from comfy_kitchen.backends import cuda as ck
@@ -422,15 +436,11 @@ def main() -> None:
     torch.cuda.synchronize()
     if dist is not None:
         dist.barrier()
-    elapsed_ms = e0.elapsed_time(e1)
     clocks = sampler.stop() if rank == 0 else None
-    if dist is not None:
-        t = torch.tensor([elapsed_ms], device=device)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        elapsed_ms = float(t.item())
+    elapsed_ms = max_over_ranks(e0.elapsed_time(e1), dist, device)
     assert wl.ck.gemm_device_status() == 0, "GEMM kernel reported a device-side timeout"
     flops = step_flops()
-    value = world * flops * args.steps / (elapsed_ms * 1e-3) / 1e12
+    value = job_throughput(world, flops, args.steps, elapsed_ms)
 
     gemm_ms = sum(a.elapsed_time(b) for a, b, _ in wl.gemm_events)
     gemm_flops = sum(f for _, _, f in wl.gemm_events)

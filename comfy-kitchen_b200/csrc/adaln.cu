@@ -7,14 +7,15 @@
 // comfy_kitchen/backends/eager/adaln.py:11-14.  Modulation rows are grouped as in
 // comfy_kitchen/backends/_modulation.py:12-57: row r reads row r / group.
 //
-// Fast path (D a multiple of 8, D <= 4096): one warp per row.  The row is read
-// once with 128-bit loads and held in registers; mean and variance are two passes
-// over registers (no E[x^2]-mean^2 cancellation); the result is either stored in
-// x's dtype, or — fused variants — rounded to x's dtype in registers and pushed
-// through the same block encoders as quantize_nvfp4 / quantize_mxfp8, so the
-// packed output is byte-identical to "adaln kernel, then quantize kernel" while
-// the intermediate activation never reaches HBM (2.5625 instead of 6.5625
-// bytes per element for NVFP4).
+// Fast path (D a multiple of 8, row <= 16 KB): persistent warps, one row per warp at a time.  Each warp
+// owns a small ring of row buffers in shared memory that it fills with cp.async.bulk (completion on
+// its own mbarriers), so the loads of the next rows are in flight while the current row is reduced
+// and written; the row is read from shared memory three times (sum, centred sum of squares, output)
+// and from HBM once.  The result is either stored in x's dtype, or — fused variants — rounded to
+// x's dtype in registers and pushed through the same block encoders as quantize_nvfp4 /
+// quantize_mxfp8, so the packed output is byte-identical to "adaln kernel, then quantize kernel"
+// while the intermediate activation never reaches HBM (2.5625 instead of 6.5625 bytes per element
+// for NVFP4).
 #include "ck_common.cuh"
 
 namespace ck {
@@ -43,114 +44,239 @@ __device__ __forceinline__ float warp_sum(float v) {
     return v;
 }
 
-template <typename T, int kNV, int kMode>
-__global__ void __launch_bounds__(256)
-norm_warp_kernel(const NormArgs a) {
-    const int lane = threadIdx.x & 31;
-    const int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+__device__ int g_norm_status = 0;  // non-zero when a bounded wait on a row copy ran out
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+// A lane's 16-element chunk from a row staged linearly in shared memory.  Lanes read 32 bytes each at
+// a 32-byte stride; had every lane read its low half first, lanes l and l+4 would hit the same banks.
+// Lanes with bit 2 set therefore read their high half first (`ordered` = false leaves the halves in
+// that order: good enough for sums; `ordered` = true puts them back).
+template <typename T, bool kOrdered>
+__device__ __forceinline__ void lds16(const T* p, int lane, float (&v)[16]) {
+    Raw16<T> r;
+    if (sizeof(T) == 2) {
+        const uint4* q = reinterpret_cast<const uint4*>(p);
+        const int rot = (lane >> 2) & 1;
+        const uint4 first = q[rot], second = q[rot ^ 1];
+        const bool swap = kOrdered && rot;
+        reinterpret_cast<uint4*>(r.w)[0] = swap ? second : first;
+        reinterpret_cast<uint4*>(r.w)[1] = swap ? first : second;
+    } else {
+        constexpr int kVecs = (int)(sizeof(r.w) / 16);
+#pragma unroll
+        for (int i = 0; i < kVecs; ++i) reinterpret_cast<uint4*>(r.w)[i] = reinterpret_cast<const uint4*>(p)[i];
+    }
+    unpack16(r, v);
+}
+
+// Position of element e (0..15) of chunk c in the shared-memory modulation cache.  Chunks are grouped
+// by 32 (one per lane); within a group the layout is [quad of elements][lane][4 floats], so the four
+// 128-bit loads of a lane are each contiguous across the warp.
+__device__ __forceinline__ int mod_pos(int c, int e) { return (c >> 5) * 512 + (e >> 2) * 128 + (c & 31) * 4 + (e & 3); }
+
+constexpr uint32_t kRowWaitLimit = 1u << 22;
+
+// Fast path.  A CTA owns a contiguous range of rows; its warps take them round-robin.  Each warp
+// streams its rows through a private ring of shared-memory buffers filled by cp.async.bulk.  The
+// modulation of the range ((1 + scale) or the RMSNorm weight, and shift) is cached in shared memory
+// as fp32 and reloaded only where the range crosses a modulation group.  Per row: one pass for the
+// statistics (shifted by the row's first element, so a large common offset does not cancel), one
+// pass for the output; a lane owns whole 16-element chunks.
+template <typename T, int kMode>
+__global__ void __launch_bounds__(512)
+norm_stream_kernel(const NormArgs a, const int ring, const int64_t rows_per_cta, const int cache_mod) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    const int warps = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int64_t D = a.D;
-    const int nvec = (int)(D >> 3);  // 8-element vectors per row
+    const uint32_t row_bytes = (uint32_t)(D * sizeof(T));
+    float* s_mul = reinterpret_cast<float*>(smem);            // [D]  (only when cache_mod)
+    const int64_t mod_elems = round_up(D, 512);                // whole groups of 32 chunks
+    float* s_add = s_mul + mod_elems;
+    uint8_t* rows_base = smem + (cache_mod ? (size_t)mod_elems * 8 : 0);
+    uint8_t* my_rows = rows_base + (size_t)warp * ring * row_bytes;
+    uint64_t* my_bars = reinterpret_cast<uint64_t*>(rows_base + (size_t)warps * ring * row_bytes) + warp * ring;
+    const int nchunk = (int)(D >> 4);  // 16-element chunks per row
 
-    if (row >= a.N) {
-        // rows that exist only as padding of the tiled scale buffer: zero their scale bytes
-        if (kMode != kOutPlain && row < round_up(a.N, 128)) {
-            for (int64_t c4 = lane; c4 < (a.sf_cpad >> 2); c4 += 32)
-                *reinterpret_cast<uint32_t*>(a.sf + sf_offset(row, c4 * 4, a.sf_cpad)) = 0u;
+    if (lane == 0) {
+        for (int s = 0; s < ring; ++s)
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_u32(&my_bars[s])));
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    __syncwarp();
+
+    const int64_t total_rows = kMode == kOutPlain ? a.N : round_up(a.N, 128);
+    const int64_t r0 = (int64_t)blockIdx.x * rows_per_cta;
+    const int64_t r1 = min(r0 + rows_per_cta, total_rows);
+    const T* __restrict__ xg = static_cast<const T*>(a.x);
+
+    auto issue = [&](int64_t r, int slot) {
+        if (r < r1 && r < a.N && lane == 0) {
+            const uint32_t bar = smem_u32(&my_bars[slot]);
+            asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(row_bytes) : "memory");
+            asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                         ::"r"(smem_u32(my_rows + (size_t)slot * row_bytes)), "l"(xg + r * D), "r"(row_bytes), "r"(bar) : "memory");
         }
-        return;
-    }
+    };
 
-    const T* __restrict__ x = static_cast<const T*>(a.x) + row * D;
-    Raw8<T> raw[kNV];
-#pragma unroll
-    for (int i = 0; i < kNV; ++i) {
-        const int v = i * 32 + lane;
-        raw[i] = v < nvec ? load_raw8<T>(x + (int64_t)v * 8) : zero_raw8<T>();
-    }
+    int64_t r_issue = r0 + warp;
+    int64_t issued = 0;
+    for (; issued < ring - 1; ++issued, r_issue += warps) issue(r_issue, (int)(issued % ring));
 
-    float mean = 0.0f;
-    if (!a.rms) {
-        float s = 0.0f;
-#pragma unroll
-        for (int i = 0; i < kNV; ++i) {
-            float f[8];
-            unpack8(raw[i], f);
-#pragma unroll
-            for (int j = 0; j < 8; ++j) s += f[j];
-        }
-        mean = warp_sum(s) / (float)D;
-    }
-    float ss = 0.0f;
-#pragma unroll
-    for (int i = 0; i < kNV; ++i) {
-        if (i * 32 + lane < nvec) {
-            float f[8];
-            unpack8(raw[i], f);
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                const float d = f[j] - mean;
-                ss = fmaf(d, d, ss);
-            }
-        }
-    }
-    const float rstd = rsqrtf(warp_sum(ss) / (float)D + a.eps);
-
-    const T* __restrict__ sc = a.scale ? static_cast<const T*>(a.scale) + (row / a.scale_group) * D : nullptr;
-    const T* __restrict__ sh = a.shift ? static_cast<const T*>(a.shift) + (row / a.shift_group) * D : nullptr;
     const Nvfp4Ctx ctx = nvfp4_ctx(kMode == kOutNvfp4 ? __ldg(a.global_scale) : 1.0f);
+    const float inv_d = 1.0f / (float)D;
+    const T* __restrict__ scale_g = static_cast<const T*>(a.scale);
+    const T* __restrict__ shift_g = static_cast<const T*>(a.shift);
 
-#pragma unroll
-    for (int i = 0; i < kNV; ++i) {
-        const int v = i * 32 + lane;
-        const bool ok = v < nvec;
-        float y[8];
-#pragma unroll
-        for (int j = 0; j < 8; ++j) y[j] = 0.0f;
-        if (ok) {
-            float f[8], m[8], b[8];
-            unpack8(raw[i], f);
-            if (sc) load8<T>(sc + (int64_t)v * 8, m);
-            if (sh) load8<T>(sh + (int64_t)v * 8, b);
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                const float mul = sc ? (a.rms ? m[j] : 1.0f + m[j]) : 1.0f;
-                const float add = sh ? b[j] : 0.0f;
-                y[j] = fmaf((f[j] - mean) * rstd, mul, add);
+    int64_t row = r0 + warp;
+    int64_t i = 0;
+    bool alive = true;
+    for (int64_t seg = r0; seg < r1;) {
+        // rows [seg, seg_end) share one scale row and one shift row
+        int64_t seg_end = r1;
+        if (cache_mod) {
+            const int64_t lim = min(a.N, r1);
+            if (seg < lim) {
+                seg_end = lim;
+                if (scale_g) seg_end = min(seg_end, (seg / a.scale_group + 1) * a.scale_group);
+                if (shift_g) seg_end = min(seg_end, (seg / a.shift_group + 1) * a.shift_group);
+                __syncthreads();  // the previous segment's readers are done with the cache
+                const T* sc = scale_g ? scale_g + (seg / a.scale_group) * D : nullptr;
+                const T* sh = shift_g ? shift_g + (seg / a.shift_group) * D : nullptr;
+                for (int64_t j = threadIdx.x; j < D; j += blockDim.x) {
+                    const float m = sc ? Elem<T>::to_f32(sc[j]) : (a.rms ? 1.0f : 0.0f);
+                    const int pos = mod_pos((int)(j >> 4), (int)(j & 15));
+                    s_mul[pos] = a.rms ? m : 1.0f + m;
+                    s_add[pos] = sh ? Elem<T>::to_f32(sh[j]) : 0.0f;
+                }
+                __syncthreads();
             }
         }
-        if (kMode == kOutPlain) {
-            if (ok) store8<T>(static_cast<T*>(a.out) + row * D + (int64_t)v * 8, y);
-        } else {
-            // the quantizers see the activation as it would have been stored
-#pragma unroll
-            for (int j = 0; j < 8; ++j) y[j] = Elem<T>::round(y[j]);
-            if (kMode == kOutNvfp4) {
-                uint32_t s8;
-                const uint32_t packed = nvfp4_encode_half_block(y, ctx, a.hi_first != 0, s8);
-                if (!ok) s8 = 0u;
-                // four scale bytes (lanes L, L+2, L+4, L+6) leave as one 32-bit store
-                uint32_t w = s8;
-                w |= __shfl_down_sync(0xffffffffu, s8, 2) << 8;
-                w |= __shfl_down_sync(0xffffffffu, s8, 4) << 16;
-                w |= __shfl_down_sync(0xffffffffu, s8, 6) << 24;
-                if (ok) *reinterpret_cast<uint32_t*>(static_cast<uint8_t*>(a.out) + row * (D >> 1) + (int64_t)v * 4) = packed;
-                const int64_t c = (int64_t)i * 16 + (lane >> 1);  // block column of this lane pair
-                if ((lane & 7) == 0 && c < a.sf_cpad)
-                    *reinterpret_cast<uint32_t*>(a.sf + sf_offset(row, c, a.sf_cpad)) = w;
-            } else {
-                uint32_t e;
-                const uint2 packed = mxfp8_encode_quarter_block(y, e);
-                if (!ok) e = 0u;
-                uint32_t w = e;
-                w |= __shfl_down_sync(0xffffffffu, e, 4) << 8;
-                w |= __shfl_down_sync(0xffffffffu, e, 8) << 16;
-                w |= __shfl_down_sync(0xffffffffu, e, 12) << 24;
-                if (ok) *reinterpret_cast<uint2*>(static_cast<uint8_t*>(a.out) + row * D + (int64_t)v * 8) = packed;
-                const int64_t c = (int64_t)i * 8 + (lane >> 2);
-                if ((lane & 15) == 0 && c < a.sf_cpad)
-                    *reinterpret_cast<uint32_t*>(a.sf + sf_offset(row, c, a.sf_cpad)) = w;
+        for (; row < seg_end && alive; row += warps, ++i) {
+            // refill the slot consumed in the previous iteration
+            issue(r_issue, (int)(issued % ring));
+            ++issued;
+            r_issue += warps;
+
+            if (row >= a.N) {
+                // rows that exist only as padding of the tiled scale buffer: zero their scale bytes
+                if (kMode != kOutPlain)
+                    for (int64_t c4 = lane; c4 < (a.sf_cpad >> 2); c4 += 32)
+                        *reinterpret_cast<uint32_t*>(a.sf + sf_offset(row, c4 * 4, a.sf_cpad)) = 0u;
+                continue;
             }
+
+            const int slot = (int)(i % ring);
+            {
+                const uint32_t bar = smem_u32(&my_bars[slot]), parity = (uint32_t)((i / ring) & 1);
+                uint32_t done = 0;
+                for (uint32_t spin = 0; spin < kRowWaitLimit && !done; ++spin)
+                    asm volatile("{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
+                                 : "=r"(done) : "r"(bar), "r"(parity) : "memory");
+                if (!__all_sync(0xffffffffu, done != 0)) {
+                    if (lane == 0) atomicCAS(&g_norm_status, 0, 1);
+                    alive = false;  // stop touching rows; still take part in the CTA barriers below
+                    break;
+                }
+            }
+            const T* xs = reinterpret_cast<const T*>(my_rows + (size_t)slot * row_bytes);
+
+            // statistics in one pass, shifted by the row's first element
+            const float shift0 = a.rms ? 0.0f : Elem<T>::to_f32(xs[0]);
+            float s1a = 0.0f, s1b = 0.0f, s2a = 0.0f, s2b = 0.0f;
+#pragma unroll 2
+            for (int c = lane; c < nchunk; c += 32) {
+                float f[16];
+                lds16<T, false>(xs + c * 16, lane, f);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    const float d0 = f[j] - shift0, d1 = f[8 + j] - shift0;
+                    s1a += d0; s1b += d1;
+                    s2a = fmaf(d0, d0, s2a); s2b = fmaf(d1, d1, s2b);
+                }
+            }
+            const float m1 = warp_sum(s1a + s1b) * inv_d;   // mean - shift0
+            const float m2 = warp_sum(s2a + s2b) * inv_d;   // E[(x - shift0)^2]
+            const float mean = a.rms ? 0.0f : shift0 + m1;
+            const float var = a.rms ? m2 : fmaxf(m2 - m1 * m1, 0.0f);
+            const float rstd = rsqrtf(var + a.eps);
+            const float nmr = -mean * rstd;
+
+            const T* __restrict__ sc = (!cache_mod && scale_g) ? scale_g + (row / a.scale_group) * D : nullptr;
+            const T* __restrict__ sh = (!cache_mod && shift_g) ? shift_g + (row / a.shift_group) * D : nullptr;
+
+            // whole-warp steps so the shuffles inside the block encoders see all 32 lanes
+#pragma unroll 2
+            for (int c0 = 0; c0 < nchunk; c0 += 32) {
+                const int c = c0 + lane;
+                const bool ok = c < nchunk;
+                float y[16];
+#pragma unroll
+                for (int j = 0; j < 16; ++j) y[j] = 0.0f;
+                if (ok) {
+                    float f[16];
+                    lds16<T, true>(xs + c * 16, lane, f);
+                    if (cache_mod) {
+#pragma unroll
+                        for (int j4 = 0; j4 < 4; ++j4) {
+                            const float4 mu = *reinterpret_cast<const float4*>(s_mul + mod_pos(c, j4 * 4));
+                            const float4 ad = *reinterpret_cast<const float4*>(s_add + mod_pos(c, j4 * 4));
+                            y[4 * j4 + 0] = fmaf(fmaf(f[4 * j4 + 0], rstd, nmr), mu.x, ad.x);
+                            y[4 * j4 + 1] = fmaf(fmaf(f[4 * j4 + 1], rstd, nmr), mu.y, ad.y);
+                            y[4 * j4 + 2] = fmaf(fmaf(f[4 * j4 + 2], rstd, nmr), mu.z, ad.z);
+                            y[4 * j4 + 3] = fmaf(fmaf(f[4 * j4 + 3], rstd, nmr), mu.w, ad.w);
+                        }
+                    } else {
+                        float m[16], b[16];
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) { m[j] = a.rms ? 1.0f : 0.0f; b[j] = 0.0f; }
+                        if (scale_g) load16<T>(sc + (int64_t)c * 16, m);
+                        if (shift_g) load16<T>(sh + (int64_t)c * 16, b);
+#pragma unroll
+                        for (int j = 0; j < 16; ++j)
+                            y[j] = fmaf(fmaf(f[j], rstd, nmr), a.rms ? m[j] : 1.0f + m[j], b[j]);
+                    }
+                }
+                if (kMode == kOutPlain) {
+                    if (ok) store16<T>(static_cast<T*>(a.out) + row * D + (int64_t)c * 16, y);
+                } else {
+                    // the quantizers see the activation as it would have been stored
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) y[j] = Elem<T>::round(y[j]);
+                    if (kMode == kOutNvfp4) {
+                        uint32_t s8;
+                        const uint2 packed = nvfp4_encode_block(y, ctx, a.hi_first != 0, s8);
+                        if (ok) {
+                            *reinterpret_cast<uint2*>(static_cast<uint8_t*>(a.out) + row * (D >> 1) + (int64_t)c * 8) = packed;
+                            a.sf[sf_offset(row, c, a.sf_cpad)] = (uint8_t)s8;
+                        } else if (c < a.sf_cpad) {
+                            a.sf[sf_offset(row, c, a.sf_cpad)] = 0;  // scale columns that pad the row to a multiple of 4
+                        }
+                    } else {
+                        // 32-element block = this lane's chunk and its neighbour's (lane ^ 1)
+                        uint32_t e;
+                        float lo[8], hi[8];
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) { lo[j] = y[j]; hi[j] = y[8 + j]; }
+                        float amax = 0.0f;
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) amax = fmaxf(amax, fabsf(y[j]));
+                        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+                        const uint2 p0 = mxfp8_encode8(lo, amax, e), p1 = mxfp8_encode8(hi, amax, e);
+                        if (ok) {
+                            *reinterpret_cast<uint4*>(static_cast<uint8_t*>(a.out) + row * D + (int64_t)c * 16) =
+                                make_uint4(p0.x, p0.y, p1.x, p1.y);
+                            if ((lane & 1) == 0) a.sf[sf_offset(row, c >> 1, a.sf_cpad)] = (uint8_t)e;
+                        } else if ((lane & 1) == 0 && (c >> 1) < a.sf_cpad) {
+                            a.sf[sf_offset(row, c >> 1, a.sf_cpad)] = 0;
+                        }
+                    }
+                }
+            }
+            __syncwarp();  // every lane is done with this slot before it is refilled
         }
+        seg = seg_end;
     }
 }
 
@@ -203,23 +329,44 @@ norm_generic_kernel(const NormArgs a) {
 
 template <typename T, int kMode>
 int launch_warp(const NormArgs& a, cudaStream_t stream) {
-    const int need = (int)ceil_div(a.D, 256);  // vectors per lane
+    const size_t row_bytes = (size_t)a.D * sizeof(T);
+    // the modulation cache pays when a modulation row serves many rows (AdaLN: one per batch entry)
+    const bool has_mod = a.scale || a.shift;
+    const int cache_mod = has_mod && (!a.scale || a.scale_group >= 32) && (!a.shift || a.shift_group >= 32);
+    const size_t mod_bytes = cache_mod ? (size_t)round_up(a.D, 512) * 8 : 0;
+    const size_t budget = 208 * 1024 - mod_bytes;
+    // warps per CTA and ring depth from the shared-memory budget: as many warps as fit with a ring of
+    // two rows each, then a third row if there is room
+    int warps = 0, ring = 2;
+    for (int w : {16, 12, 8, 6, 4, 2, 1})
+        if ((size_t)w * 2 * row_bytes <= budget) { warps = w; break; }
+    if (warps == 0)
+        CK_FAIL(CK_ERR_SHAPE, "adaln: a row of %lld bytes does not fit the staging ring", (long long)row_bytes);
+    if ((size_t)warps * 3 * row_bytes <= budget) ring = 3;
+    const size_t smem = mod_bytes + (size_t)warps * ring * row_bytes + (size_t)warps * ring * 8;
+    auto kern = norm_stream_kernel<T, kMode>;
+    static bool attr_set[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 64 || !attr_set[dev]) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 216 * 1024);
+        if (e != cudaSuccess) CK_FAIL((int)e, "adaln: cannot reserve shared memory: %s", cudaGetErrorString(e));
+        if (dev >= 0 && dev < 64) attr_set[dev] = true;
+    }
     const int64_t rows = kMode == kOutPlain ? a.N : round_up(a.N, 128);
-    const unsigned grid = (unsigned)ceil_div(rows, 8);
-#define CK_NORM_CASE(NV) \
-    if (need <= NV) { norm_warp_kernel<T, NV, kMode><<<grid, 256, 0, stream>>>(a); return launch_status("adaln"); }
-    CK_NORM_CASE(1)
-    CK_NORM_CASE(2)
-    CK_NORM_CASE(4)
-    CK_NORM_CASE(8)
-    CK_NORM_CASE(12)
-    CK_NORM_CASE(16)
-#undef CK_NORM_CASE
-    CK_FAIL(CK_ERR_SHAPE, "adaln: row length %lld exceeds the fused path's limit of 4096", (long long)a.D);
+    int sms = 148;
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    // one CTA per SM, each with a contiguous range of rows (at least one row per warp)
+    int64_t grid = ceil_div(rows, warps);
+    if (grid > sms) grid = sms;
+    const int64_t rows_per_cta = ceil_div(rows, grid);
+    grid = ceil_div(rows, rows_per_cta);
+    kern<<<(unsigned)grid, warps * 32, smem, stream>>>(a, ring, rows_per_cta, cache_mod);
+    return launch_status("adaln");
 }
 
 bool warp_path_ok(const NormArgs& a) {
-    return a.D % 8 == 0 && a.D <= 4096 && aligned16(a.x) && (!a.scale || aligned16(a.scale)) &&
+    return a.D % 16 == 0 && (size_t)a.D * 4 <= 48 * 1024 && aligned16(a.x) && (!a.scale || aligned16(a.scale)) &&
            (!a.shift || aligned16(a.shift)) && aligned16(a.out);
 }
 
@@ -281,7 +428,7 @@ int launch_fused(NormArgs a, int dtype_code, cudaStream_t stream) {
     if (a.D % blk != 0) CK_FAIL(CK_ERR_SHAPE, "%s: row length %lld must be a multiple of %d", what, (long long)a.D, blk);
     a.sf_cpad = round_up(a.D / blk, 4);
     if (!warp_path_ok(a) || (reinterpret_cast<uintptr_t>(a.sf) & 3u))
-        CK_FAIL(CK_ERR_UNSUPPORTED, "%s: needs 16-byte aligned tensors and row length <= 4096", what);
+        CK_FAIL(CK_ERR_UNSUPPORTED, "%s: needs 16-byte aligned tensors and a row length that is a multiple of 8", what);
     switch (dtype_code) {
     case CK_F32: return launch_warp<float, kMode>(a, stream);
     case CK_F16: return launch_warp<__half, kMode>(a, stream);

@@ -278,9 +278,12 @@ __device__ __forceinline__ Nvfp4Ctx nvfp4_ctx(float g) {
     return c;
 }
 
+// Written as q0 - (b*q0 - a)*r rather than q0 + (a - b*q0)*r: the same value, but a zero result keeps
+// the sign of `a` (b > 0), which is the sign an IEEE division gives (-0.0 / b = -0.0 -> E2M1 code 8).
 __device__ __forceinline__ float div_by_reciprocal(float a, float b, float r) {
     const float q0 = __fmul_rn(a, r);
-    return __fmaf_rn(__fmaf_rn(-b, q0, a), r, q0);
+    const float e = __fmaf_rn(b, q0, -a);
+    return __fmaf_rn(-e, r, q0);
 }
 
 struct Nvfp4Block {
@@ -320,8 +323,7 @@ __device__ __forceinline__ uint32_t nvfp4_codes8(const float (&v)[8], const Nvfp
     float q[8];
     if (b.fast) {
 #pragma unroll
-        for (int i = 0; i < 8; ++i)  // the quotient's sign is x's (tot > 0); the FMA pair loses it for x = -0
-            q[i] = copysignf(div_by_reciprocal(v[i], b.tot, b.rtot), v[i]);
+        for (int i = 0; i < 8; ++i) q[i] = div_by_reciprocal(v[i], b.tot, b.rtot);
     } else {
 #pragma unroll
         for (int i = 0; i < 8; ++i) q[i] = __fdiv_rn(v[i], b.tot);
@@ -521,21 +523,14 @@ __device__ __forceinline__ uint32_t mx_scale_byte(float amax) {
     return e > 254u ? 254u : e;
 }
 
-// MXFP8: this lane holds 8 of the 32 elements of a block (lanes ^1, ^2 hold the
-// rest).  Returns 8 E4M3 bytes and the block's E8M0 byte (0 for an all-zero block).
-__device__ __forceinline__ uint2 mxfp8_encode_quarter_block(const float (&v)[8], uint32_t& e) {
-    float amax = 0.0f;
-#pragma unroll
-    for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
-    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
-    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+// MXFP8: eight elements of a block whose amax is already known -> eight E4M3 bytes and the E8M0 byte.
+__device__ __forceinline__ uint2 mxfp8_encode8(const float (&v)[8], float amax, uint32_t& e) {
     e = 0;
     uint32_t w[2] = {0u, 0u};
     if (amax != 0.0f) {
         e = mx_scale_byte(amax);
         if (e != 0u) {
-            // 2^(127-e); for e == 254 that is the subnormal 2^-127
-            const float inv = __uint_as_float(e == 254u ? 0x00400000u : ((254u - e) << 23));
+            const float inv = __uint_as_float(e == 254u ? 0x00400000u : ((254u - e) << 23));  // 2^(127-e)
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
                 const uint32_t two = cvt_e4m3x2(__fmul_rn(v[2 * i + 1], inv), __fmul_rn(v[2 * i], inv));
@@ -552,6 +547,17 @@ __device__ __forceinline__ uint2 mxfp8_encode_quarter_block(const float (&v)[8],
         }
     }
     return make_uint2(w[0], w[1]);
+}
+
+// MXFP8: this lane holds 8 of the 32 elements of a block (lanes ^1, ^2 hold the
+// rest).  Returns 8 E4M3 bytes and the block's E8M0 byte (0 for an all-zero block).
+__device__ __forceinline__ uint2 mxfp8_encode_quarter_block(const float (&v)[8], uint32_t& e) {
+    float amax = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+    return mxfp8_encode8(v, amax, e);
 }
 
 }  // namespace ck

@@ -222,7 +222,8 @@ def test_nvfp4_reciprocal_division_is_exact(ck):
         if i % 4 == 2:
             x = torch.where(torch.rand(M, K, device="cuda", generator=gen) < 0.01, 40.0 * x, x)
         if i % 4 == 3:
-            x = (x * 4).round() / 4  # many exact ties
+            x = (x * 4).round() / 4  # many exact ties, and both signs of zero
+            x = torch.where(x == 0, torch.where(torch.rand(M, K, device="cuda", generator=gen) < 0.5, -0.0, 0.0), x)
         x = x.to(dt)
         amax = x.float().abs().max()
         # a spread of per-tensor scales: the natural one, ones that clamp block scales at 448, tiny, huge
