@@ -11,23 +11,29 @@
 // (MXFP8); the reference's CUDA backend forwards NVFP4 to a library GEMM
 // (backends/cuda/ops/cublas_gemm_nvfp4.cu:64-340) and has no MXFP8 kernel.
 //
-// Kernel structure (one persistent CTA per SM, 192 threads):
-//   warp 0      TMA producer: per k-tile one 128x128B box of A, one 192x128B box
-//               of W (both SWIZZLE_128B) and the scale tiles (plain bulk copies)
-//               into a 4-stage shared-memory ring, completion on mbarriers.
-//   warp 1      MMA issuer: tcgen05.cp scale tiles smem->TMEM, then four
-//               tcgen05.mma.kind::{mxf4nvf4,mxf8f6f4}.block_scale per k-tile
-//               (128x192xK64 for FP4, xK32 for FP8), accumulating in TMEM;
-//               tcgen05.commit releases the stage and, per tile, publishes the
-//               accumulator.
-//   warps 2-5   epilogue: tcgen05.ld the 128x192 fp32 accumulator (each warp its
-//               32 TMEM lanes), alpha*acc + bias, convert, 64-byte row stores.
-// Two accumulators (TMEM columns 0 and 256) let the epilogue of tile i overlap the
-// main loop of tile i+1.  Tile = 128x192: two 192-column accumulators plus the
-// scale-factor columns fit the 512 TMEM columns; 192 divides every N of the
-// target shapes (3072, 9216, 12288).  A 192-wide tile starts on a 128-row scale
-// tile boundary only every other tile; odd tiles load the enclosing two scale
-// tiles and hand the MMA a TMEM address two columns in.
+// Kernel structure (one persistent CTA per SM, 448 threads, tile 128 x 256):
+//   warp 0       TMA producer: per k-tile one 128x128B box of A, one 256x128B box
+//                of W (both SWIZZLE_128B) and the scale tiles (plain bulk copies)
+//                into a 4-stage shared-memory ring, completion on mbarriers.
+//   warps 10-13  scale movers: shared memory -> registers -> TMEM (tcgen05.st), one
+//                warp per 32-lane quarter of TMEM, into a ring of three scale
+//                buffers.  tcgen05.cp could do this move too, but it queues on the
+//                tensor pipe in front of the MMAs (~22 clocks per 512-byte tile
+//                measured); the register path runs beside the MMAs instead.
+//   warp 1       MMA issuer: four tcgen05.mma.kind::{mxf4nvf4,mxf8f6f4}.block_scale
+//                per k-tile (128x256xK64 for FP4, xK32 for FP8), accumulating in
+//                TMEM; tcgen05.commit releases the stage and its scale buffer and,
+//                per tile, publishes the accumulator.
+//   warps 2-9    epilogue: each warp reads its 32 TMEM lanes x 128 columns of the
+//                fp32 accumulator into registers (tcgen05.ld), hands the accumulator
+//                back, then applies alpha and bias, converts and stores, which
+//                overlaps the next tile's main loop.
+// Why 256 columns: measured on B200, one block-scaled MMA with M = 128 occupies the
+// issuing thread ~140 clocks whether N is 64, 128, 192 or 256, so only N = 256
+// reaches the tensor cores' rate.  The 256-column accumulator leaves room for the
+// scale ring (A: 16 columns, W: 32 columns per k-tile, three buffers) but not for a
+// second accumulator, hence the register-buffered epilogue: the accumulator is
+// busy for a few hundred clocks per tile instead of a whole epilogue.
 //
 // Every wait in this file is bounded: on expiry the CTA records a status word,
 // stops issuing work, drains its own copies and frees its TMEM before returning.
@@ -42,24 +48,33 @@ namespace ck {
 namespace {
 
 constexpr int BM = 128;
-constexpr int BN = 192;
-constexpr int kStages = 4;
-constexpr int kThreads = 192;
+constexpr int BN = 256;
+#ifndef CK_GEMM_STAGES
+#define CK_GEMM_STAGES 4
+#endif
+constexpr int kStages = CK_GEMM_STAGES;
+constexpr int kFirstEpiWarp = 2, kEpiWarps = 8;   // two warps per TMEM lane quarter, 128 columns each
+constexpr int kFirstMoverWarp = kFirstEpiWarp + kEpiWarps;
+constexpr int kMoverGroups = 2;   // groups of four warps (one per TMEM lane quarter) taking k-tiles in turn
+constexpr int kThreads = 32 * (kFirstMoverWarp + 4 * kMoverGroups);
+constexpr int kSfBufs = 3;
 constexpr int kKbPerTile = 4;  // MMAs per k-tile
 
 constexpr int kSmemA = BM * 128;            // 16 KB
-constexpr int kSmemB = BN * 128;            // 24 KB
-constexpr int kSmemSfA = 4 * 512;           // up to four 512-byte tiles (NVFP4)
-constexpr int kSmemSfB = 2 * 4 * 512;       // two row tiles x four
-constexpr int kStageBytes = kSmemA + kSmemB + kSmemSfA + kSmemSfB;  // 47104
-constexpr int kSmemBias = 4 * BN * 4;       // per-epilogue-warp bias row
-constexpr int kSmemBytes = kStages * kStageBytes + kSmemBias + 256 /*barriers*/ + 1024 /*alignment slack*/;
+constexpr int kSmemB = BN * 128;            // 32 KB
+constexpr int kStageBytes = kSmemA + kSmemB;   // 48 KB
+constexpr int kSmemOut = kEpiWarps * 4096;   // per-epilogue-warp staging: 32 rows x 128 bytes, 128-byte swizzle
+constexpr int kSmemBytes = kStages * kStageBytes + kSmemOut + 256 /*barriers*/ + 1024 /*alignment slack*/;
+static_assert(kSmemBytes <= 232448, "exceeds the 227 KB of shared memory a CTA can have");
 
 constexpr uint32_t kTmemCols = 512;
-constexpr uint32_t kTmemAcc0 = 0, kTmemAcc1 = 256, kTmemSfA = 448, kTmemSfB = 464;
+// accumulator in columns 0..255; scale buffer b: A scales 16 columns at 256 + 48 b, W scales 32 columns after them
+constexpr uint32_t kTmemAcc = 0;
+__device__ __forceinline__ uint32_t tmem_sfa_col(uint32_t b) { return 256u + 48u * b; }
+__device__ __forceinline__ uint32_t tmem_sfb_col(uint32_t b) { return 272u + 48u * b; }
 
 #ifndef CK_GEMM_PROBE
-#define CK_GEMM_PROBE 0   // timing experiments only: 1 = no scale copies, 2 = no TMA payload, 4 = no MMA
+#define CK_GEMM_PROBE 0   // timing experiments only: 1 = no scale moves, 2 = no TMA payload, 4 = no MMA, 8 = timestamps, 16 = no epilogue work
 #endif
 
 constexpr uint32_t kSpinLimit = 1u << 22;   // polls of mbarrier.try_wait before giving up (a fraction of a second)
@@ -69,7 +84,7 @@ __device__ int g_gemm_status = 0;
 __device__ long long g_probe_ts[4 * 256];   // MMA warp of CTA 0, per k-tile: before wait, after wait, after issue
 #endif           // 0 ok; otherwise (code << 16 | detail) of the first failure
 
-enum : int { kTimeoutFull = 1, kTimeoutEmpty = 2, kTimeoutTmemFull = 3, kTimeoutTmemEmpty = 4 };
+enum : int { kTimeoutFull = 1, kTimeoutEmpty = 2, kTimeoutTmemFull = 3, kTimeoutTmemEmpty = 4, kTimeoutSfFull = 5 };
 
 // ------------------------------------------------------------------ PTX wrappers
 
@@ -128,11 +143,15 @@ __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, i
         "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
         ::"r"(smem_u32(dst)), "l"(map), "r"(c0), "r"(c1), "r"(smem_u32(bar)) : "memory");
 }
-__device__ __forceinline__ void bulk_load(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
-    asm volatile(
-        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-        ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
+// Shared -> global tile store (clipped at the tensor's edges), tracked by the issuing thread's bulk groups.
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, const void* src, int c0, int c1) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+                 ::"l"(map), "r"(smem_u32(src)), "r"(c0), "r"(c1) : "memory");
+    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
 }
+__device__ __forceinline__ void bulk_wait_read_all() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
@@ -147,20 +166,9 @@ __device__ __forceinline__ void tc_commit(uint64_t* bar) {
 // leading-offset field for the swizzled form) and a constant high word:
 //   operand tiles: K-major, 128-byte rows, 128-byte swizzle, 8-row groups 1024 bytes apart
 //                  -> hi = SBO 64 | version 1 (bit 46) | layout SWIZZLE_128B (bits 61-63)
-//   scale tiles:   32 rows x 16 bytes, unswizzled, 8-row groups 128 bytes apart
-//                  -> hi = SBO 8 | version 1
 constexpr uint32_t kDescHiOperand = 64u | (1u << 14) | (2u << 29);
-constexpr uint32_t kDescHiScale = 8u | (1u << 14);
 constexpr uint32_t kDescLoLbo1 = 1u << 16;
 
-__device__ __forceinline__ void tc_cp_sf(uint32_t tmem_addr, uint32_t desc_lo) {
-    if (CK_GEMM_PROBE & 1) return;
-    if (elect_one())
-    asm volatile(
-        "{ .reg .b64 d; mov.b64 d, {%1, %2};\n"
-        "tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], d; }"
-        ::"r"(tmem_addr), "r"(desc_lo), "n"(kDescHiScale) : "memory");
-}
 template <bool kFp4>
 __device__ __forceinline__ void tc_mma(uint32_t d, uint32_t a_lo, uint32_t b_lo, uint32_t idesc, uint32_t accumulate,
                                        uint32_t sfa, uint32_t sfb) {
@@ -192,6 +200,23 @@ __device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
         : "r"(taddr) : "memory");
 }
 __device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+// Register -> TMEM stores: thread i of the warp writes lane (32 * (warp % 4) + i), consecutive columns.
+__device__ __forceinline__ void tc_st16(uint32_t taddr, const uint32_t* r) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+        "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+          "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]) : "memory");
+}
+__device__ __forceinline__ void tc_st8(uint32_t taddr, const uint32_t* r) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};"
+                 ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]) : "memory");
+}
+__device__ __forceinline__ void tc_st4(uint32_t taddr, const uint32_t* r) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x4.b32 [%0], {%1,%2,%3,%4};"
+                 ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]) : "memory");
+}
+__device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
 struct GemmParams {
     const uint8_t* sfa;
@@ -205,6 +230,19 @@ struct GemmParams {
     int out_code, bias_code;
     int tiles_m, tiles_n;
 };
+
+template <typename T16>
+__device__ __forceinline__ uint32_t pack_pair(float a, float b);
+template <>
+__device__ __forceinline__ uint32_t pack_pair<__nv_bfloat16>(float a, float b) {
+    const __nv_bfloat162 v = __floats2bfloat162_rn(a, b);   // .x = a in the low half
+    return *reinterpret_cast<const uint32_t*>(&v);
+}
+template <>
+__device__ __forceinline__ uint32_t pack_pair<__half>(float a, float b) {
+    const __half2 v = __floats2half2_rn(a, b);
+    return *reinterpret_cast<const uint32_t*>(&v);
+}
 
 template <typename TO>
 __device__ __forceinline__ void store_row32(TO* dst, const float (&v)[32], int valid) {
@@ -223,18 +261,20 @@ __device__ __forceinline__ void store_row32(TO* dst, const float (&v)[32], int v
 template <bool kFp4>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                        const GemmParams p) {
+                        const __grid_constant__ CUtensorMap map_out, const GemmParams p) {
     extern __shared__ uint8_t smem_raw[];
     // 1024-byte alignment for the swizzled operand tiles
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* stage_base = smem;
-    float* s_bias = reinterpret_cast<float*>(smem + kStages * kStageBytes);
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages * kStageBytes + kSmemBias);
-    uint64_t* full = bars;                    // [kStages]  TMA -> MMA
-    uint64_t* empty = bars + kStages;         // [kStages]  MMA -> TMA
-    uint64_t* tmem_full = bars + 2 * kStages; // [2]        MMA -> epilogue
-    uint64_t* tmem_empty = tmem_full + 2;     // [2]        epilogue -> MMA
-    uint32_t* s_tmem_base = reinterpret_cast<uint32_t*>(tmem_empty + 2);
+    uint8_t* s_out = smem + kStages * kStageBytes;   // 1024-byte aligned: kStageBytes is a multiple of 1024
+    uint64_t* bars = reinterpret_cast<uint64_t*>(s_out + kSmemOut);
+    uint64_t* full = bars;                    // [kStages]  TMA landed -> scale movers (and, through sf_full, the MMA issuer)
+    uint64_t* empty = bars + kStages;         // [kStages]  movers have read the scales + MMAs of the k-tile done
+                                              //            -> TMA producer (stage free), movers (scale buffer free)
+    uint64_t* sf_full = bars + 2 * kStages;   // [kSfBufs]  scales in TMEM -> MMA issuer
+    uint64_t* tmem_full = sf_full + kSfBufs;  //            accumulator complete -> epilogue
+    uint64_t* tmem_empty = tmem_full + 1;     //            accumulator copied to registers -> MMA issuer
+    uint32_t* s_tmem_base = reinterpret_cast<uint32_t*>(tmem_empty + 1);
     volatile int* s_abort = reinterpret_cast<volatile int*>(s_tmem_base + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -246,7 +286,9 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
-        for (int b = 0; b < 2; ++b) { mbar_init(&tmem_full[b], 1); mbar_init(&tmem_empty[b], 4); }
+        for (int b = 0; b < kSfBufs; ++b) mbar_init(&sf_full[b], 4);
+        mbar_init(tmem_full, 1);
+        mbar_init(tmem_empty, kEpiWarps);
         *s_abort = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -266,11 +308,6 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
         bool ok = true;
         for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
             const int tm = tile % p.tiles_m, tn = tile / p.tiles_m;
-            const int row_tile_b = (tn * BN) >> 7;  // first 128-row scale tile touched by this W tile
-            const int b_tiles = (row_tile_b + 1 < p.sf_row_tiles_b) ? 2 : 1;
-            const size_t sf_row_pitch = (size_t)p.sf_tiles_k * 512;
-            const uint8_t* sfa_src = p.sfa + (size_t)tm * sf_row_pitch;
-            const uint8_t* sfb_src = p.sfb + (size_t)row_tile_b * sf_row_pitch;
             for (int kt = 0; kt < k_tiles && ok; ++kt, ++it) {
                 const int s = it % kStages;
                 const uint32_t round = it / kStages;
@@ -278,11 +315,7 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
                 if (!ok) break;
                 // operands are computed by the whole warp; one elected lane issues the copies
                 uint8_t* st = stage_base + s * kStageBytes;
-                int n_sf = p.sf_tiles_k - kt * kSfTilesPerStage;  // scale tiles valid in this k-tile (the last may be short)
-                if (n_sf > kSfTilesPerStage) n_sf = kSfTilesPerStage;
-                const uint32_t sf_bytes = (uint32_t)n_sf * 512u;
-                const size_t sf_off = (size_t)kt * (kSfTilesPerStage * 512);
-                const uint32_t tx_bytes = kSmemA + kSmemB + sf_bytes * (1 + b_tiles);
+                const uint32_t tx_bytes = kSmemA + kSmemB;
                 if (elect_one()) {
                     if (CK_GEMM_PROBE & 2) {
                         mbar_arrive(&full[s]);
@@ -290,11 +323,6 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
                         mbar_expect_tx(&full[s], tx_bytes);
                         tma_load_2d(st, &map_a, kt * 128, tm * BM, &full[s]);
                         tma_load_2d(st + kSmemA, &map_b, kt * 128, tn * BN, &full[s]);
-                        bulk_load(st + kSmemA + kSmemB, sfa_src + sf_off, sf_bytes, &full[s]);
-                        bulk_load(st + kSmemA + kSmemB + kSmemSfA, sfb_src + sf_off, sf_bytes, &full[s]);
-                        if (b_tiles == 2)
-                            bulk_load(st + kSmemA + kSmemB + kSmemSfA + kSmemSfB / 2, sfb_src + sf_row_pitch + sf_off,
-                                      sf_bytes, &full[s]);
                     }
                 }
                 __syncwarp();
@@ -305,6 +333,74 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
         for (uint32_t j = first; j < it; ++j) {
             const int s = j % kStages;
             (void)mbar_wait(&full[s], (j / kStages) & 1, s_abort, kTimeoutFull);
+        }
+    } else if (warp >= kFirstMoverWarp) {
+        // ------------------------------------------------------------ scale movers (global -> registers -> TMEM)
+        // A 512-byte scale tile is 32 rows x 16 bytes: row i holds, for the four 32-row groups g of a
+        // 128-row tile, the scale bytes of row 32g + i.  The MMA wants it in TMEM as 32 lanes x 4 columns
+        // (column g), the same in each 32-lane quarter.  Each mover warp owns one quarter: lane i reads row
+        // i of every tile of the k-tile with 128-bit loads (512 contiguous bytes per warp and load; the four
+        // warps read the same lines, which L1 serves) and stores the words to TMEM lane i.  Two groups of four
+        // warps take the k-tiles in turn, so a group's loads have two k-tiles' time to arrive.  k-tile `it`
+        // uses scale buffer it % 3, last read by the MMAs of k-tile it - 3, whose completion empty[] reports.
+        const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
+        constexpr int kNa = kFp4 ? 16 : 4, kNb = kFp4 ? 32 : 8;   // words per lane: A scales, W scales
+        const size_t sf_row_pitch = (size_t)p.sf_tiles_k * 512;
+        uint32_t nxt_a[kNa], nxt_b[kNb];
+        auto fetch = [&](int tile, int kt) {
+            const int tm = tile % p.tiles_m, tn = tile / p.tiles_m;
+            const int row_tile_b = tn * (BN / 128);   // first of the two 128-row scale tiles of this W tile
+            const bool second = row_tile_b + 1 < p.sf_row_tiles_b;
+            const uint8_t* a_src = p.sfa + (size_t)tm * sf_row_pitch + (size_t)kt * (kSfTilesPerStage * 512) + lane * 16;
+            const uint8_t* b_src = p.sfb + (size_t)row_tile_b * sf_row_pitch + (size_t)kt * (kSfTilesPerStage * 512) + lane * 16;
+            const int n_sf = p.sf_tiles_k - kt * kSfTilesPerStage;   // tiles that exist in this k-tile (the last may be short)
+#pragma unroll
+            for (int t = 0; t < kSfTilesPerStage; ++t) {   // k-block t: A columns 4t.., W columns 8t.. (first, then second row tile)
+                uint4 va = make_uint4(0, 0, 0, 0), v0 = va, v1 = va;
+                if (t < n_sf && !(CK_GEMM_PROBE & 1)) {
+                    va = __ldg(reinterpret_cast<const uint4*>(a_src + t * 512));
+                    v0 = __ldg(reinterpret_cast<const uint4*>(b_src + t * 512));
+                    if (second) v1 = __ldg(reinterpret_cast<const uint4*>(b_src + sf_row_pitch + t * 512));
+                }
+                nxt_a[4 * t] = va.x; nxt_a[4 * t + 1] = va.y; nxt_a[4 * t + 2] = va.z; nxt_a[4 * t + 3] = va.w;
+                nxt_b[8 * t + 0] = v0.x; nxt_b[8 * t + 1] = v0.y; nxt_b[8 * t + 2] = v0.z; nxt_b[8 * t + 3] = v0.w;
+                nxt_b[8 * t + 4] = v1.x; nxt_b[8 * t + 5] = v1.y; nxt_b[8 * t + 6] = v1.z; nxt_b[8 * t + 7] = v1.w;
+            }
+        };
+        const uint32_t group = (uint32_t)(warp - kFirstMoverWarp) >> 2;
+        const uint32_t my_tiles = blockIdx.x < (uint32_t)num_tiles ? (num_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+        const uint32_t total = my_tiles * (uint32_t)k_tiles;   // k-tiles this CTA works through, in order
+        auto fetch_nth = [&](uint32_t j) { fetch((int)(blockIdx.x + (j / k_tiles) * gridDim.x), (int)(j % k_tiles)); };
+        bool ok = true;
+        if (group < total) fetch_nth(group);
+        for (uint32_t it = group; it < total && ok; it += kMoverGroups) {
+            const int s = it % kStages;
+            const uint32_t b = it % kSfBufs;
+            if (it >= (uint32_t)kSfBufs) {
+                const uint32_t prev = it - kSfBufs;
+                ok = mbar_wait(&empty[prev % kStages], (prev / kStages) & 1, s_abort, kTimeoutEmpty);
+                if (!ok) break;
+            }
+            tc_fence_after();
+            const uint32_t t_sfa = tmem_base + lane_base + tmem_sfa_col(b);
+            const uint32_t t_sfb = tmem_base + lane_base + tmem_sfb_col(b);
+            if constexpr ((CK_GEMM_PROBE & 1) != 0) {
+            } else if constexpr (kFp4) {
+                tc_st16(t_sfa, nxt_a);
+                tc_st16(t_sfb, nxt_b);
+                tc_st16(t_sfb + 16, nxt_b + 16);
+            } else {
+                tc_st4(t_sfa, nxt_a);
+                tc_st8(t_sfb, nxt_b);
+            }
+            tc_wait_st();
+            tc_fence_before();
+            // the registers are free again: start this group's next k-tile's loads
+            if (it + kMoverGroups < total) fetch_nth(it + kMoverGroups);
+            // sf_full tells the MMA issuer that this k-tile can go: scales in TMEM and operands in shared memory
+            ok = mbar_wait(&full[s], (it / kStages) & 1, s_abort, kTimeoutFull);
+            if (!ok) break;
+            if (lane == 0) mbar_arrive(&sf_full[b]);
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------ MMA issuer
@@ -320,21 +416,19 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
         uint32_t it = 0, local_tile = 0;
         bool ok = true, ready = false;
         for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local_tile) {
-            const int tn = tile / p.tiles_m;
-            const uint32_t buf = local_tile & 1, use = local_tile >> 1;
-            if (use > 0) ok = mbar_wait(&tmem_empty[buf], (use - 1) & 1, s_abort, kTimeoutTmemEmpty);
+            if (local_tile > 0) ok = mbar_wait(tmem_empty, (local_tile - 1) & 1, s_abort, kTimeoutTmemEmpty);
             if (!ok) break;
             tc_fence_after();
-            const uint32_t d_tmem = tmem_base + (buf ? kTmemAcc1 : kTmemAcc0);
-            // a 192-wide tile that starts mid scale-tile reads its scales 64 rows (two columns) in
-            const uint32_t sfb_shift = ((tn * BN) & 127) ? 2u : 0u;
+            const uint32_t d_tmem = tmem_base + kTmemAcc;
             for (int kt = 0; kt < k_tiles && ok; ++kt, ++it) {
                 const int s = it % kStages;
+                const uint32_t sb = it % kSfBufs;
 #if CK_GEMM_PROBE & 8
                 if (blockIdx.x == 0 && lane == 0 && it < 256) g_probe_ts[4 * it + 0] = clock64();
 #endif
-                // `ready` is an early look at this barrier taken while the previous k-tile was being issued
-                if (!__all_sync(0xffffffffu, ready)) ok = mbar_wait(&full[s], (it / kStages) & 1, s_abort, kTimeoutFull);
+                // The movers publish sf_full only after they saw full[s], so this one wait covers the operands
+                // too.  `ready` is an early look at it taken while the previous k-tile was being issued.
+                if (!__all_sync(0xffffffffu, ready)) ok = mbar_wait(&sf_full[sb], (it / kSfBufs) & 1, s_abort, kTimeoutSfFull);
                 if (!ok) break;
                 tc_fence_after();
 #if CK_GEMM_PROBE & 8
@@ -343,94 +437,132 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
                 // every descriptor of this stage is "stage start >> 4" plus a constant
                 const uint32_t st16 = smem16 + (uint32_t)s * (kStageBytes >> 4);
                 const uint32_t a_lo = st16 | kDescLoLbo1, b_lo = (st16 + (kSmemA >> 4)) | kDescLoLbo1;
-                const uint32_t sfa16 = st16 + ((kSmemA + kSmemB) >> 4), sfb16 = sfa16 + (kSmemSfA >> 4);
-                const uint32_t t_sfa = tmem_base + kTmemSfA, t_sfb = tmem_base + kTmemSfB;
-                // The tensor pipe runs the copies and MMAs of one thread in issue order, so the scale copies of a
-                // k-tile simply precede its MMAs (issuing them as one batch measured faster than interleaving).
-                auto issue = [&](int n_sf, int n_kb) {
+                const uint32_t t_sfa = tmem_base + tmem_sfa_col(sb), t_sfb = tmem_base + tmem_sfb_col(sb);
+                int n_kb = kKbPerTile;
+                if (kt + 1 == k_tiles && !tail_full) n_kb = (p.K - kt * kElemsPerTile + kMmaK - 1) / kMmaK;
 #pragma unroll
-                    for (int t = 0; t < kSfTilesPerStage; ++t) {
-                        if (t < n_sf) {
-                            tc_cp_sf(t_sfa + 4 * t, sfa16 + t * 32);
-                            tc_cp_sf(t_sfb + 8 * t, sfb16 + t * 32);
-                            tc_cp_sf(t_sfb + 8 * t + 4, sfb16 + (kSmemSfB >> 5) + t * 32);
-                        }
+                for (int kb = 0; kb < kKbPerTile; ++kb) {
+                    if (kb < n_kb) {
+                        // 32 bytes along K per MMA inside the 128-byte swizzled row
+                        uint32_t idesc = idesc_base, sfa = t_sfa, sfb = t_sfb;
+                        if (kFp4) { sfa += 4 * kb; sfb += 8 * kb; }
+                        else { idesc |= ((uint32_t)kb << 29) | ((uint32_t)kb << 4); }
+                        tc_mma<kFp4>(d_tmem, a_lo + 2 * kb, b_lo + 2 * kb, idesc, (kt > 0 || kb > 0) ? 1u : 0u, sfa, sfb);
                     }
-#pragma unroll
-                    for (int kb = 0; kb < kKbPerTile; ++kb) {
-                        if (kb < n_kb) {
-                            // 32 bytes along K per MMA inside the 128-byte swizzled row
-                            uint32_t idesc = idesc_base, sfa = t_sfa, sfb = t_sfb + sfb_shift;
-                            if (kFp4) { sfa += 4 * kb; sfb += 8 * kb; }
-                            else { idesc |= ((uint32_t)kb << 29) | ((uint32_t)kb << 4); }
-                            tc_mma<kFp4>(d_tmem, a_lo + 2 * kb, b_lo + 2 * kb, idesc, (kt > 0 || kb > 0) ? 1u : 0u, sfa, sfb);
-                        }
-                    }
-                };
-                if (kt + 1 < k_tiles || tail_full) {
-                    issue(kSfTilesPerStage, kKbPerTile);
-                } else {  // last, short k-tile
-                    issue(p.sf_tiles_k - kt * kSfTilesPerStage, (p.K - kt * kElemsPerTile + kMmaK - 1) / kMmaK);
+                    // the pipe is busy with these for a while: look at the next k-tile's barrier now
+                    if (kb == 1) ready = mbar_test_wait(&sf_full[(it + 1) % kSfBufs], ((it + 1) / kSfBufs) & 1);
                 }
-                // the pipe is busy with these for a while: look at the next k-tile's barrier now
-                ready = mbar_test_wait(&full[(it + 1) % kStages], ((it + 1) / kStages) & 1);
-                tc_commit(&empty[s]);                      // stage reusable once these MMAs have read it
-                if (kt == k_tiles - 1) tc_commit(&tmem_full[buf]);  // accumulator complete
+                tc_commit(&empty[s]);                      // stage and scale buffer reusable once these MMAs are done
+                if (kt == k_tiles - 1) tc_commit(tmem_full);  // accumulator complete
 #if CK_GEMM_PROBE & 8
                 if (blockIdx.x == 0 && lane == 0 && it < 256) g_probe_ts[4 * it + 2] = clock64();
 #endif
             }
         }
     } else {
-        // ------------------------------------------------------------ epilogue (warps 2..5)
-        const int q = warp & 3;  // TMEM lanes 32q .. 32q+31 belong to this warp
-        float* bias_row = s_bias + (warp - 2) * BN;
+        // ------------------------------------------------------------ epilogue (warps 2..9)
+        const int q = warp & 3;                        // TMEM lanes 32q .. 32q+31 belong to this warp
+        const int half = (warp - kFirstEpiWarp) >> 2;  // which 128 columns of the tile
+        uint8_t* stg = s_out + (warp - kFirstEpiWarp) * 4096;
         const float alpha = p.alpha ? __ldg(p.alpha) : 1.0f;
         uint32_t local_tile = 0;
         bool ok = true;
         for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local_tile) {
             const int tm = tile % p.tiles_m, tn = tile / p.tiles_m;
-            const uint32_t buf = local_tile & 1, use = local_tile >> 1;
-            const int n0 = tn * BN;
-            // bias row for this tile, private to the warp
-            for (int j = lane; j < BN; j += 32) {
+            const int n0 = tn * BN + half * 128;
+            // bias for these 128 columns: lane l keeps columns l, l + 32, l + 64, l + 96 and the others
+            // fetch them with shuffles
+            float bias_reg[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
                 float b = 0.0f;
-                const int n = n0 + j;
+                const int n = n0 + k * 32 + lane;
                 if (p.bias && n < p.N) {
                     if (p.bias_code == CK_F32) b = static_cast<const float*>(p.bias)[n];
                     else if (p.bias_code == CK_F16) b = __half2float(static_cast<const __half*>(p.bias)[n]);
                     else b = __bfloat162float(static_cast<const __nv_bfloat16*>(p.bias)[n]);
                 }
-                bias_row[j] = b;
+                bias_reg[k] = b;
             }
-            __syncwarp();
-            ok = mbar_wait(&tmem_full[buf], use & 1, s_abort, kTimeoutTmemFull);
+            auto bias_at = [&](int col) { return __shfl_sync(0xffffffffu, bias_reg[col >> 5], col & 31); };
+            ok = mbar_wait(tmem_full, local_tile & 1, s_abort, kTimeoutTmemFull);
             if (!ok) break;
             tc_fence_after();
-            const uint32_t acc = tmem_base + (buf ? kTmemAcc1 : kTmemAcc0) + ((uint32_t)(q * 32) << 16);
-            const int row = tm * BM + q * 32 + lane;
-#pragma unroll 1
-            for (int c = 0; c < BN / 32; ++c) {
-                uint32_t r[32];
-                tc_ld32(acc + c * 32, r);
-                tc_wait_ld();
-                float v[32];
+            const uint32_t acc = tmem_base + kTmemAcc + ((uint32_t)(q * 32) << 16) + (uint32_t)(half * 128);
+            const int row0 = tm * BM + q * 32;   // first of this warp's 32 rows
+            if (CK_GEMM_PROBE & 16) {
+                __syncwarp();
+                if (lane == 0) mbar_arrive(tmem_empty);
+                continue;
+            }
+            // Results leave through shared memory: lane i owns row i of the warp's 32 rows and writes 128 bytes of
+            // it per chunk (16-byte pieces placed with the 128-byte swizzle, which keeps the writes conflict-free);
+            // a TMA store then moves the 32 x 128-byte chunk to global memory in full lines and clips it at the
+            // matrix edges.  Lane 0 issues every store of this warp and waits for the previous one to have read
+            // the staging buffer before it is overwritten.
+            auto stage_chunk = [&](const uint32_t* w, int col) {
+                if (lane == 0) bulk_wait_read_all();
+                __syncwarp();
 #pragma unroll
-                for (int j = 0; j < 32; ++j) v[j] = fmaf(__uint_as_float(r[j]), alpha, bias_row[c * 32 + j]);
-                const int col = n0 + c * 32;
-                int valid = p.N - col;
-                if (valid > 32) valid = 32;
-                if (row < p.M && valid > 0) {
-                    const size_t off = (size_t)row * p.N + col;
-                    if (p.out_code == CK_BF16) store_row32(static_cast<__nv_bfloat16*>(p.out) + off, v, valid);
-                    else if (p.out_code == CK_F16) store_row32(static_cast<__half*>(p.out) + off, v, valid);
-                    else store_row32(static_cast<float*>(p.out) + off, v, valid);
+                for (int j = 0; j < 8; ++j)
+                    *reinterpret_cast<uint4*>(stg + lane * 128 + ((j ^ (lane & 7)) << 4)) =
+                        make_uint4(w[4 * j], w[4 * j + 1], w[4 * j + 2], w[4 * j + 3]);
+                fence_async_smem();
+                __syncwarp();
+                if (lane == 0 && col < p.N && !(CK_GEMM_PROBE & 32)) tma_store_2d(&map_out, stg, col, row0);
+            };
+            if (p.out_code != CK_F32) {
+                // 16-bit outputs: the first 64 columns wait in registers as packed pairs while the second 64 are
+                // read, so the accumulator goes back to the MMA issuer before any store is issued.
+                uint32_t packed[32];
+                uint32_t r[2][32];
+                if (!(CK_GEMM_PROBE & 64)) {
+                tc_ld32(acc, r[0]);
+                tc_ld32(acc + 32, r[1]);
+                tc_wait_ld();
+                }
+#pragma unroll
+                for (int j = 0; j < 64; j += 2) {
+                    const float a = fmaf(__uint_as_float(r[j >> 5][j & 31]), alpha, bias_at(j));
+                    const float b = fmaf(__uint_as_float(r[j >> 5][(j & 31) + 1]), alpha, bias_at(j + 1));
+                    packed[j >> 1] = p.out_code == CK_BF16 ? pack_pair<__nv_bfloat16>(a, b) : pack_pair<__half>(a, b);
+                }
+                if (!(CK_GEMM_PROBE & 64)) {
+                tc_ld32(acc + 64, r[0]);
+                tc_ld32(acc + 96, r[1]);
+                tc_wait_ld();
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(tmem_empty);
+                stage_chunk(packed, n0);
+#pragma unroll
+                for (int j = 0; j < 64; j += 2) {
+                    const float a = fmaf(__uint_as_float(r[j >> 5][j & 31]), alpha, bias_at(64 + j));
+                    const float b = fmaf(__uint_as_float(r[j >> 5][(j & 31) + 1]), alpha, bias_at(64 + j + 1));
+                    packed[j >> 1] = p.out_code == CK_BF16 ? pack_pair<__nv_bfloat16>(a, b) : pack_pair<__half>(a, b);
+                }
+                stage_chunk(packed, n0 + 64);
+            } else {
+                // fp32 output: 32 columns (128 bytes per row) at a time
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    uint32_t r[32];
+                    tc_ld32(acc + c * 32, r);
+                    tc_wait_ld();
+                    if (c == 3) {
+                        tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(tmem_empty);
+                    }
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(fmaf(__uint_as_float(r[j]), alpha, bias_at(c * 32 + j)));
+                    stage_chunk(r, n0 + c * 32);
                 }
             }
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&tmem_empty[buf]);
         }
+        if (lane == 0) bulk_wait_all();   // the staging buffer must outlive the stores that read it
+        __syncwarp();
     }
 
     tc_fence_before();
@@ -475,6 +607,22 @@ int make_operand_map(CUtensorMap* map, const void* base, int64_t rows, int64_t r
     return CK_OK;
 }
 
+// Output [rows, cols] of 2- or 4-byte elements, box = 128 bytes x 32 rows, 128-byte swizzle (the layout the
+// epilogue writes into its staging buffers).
+int make_output_map(CUtensorMap* map, void* base, int64_t rows, int64_t cols, int elem_bytes) {
+    EncodeFn enc = get_encode();
+    if (!enc) CK_FAIL(CK_ERR_UNSUPPORTED, "scaled_mm: cuTensorMapEncodeTiled is not available from the driver");
+    cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)(cols * elem_bytes)};
+    cuuint32_t box[2] = {(cuuint32_t)(128 / elem_bytes), 32u};
+    cuuint32_t estr[2] = {1u, 1u};
+    CUresult r = enc(map, elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_UINT16 : CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, base, dims,
+                     strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                     CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) CK_FAIL(CK_ERR_UNSUPPORTED, "scaled_mm: cuTensorMapEncodeTiled (output) failed with %d", (int)r);
+    return CK_OK;
+}
+
 int sm_count() {
     static int cached[64] = {};
     int dev = 0;
@@ -514,9 +662,10 @@ int launch_gemm(const void* a, const void* sfa, const void* b, const void* sfb, 
         if (dev >= 0 && dev < 64) attr_set[kFp4][dev] = true;
     }
 
-    CUtensorMap map_a, map_b;
+    CUtensorMap map_a, map_b, map_out;
     if (int rc = make_operand_map(&map_a, a, M, row_bytes, BM)) return rc;
     if (int rc = make_operand_map(&map_b, b, N, row_bytes, BN)) return rc;
+    if (int rc = make_output_map(&map_out, d, M, N, out_code == CK_F32 ? 4 : 2)) return rc;
 
     GemmParams p{};
     p.sfa = static_cast<const uint8_t*>(sfa);
@@ -534,7 +683,7 @@ int launch_gemm(const void* a, const void* sfa, const void* b, const void* sfb, 
     p.tiles_n = (int)ceil_div(N, BN);
     const int64_t tiles = (int64_t)p.tiles_m * p.tiles_n;
     const int grid = (int)(tiles < sm_count() ? tiles : sm_count());
-    gemm_blockscaled_kernel<kFp4><<<grid, kThreads, kSmemBytes, stream>>>(map_a, map_b, p);
+    gemm_blockscaled_kernel<kFp4><<<grid, kThreads, kSmemBytes, stream>>>(map_a, map_b, map_out, p);
     return launch_status(what);
 }
 
