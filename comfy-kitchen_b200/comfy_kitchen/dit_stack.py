@@ -1,0 +1,458 @@
+"""Synthetic Flux-like DiT stack on the quantized-linear path, with Megatron tensor parallelism.
+
+The reference ships kernels and tensor wrappers but no model; this module is the workload its
+NVFP4 path is aimed at (an MMDiT with double-stream and single-stream blocks), built only from
+the package's own operators so that one forward exercises every kernel of the path:
+
+    LayerNorm + AdaLN modulation -> NVFP4   adaln_quantize_nvfp4      (fused front end)
+    block-scaled GEMM, alpha and bias fused  scaled_mm_nvfp4
+    per-head RMSNorm of q and k              rmsnorm
+    rotary embedding of q and k              apply_rope
+    activation re-quantisation               quantize_nvfp4
+
+Attention itself is torch's scaled_dot_product_attention in bf16.
+
+Tensor parallelism (world size t, one process per GPU): attention heads and MLP columns are split
+across ranks.  The first GEMM of each half-block is column-parallel (no exchange), the second is
+row-parallel and ends in one all-reduce(sum) of the [tokens, hidden] partial result over the
+process group (NCCL on GPUs, gloo in the CPU tests).  A forward of the full model issues
+2 * n_double + n_single all-reduces (76 for 19 + 38 blocks).  Weights are quantised after slicing,
+with the per-tensor scale taken from the unsliced weight, so every rank's shard decodes to the
+same values as the corresponding part of the full weight.  K-shards are multiples of 64 elements
+and N-shards multiples of 128 rows for the configurations used (hidden 3072, t <= 8), which keeps
+whole 128x4 scale tiles on one rank.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass, field
+
+import torch
+import torch.nn.functional as F
+
+F4_MAX = 6.0
+E4M3_MAX = 448.0
+
+
+@dataclass
+class DiTConfig:
+    hidden: int = 3072
+    heads: int = 24
+    head_dim: int = 128
+    mlp_ratio: int = 4
+    n_double: int = 19
+    n_single: int = 38
+    txt_tokens: int = 512
+    img_grid: tuple[int, int] = (64, 64)
+    axes_dim: tuple[int, int, int] = (16, 56, 56)
+    theta: float = 10000.0
+    eps: float = 1e-6
+    seed: int = 0
+    weight_std: float = 0.02
+
+    @property
+    def img_tokens(self) -> int:
+        return self.img_grid[0] * self.img_grid[1]
+
+    @property
+    def tokens(self) -> int:
+        return self.txt_tokens + self.img_tokens
+
+    @property
+    def mlp_hidden(self) -> int:
+        return self.mlp_ratio * self.hidden
+
+    def validate(self, world: int) -> None:
+        assert self.hidden == self.heads * self.head_dim, "hidden must equal heads * head_dim"
+        assert sum(self.axes_dim) == self.head_dim, "rope axes must add up to head_dim"
+        assert self.heads % world == 0, f"{self.heads} heads do not split over {world} ranks"
+        assert self.mlp_hidden % world == 0
+        assert (self.hidden // world) % 64 == 0 and (self.mlp_hidden // world) % 64 == 0, \
+            "K-shards must be multiples of 64 elements (one scale tile)"
+
+
+class TensorParallel:
+    """Rank bookkeeping and the one collective the stack needs."""
+
+    def __init__(self, group=None):
+        import torch.distributed as dist
+
+        self._dist = dist
+        if dist.is_available() and dist.is_initialized():
+            self.group = group
+            self.rank = dist.get_rank(group)
+            self.world = dist.get_world_size(group)
+        else:
+            self.group, self.rank, self.world = None, 0, 1
+        self.all_reduce_calls = 0
+
+    def all_reduce_sum(self, t: torch.Tensor) -> torch.Tensor:
+        self.all_reduce_calls += 1
+        if self.world > 1:
+            self._dist.all_reduce(t, op=self._dist.ReduceOp.SUM, group=self.group)
+        return t
+
+    def all_reduce_max(self, t: torch.Tensor) -> torch.Tensor:
+        if self.world > 1:
+            self._dist.all_reduce(t, op=self._dist.ReduceOp.MAX, group=self.group)
+        return t
+
+
+def rope_freqs(cfg: DiTConfig, device, dtype=torch.float32) -> torch.Tensor:
+    """[1, 1, tokens, head_dim/2, 2, 2] rotation matrices [[cos, -sin], [sin, cos]].
+
+    Position ids: text tokens (0, 0, 0), image tokens (0, row, col) on the image grid; pair i of
+    axis a (axes_dim[a] / 2 pairs) turns by pos_a * theta^(-2i / axes_dim[a]).
+    """
+    gh, gw = cfg.img_grid
+    ids = torch.zeros(cfg.tokens, 3, dtype=torch.float64)
+    rows = torch.arange(gh, dtype=torch.float64).repeat_interleave(gw)
+    cols = torch.arange(gw, dtype=torch.float64).repeat(gh)
+    ids[cfg.txt_tokens:, 1] = rows
+    ids[cfg.txt_tokens:, 2] = cols
+    parts = []
+    for a, d in enumerate(cfg.axes_dim):
+        omega = cfg.theta ** (-torch.arange(0, d, 2, dtype=torch.float64) / d)
+        parts.append(ids[:, a:a + 1] * omega[None, :])
+    ang = torch.cat(parts, dim=1)  # [tokens, head_dim / 2]
+    cos, sin = ang.cos(), ang.sin()
+    m = torch.stack([torch.stack([cos, -sin], dim=-1), torch.stack([sin, cos], dim=-1)], dim=-2)
+    return m.to(dtype)[None, None].contiguous().to(device)
+
+
+class QuantLinear:
+    """One NVFP4 weight shard: packed codes [N, K/2], tiled E4M3 block scales, fp32 tensor scale."""
+
+    def __init__(self, ops, w: torch.Tensor, tensor_scale: torch.Tensor, bias: torch.Tensor | None):
+        self.ops = ops
+        self.n, self.k = w.shape
+        self.tensor_scale = tensor_scale.float().reshape(())
+        self.qdata, self.block_scales = ops.quantize_nvfp4(w.contiguous(), self.tensor_scale)
+        self.bias = bias
+
+    def __call__(self, qx: torch.Tensor, sx: torch.Tensor, act_scale: torch.Tensor) -> torch.Tensor:
+        alpha = (act_scale * self.tensor_scale).reshape(1)
+        return self.ops.scaled_mm_nvfp4(qx, self.qdata, act_scale, self.tensor_scale, sx, self.block_scales,
+                                        bias=self.bias, out_dtype=torch.bfloat16, alpha=alpha)
+
+
+def _weight_scale(w: torch.Tensor) -> torch.Tensor:
+    return (w.float().abs().max() / (F4_MAX * E4M3_MAX)).reshape(())
+
+
+@dataclass
+class _Sites:
+    """Per-tensor activation scales, one per quantisation site, keyed by name."""
+    static: dict = field(default_factory=dict)
+    observed: dict = field(default_factory=dict)
+    recording: bool = False
+
+
+class DiTStack:
+    """The stack's weights for one rank and its forward pass.
+
+    ops: a module or object with the package's operator names (default: the CUDA backend).
+    """
+
+    def __init__(self, cfg: DiTConfig, device, tp: TensorParallel | None = None, ops=None):
+        if ops is None:
+            from comfy_kitchen.backends import cuda as ops  # raises if the native library is missing
+        self.cfg, self.ops, self.device = cfg, ops, torch.device(device)
+        self.tp = tp or TensorParallel()
+        cfg.validate(self.tp.world)
+        self.sites = _Sites()
+        self.heads_local = cfg.heads // self.tp.world
+        self.freqs = rope_freqs(cfg, self.device)
+        self.double = [self._make_double(i) for i in range(cfg.n_double)]
+        self.single = [self._make_single(i) for i in range(cfg.n_single)]
+
+    # ------------------------------------------------------------------ weights
+
+    def _randn(self, shape, layer: int, name: str, std: float) -> torch.Tensor:
+        g = torch.Generator(device=self.device)
+        g.manual_seed((self.cfg.seed * 1_000_003 + layer * 101 + sum(map(ord, name))) & 0x7FFFFFFF)
+        return (std * torch.randn(shape, generator=g, device=self.device, dtype=torch.float32)).bfloat16()
+
+    def _head_rows(self, per_part_rows: int) -> torch.Tensor:
+        """Row indices of this rank's heads inside one of q / k / v (each heads * head_dim rows)."""
+        hd = self.cfg.head_dim
+        lo = self.tp.rank * self.heads_local * hd
+        return torch.arange(lo, lo + self.heads_local * hd, device=self.device)
+
+    def _qkv_rows(self) -> torch.Tensor:
+        h = self.cfg.hidden
+        r = self._head_rows(h)
+        return torch.cat([r, r + h, r + 2 * h])
+
+    def _mlp_slice(self) -> slice:
+        n = self.cfg.mlp_hidden // self.tp.world
+        return slice(self.tp.rank * n, (self.tp.rank + 1) * n)
+
+    def _linear(self, w_full: torch.Tensor, rows=None, cols=None, bias_full=None, row_parallel=False) -> QuantLinear:
+        ts = _weight_scale(w_full)
+        w = w_full
+        if rows is not None:
+            w = w[rows]
+        if cols is not None:
+            w = w[:, cols]
+        bias = None
+        if bias_full is not None:
+            if row_parallel:  # the partial results are summed: the bias goes in once
+                bias = bias_full if self.tp.rank == 0 else None
+            else:
+                bias = bias_full[rows] if rows is not None else bias_full
+        return QuantLinear(self.ops, w, ts, None if bias is None else bias.float().contiguous())
+
+    def _make_double(self, i: int) -> dict:
+        c, blk = self.cfg, {}
+        h, hd = c.hidden, c.head_dim
+        attn_cols = self._head_rows(h)
+        for s in ("img", "txt"):
+            L = 1000 + 2 * i + (s == "txt")
+            p = {}
+            p["mod_w"] = self._randn((6 * h, h), L, "mod_w", c.weight_std)
+            p["mod_b"] = self._randn((6 * h,), L, "mod_b", c.weight_std)
+            p["qkv"] = self._linear(self._randn((3 * h, h), L, "qkv", c.weight_std), rows=self._qkv_rows(),
+                                    bias_full=self._randn((3 * h,), L, "qkv_b", c.weight_std))
+            p["q_norm"] = torch.ones(hd, device=self.device, dtype=torch.bfloat16)
+            p["k_norm"] = torch.ones(hd, device=self.device, dtype=torch.bfloat16)
+            p["proj"] = self._linear(self._randn((h, h), L, "proj", c.weight_std), cols=attn_cols,
+                                     bias_full=self._randn((h,), L, "proj_b", c.weight_std), row_parallel=True)
+            ms = self._mlp_slice()
+            mrows = torch.arange(ms.start, ms.stop, device=self.device)
+            p["up"] = self._linear(self._randn((c.mlp_hidden, h), L, "up", c.weight_std), rows=mrows,
+                                   bias_full=self._randn((c.mlp_hidden,), L, "up_b", c.weight_std))
+            p["down"] = self._linear(self._randn((h, c.mlp_hidden), L, "down", c.weight_std), cols=mrows,
+                                     bias_full=self._randn((h,), L, "down_b", c.weight_std), row_parallel=True)
+            blk[s] = p
+        return blk
+
+    def _make_single(self, i: int) -> dict:
+        c = self.cfg
+        h = c.hidden
+        L = 5000 + i
+        ms = self._mlp_slice()
+        mrows = torch.arange(ms.start, ms.stop, device=self.device)
+        p = {}
+        p["mod_w"] = self._randn((3 * h, h), L, "mod_w", c.weight_std)
+        p["mod_b"] = self._randn((3 * h,), L, "mod_b", c.weight_std)
+        # linear1 rows: [q | k | v | mlp]; this rank keeps its heads of q, k, v and its slice of the MLP
+        rows1 = torch.cat([self._qkv_rows(), 3 * h + mrows])
+        p["linear1"] = self._linear(self._randn((3 * h + c.mlp_hidden, h), L, "linear1", c.weight_std), rows=rows1,
+                                    bias_full=self._randn((3 * h + c.mlp_hidden,), L, "linear1_b", c.weight_std))
+        p["q_norm"] = torch.ones(c.head_dim, device=self.device, dtype=torch.bfloat16)
+        p["k_norm"] = torch.ones(c.head_dim, device=self.device, dtype=torch.bfloat16)
+        # linear2 columns: [attention output | MLP activations], sliced the same way
+        cols2 = torch.cat([self._head_rows(h), h + mrows])
+        p["linear2"] = self._linear(self._randn((h, h + c.mlp_hidden), L, "linear2", c.weight_std), cols=cols2,
+                                    bias_full=self._randn((h,), L, "linear2_b", c.weight_std), row_parallel=True)
+        return p
+
+    # ------------------------------------------------------------------ activation scales
+
+    def _act_scale(self, site: str, x: torch.Tensor | None = None, amax: torch.Tensor | None = None) -> torch.Tensor:
+        """Static scale when calibrated; otherwise amax / (6 * 448) of this call's tensor."""
+        st = self.sites
+        if not st.recording and site in st.static:
+            return st.static[site]
+        if amax is None:
+            amax = x.float().abs().max()
+        amax = amax.reshape(())
+        if st.recording:
+            prev = st.observed.get(site)
+            st.observed[site] = amax if prev is None else torch.maximum(prev, amax)
+        return torch.clamp(amax, min=1e-12) / (F4_MAX * E4M3_MAX)
+
+    @torch.no_grad()
+    def calibrate(self, img: torch.Tensor, txt: torch.Tensor, vec: torch.Tensor, margin: float = 1.0) -> None:
+        """One forward with per-call scales; the observed maxima (over ranks too) become static scales."""
+        self.sites.recording, self.sites.observed = True, {}
+        try:
+            self.forward(img, txt, vec)
+        finally:
+            self.sites.recording = False
+        names = sorted(self.sites.observed)
+        if names:
+            packed = torch.stack([self.sites.observed[n].float() for n in names])
+            self.tp.all_reduce_max(packed)
+            for n, a in zip(names, packed):
+                self.sites.static[n] = (torch.clamp(a * margin, min=1e-12) / (F4_MAX * E4M3_MAX)).reshape(())
+
+    # ------------------------------------------------------------------ pieces of the forward
+
+    def _modulation(self, p: dict, vec: torch.Tensor, n: int):
+        m = F.linear(F.silu(vec), p["mod_w"], p["mod_b"])  # [1, n * hidden], replicated on every rank
+        return m.chunk(n, dim=-1)
+
+    def _norm_quant(self, site: str, x: torch.Tensor, scale: torch.Tensor, shift: torch.Tensor):
+        """LayerNorm + modulation + NVFP4 quantise in one kernel.  Without a static scale the maximum comes
+        from the standalone AdaLN kernel first (calibration only)."""
+        if self.sites.recording or site not in self.sites.static:
+            y = self.ops.adaln(x[None], scale, shift, self.cfg.eps)
+            g = self._act_scale(site, y)
+        else:
+            g = self.sites.static[site]
+        qx, sx = self.ops.adaln_quantize_nvfp4(x[None], scale, shift, g, self.cfg.eps)
+        return qx, sx, g
+
+    def _quant(self, site: str, x: torch.Tensor):
+        g = self._act_scale(site, x)
+        qx, sx = self.ops.quantize_nvfp4(x.contiguous(), g)
+        return qx, sx, g
+
+    def _attention(self, qkv: torch.Tensor, q_w: torch.Tensor, k_w: torch.Tensor) -> torch.Tensor:
+        """qkv [tokens, 3 * heads_local * head_dim] -> attention output [tokens, heads_local * head_dim]."""
+        c, hl = self.cfg, self.heads_local
+        t = qkv.shape[0]
+        q, k, v = qkv.view(t, 3, hl, c.head_dim).unbind(1)
+        q = self.ops.rmsnorm(q.contiguous(), q_w, c.eps)
+        k = self.ops.rmsnorm(k.contiguous(), k_w, c.eps)
+        q = q.permute(1, 0, 2)[None]  # [1, heads, tokens, head_dim]
+        k = k.permute(1, 0, 2)[None]
+        q, k = self.ops.apply_rope(q, k, self.freqs[:, :, :t])
+        o = F.scaled_dot_product_attention(q, k, v.permute(1, 0, 2)[None])
+        return o[0].permute(1, 0, 2).reshape(t, hl * c.head_dim)
+
+    def _double_block(self, i: int, img: torch.Tensor, txt: torch.Tensor, vec: torch.Tensor):
+        blk, tt = self.double[i], self.cfg.txt_tokens
+        mods = {s: self._modulation(blk[s], vec, 6) for s in ("img", "txt")}
+        xs = {"img": img, "txt": txt}
+        qkv = {}
+        for s in ("txt", "img"):
+            shift1, scale1 = mods[s][0], mods[s][1]
+            qx, sx, g = self._norm_quant(f"d{i}.{s}.attn_in", xs[s], scale1, shift1)
+            qkv[s] = blk[s]["qkv"](qx, sx, g)
+        # joint attention over text then image tokens; q/k norms differ per stream, so normalise before joining
+        c, hl = self.cfg, self.heads_local
+        parts = {}
+        for s in ("txt", "img"):
+            t = qkv[s].shape[0]
+            q, k, v = qkv[s].view(t, 3, hl, c.head_dim).unbind(1)
+            parts[s] = (self.ops.rmsnorm(q.contiguous(), blk[s]["q_norm"], c.eps),
+                        self.ops.rmsnorm(k.contiguous(), blk[s]["k_norm"], c.eps), v)
+        q = torch.cat([parts["txt"][0], parts["img"][0]]).permute(1, 0, 2)[None]
+        k = torch.cat([parts["txt"][1], parts["img"][1]]).permute(1, 0, 2)[None]
+        v = torch.cat([parts["txt"][2], parts["img"][2]]).permute(1, 0, 2)[None]
+        q, k = self.ops.apply_rope(q, k, self.freqs)
+        o = F.scaled_dot_product_attention(q, k, v)[0].permute(1, 0, 2).reshape(c.tokens, hl * c.head_dim)
+        attn = {"txt": o[:tt], "img": o[tt:]}
+        # row-parallel projections of both streams, one all-reduce for the pair
+        ys = []
+        for s in ("txt", "img"):
+            qx, sx, g = self._quant(f"d{i}.{s}.attn_out", attn[s])
+            ys.append(blk[s]["proj"](qx, sx, g))
+        y = self.tp.all_reduce_sum(torch.cat(ys))
+        for s, ysl in (("txt", y[:tt]), ("img", y[tt:])):
+            xs[s] = torch.addcmul(xs[s], mods[s][2], ysl)
+        # MLP
+        ys = []
+        for s in ("txt", "img"):
+            shift2, scale2 = mods[s][3], mods[s][4]
+            qx, sx, g = self._norm_quant(f"d{i}.{s}.mlp_in", xs[s], scale2, shift2)
+            hmid = F.gelu(blk[s]["up"](qx, sx, g), approximate="tanh")
+            qx, sx, g = self._quant(f"d{i}.{s}.mlp_mid", hmid)
+            ys.append(blk[s]["down"](qx, sx, g))
+        y = self.tp.all_reduce_sum(torch.cat(ys))
+        for s, ysl in (("txt", y[:tt]), ("img", y[tt:])):
+            xs[s] = torch.addcmul(xs[s], mods[s][5], ysl)
+        return xs["img"], xs["txt"]
+
+    def _single_block(self, i: int, x: torch.Tensor, vec: torch.Tensor) -> torch.Tensor:
+        p, c, hl = self.single[i], self.cfg, self.heads_local
+        shift, scale, gate = self._modulation(p, vec, 3)
+        qx, sx, g = self._norm_quant(f"s{i}.in", x, scale, shift)
+        h1 = p["linear1"](qx, sx, g)
+        n_qkv = 3 * hl * c.head_dim
+        attn = self._attention(h1[:, :n_qkv], p["q_norm"], p["k_norm"])
+        mid = torch.cat([attn, F.gelu(h1[:, n_qkv:], approximate="tanh")], dim=1)
+        qx, sx, g = self._quant(f"s{i}.mid", mid)
+        y = self.tp.all_reduce_sum(p["linear2"](qx, sx, g))
+        return torch.addcmul(x, gate, y)
+
+    @torch.no_grad()
+    def forward(self, img: torch.Tensor, txt: torch.Tensor, vec: torch.Tensor) -> torch.Tensor:
+        """img [img_tokens, hidden], txt [txt_tokens, hidden], vec [1, hidden] (bf16) -> [tokens, hidden],
+        text tokens first.  Every rank receives the same inputs and returns the same (replicated) output."""
+        for i in range(self.cfg.n_double):
+            img, txt = self._double_block(i, img, txt, vec)
+        x = torch.cat([txt, img])
+        for i in range(self.cfg.n_single):
+            x = self._single_block(i, x, vec)
+        return x
+
+    __call__ = forward
+
+    def expected_all_reduces(self) -> int:
+        return 2 * self.cfg.n_double + self.cfg.n_single
+
+
+def gemm_flops_per_forward(cfg: DiTConfig) -> float:
+    """Multiply-add work of the quantized linears of one forward, in flop (2 per multiply-add)."""
+    h, m = cfg.hidden, cfg.mlp_hidden
+    per_token_double = 2 * (3 * h * h + h * h + 2 * h * m)      # qkv, proj, up, down per stream token
+    per_token_single = 2 * ((3 * h + m) * h + (h + m) * h)       # linear1, linear2
+    return float(cfg.tokens) * (cfg.n_double * per_token_double + cfg.n_single * per_token_single)
+
+
+def attention_flops_per_forward(cfg: DiTConfig) -> float:
+    return 4.0 * cfg.tokens * cfg.tokens * cfg.hidden * (cfg.n_double + cfg.n_single)
+
+
+def reference_forward(stack: DiTStack, img: torch.Tensor, txt: torch.Tensor, vec: torch.Tensor, dequant) -> torch.Tensor:
+    """The same graph with every quantized linear replaced by bf16 F.linear on the dequantized weight shard
+    (dequant(qdata, tensor_scale, block_scales) -> bf16 [N, K]) and unquantised activations.  World size 1 only;
+    the tests use it to bound the quantisation error of the stack."""
+    assert stack.tp.world == 1
+    c, ops = stack.cfg, stack.ops
+
+    def lin(q: QuantLinear, x):
+        w = dequant(q.qdata, q.tensor_scale, q.block_scales)
+        return F.linear(x, w, None if q.bias is None else q.bias.to(x.dtype))
+
+    def ln_mod(x, scale, shift):
+        return (F.layer_norm(x.float(), (c.hidden,), eps=c.eps) * (1 + scale.float()) + shift.float()).to(x.dtype)
+
+    def heads(t3):
+        t = t3.shape[0]
+        return t3.view(t, 3, c.heads, c.head_dim).unbind(1)
+
+    def rope(x):  # x [1, heads, tokens, head_dim]
+        f = stack.freqs[:, :, :x.shape[2]].to(torch.float32)
+        xp = x.float().reshape(*x.shape[:-1], -1, 1, 2)
+        return (f[..., 0] * xp[..., 0] + f[..., 1] * xp[..., 1]).reshape(x.shape).to(x.dtype)
+
+    def rms(x, w):
+        xf = x.float()
+        return (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + c.eps) * w.float()).to(x.dtype)
+
+    def attend(q, k, v):
+        q = rope(q.permute(1, 0, 2)[None])
+        k = rope(k.permute(1, 0, 2)[None])
+        o = F.scaled_dot_product_attention(q, k, v.permute(1, 0, 2)[None])
+        return o[0].permute(1, 0, 2).reshape(q.shape[2], c.hidden)
+
+    tt = c.txt_tokens
+    for i in range(c.n_double):
+        blk = stack.double[i]
+        xs = {"img": img, "txt": txt}
+        mods = {s: stack._modulation(blk[s], vec, 6) for s in xs}
+        qs, ks, vs = [], [], []
+        for s in ("txt", "img"):
+            q, k, v = heads(lin(blk[s]["qkv"], ln_mod(xs[s], mods[s][1], mods[s][0])))
+            qs.append(rms(q, blk[s]["q_norm"])); ks.append(rms(k, blk[s]["k_norm"])); vs.append(v)
+        o = attend(torch.cat(qs), torch.cat(ks), torch.cat(vs))
+        for s, osl in (("txt", o[:tt]), ("img", o[tt:])):
+            xs[s] = torch.addcmul(xs[s], mods[s][2], lin(blk[s]["proj"], osl))
+            hmid = F.gelu(lin(blk[s]["up"], ln_mod(xs[s], mods[s][4], mods[s][3])), approximate="tanh")
+            xs[s] = torch.addcmul(xs[s], mods[s][5], lin(blk[s]["down"], hmid))
+        img, txt = xs["img"], xs["txt"]
+    x = torch.cat([txt, img])
+    for i in range(c.n_single):
+        p = stack.single[i]
+        shift, scale, gate = stack._modulation(p, vec, 3)
+        h1 = lin(p["linear1"], ln_mod(x, scale, shift))
+        q, k, v = heads(h1[:, :3 * c.hidden].contiguous())
+        o = attend(rms(q, p["q_norm"]), rms(k, p["k_norm"]), v)
+        mid = torch.cat([o, F.gelu(h1[:, 3 * c.hidden:], approximate="tanh")], dim=1)
+        x = torch.addcmul(x, gate, lin(p["linear2"], mid))
+    return x

@@ -5,38 +5,44 @@
 //
 // A is [M,K] and W is [N,K], both K-contiguous ("TN"); the scale factors arrive in
 // the 128x4 tiled layout written by the quantizers (ck_common.cuh: sf_offset), one
-// 512-byte tile per 128 rows x 4 scale columns — exactly the 32-lane x 128-bit
-// unit that tcgen05.cp moves from shared memory into TMEM.  Semantics follow
+// 512-byte tile per 128 rows x 4 scale columns.  Semantics follow
 // comfy_kitchen/backends/eager/quantization.py:224-248 (NVFP4) and :369-404
 // (MXFP8); the reference's CUDA backend forwards NVFP4 to a library GEMM
 // (backends/cuda/ops/cublas_gemm_nvfp4.cu:64-340) and has no MXFP8 kernel.
 //
-// Kernel structure (one persistent CTA per SM, 448 threads, tile 128 x 256):
-//   warp 0       TMA producer: per k-tile one 128x128B box of A, one 256x128B box
-//                of W (both SWIZZLE_128B) and the scale tiles (plain bulk copies)
-//                into a 4-stage shared-memory ring, completion on mbarriers.
-//   warps 10-13  scale movers: shared memory -> registers -> TMEM (tcgen05.st), one
+// Kernel structure: persistent clusters of two CTAs (one per SM of a pair), 704
+// threads each.  A pair works on a 256 x 256 output tile with tcgen05.mma
+// .cta_group::2: CTA r of the pair holds rows 128r..128r+127 of the A tile, rows
+// 128r..128r+127 of the W tile (i.e. half of N) and, in TMEM, the 128 x 256 fp32
+// accumulator of its own rows.  Per CTA:
+//   warp 0       TMA producer: per k-tile one 128x128B box of A, one 128x128B box of
+//                W (both SWIZZLE_128B) and the scale tiles (its A rows' tile, both W
+//                tiles; plain bulk copies) into a 5-stage shared-memory ring.
+//   warps 18-21  scale movers: shared memory -> registers -> TMEM (tcgen05.st), one
 //                warp per 32-lane quarter of TMEM, into a ring of three scale
-//                buffers.  tcgen05.cp could do this move too, but it queues on the
-//                tensor pipe in front of the MMAs (~22 clocks per 512-byte tile
-//                measured); the register path runs beside the MMAs instead.
-//   warp 1       MMA issuer: four tcgen05.mma.kind::{mxf4nvf4,mxf8f6f4}.block_scale
-//                per k-tile (128x256xK64 for FP4, xK32 for FP8), accumulating in
-//                TMEM; tcgen05.commit releases the stage and its scale buffer and,
-//                per tile, publishes the accumulator.
-//   warps 2-9    epilogue: each warp reads its 32 TMEM lanes x 128 columns of the
-//                fp32 accumulator into registers (tcgen05.ld), hands the accumulator
-//                back, then applies alpha and bias, converts and stores, which
-//                overlaps the next tile's main loop.
-// Why 256 columns: measured on B200, one block-scaled MMA with M = 128 occupies the
-// issuing thread ~140 clocks whether N is 64, 128, 192 or 256, so only N = 256
-// reaches the tensor cores' rate.  The 256-column accumulator leaves room for the
-// scale ring (A: 16 columns, W: 32 columns per k-tile, three buffers) but not for a
-// second accumulator, hence the register-buffered epilogue: the accumulator is
-// busy for a few hundred clocks per tile instead of a whole epilogue.
+//                buffers; they tell the leader CTA's MMA issuer when a k-tile's
+//                scales (and, transitively, its operands) are in place.
+//   warp 1       in the leader CTA (rank 0) the MMA issuer: four tcgen05.mma
+//                .kind::{mxf4nvf4,mxf8f6f4}.block_scale per k-tile (256x256xK64 for
+//                FP4, xK32 for FP8); tcgen05.commit (multicast to both CTAs) releases
+//                the stage and its scale buffer and, per tile, publishes the
+//                accumulator.  In both CTAs this warp allocates and frees TMEM.
+//   warps 2-17   epilogue: each warp reads its 32 TMEM lanes x 64 columns into
+//                registers, hands the accumulator back, then applies alpha and bias,
+//                converts and writes through a swizzled staging buffer with TMA
+//                stores, overlapping the next tile's main loop.
+// Why this shape: measured on B200, one block-scaled MMA with 128 rows per CTA keeps
+// the issuing thread ~140 clocks whether N is 64 or 256, so only N = 256 reaches the
+// tensor cores' rate; with one CTA per tile that costs 96 KB of shared-memory traffic
+// per k-tile, and pairing the CTAs halves the W traffic of each SM.  The 256-column
+// accumulator leaves room for the scale ring (A: 16 columns, W: 32 columns per
+// k-tile, three buffers) but not for a second accumulator, hence the
+// register-buffered epilogue.  (tcgen05.cp could move the scales too, but it queues
+// on the tensor pipe in front of the MMAs: ~22 clocks per 512-byte tile measured.)
 //
-// Every wait in this file is bounded: on expiry the CTA records a status word,
-// stops issuing work, drains its own copies and frees its TMEM before returning.
+// Every wait on an mbarrier in this file is bounded: on expiry the CTA records a
+// status word, stops issuing work, drains its own copies and frees its TMEM before
+// returning.
 #include <cuda.h>
 #include <cudaTypedefs.h>
 
@@ -47,24 +53,26 @@
 namespace ck {
 namespace {
 
-constexpr int BM = 128;
-constexpr int BN = 256;
+constexpr int BM = 128;            // rows per CTA (256 per pair)
+constexpr int BN = 256;            // columns per pair tile; each CTA stages 128 of the W rows
 #ifndef CK_GEMM_STAGES
-#define CK_GEMM_STAGES 4
+#define CK_GEMM_STAGES 5
 #endif
 constexpr int kStages = CK_GEMM_STAGES;
-constexpr int kFirstEpiWarp = 2, kEpiWarps = 8;   // two warps per TMEM lane quarter, 128 columns each
+constexpr int kFirstEpiWarp = 2, kEpiWarps = 16;  // four warps per TMEM lane quarter, 64 columns each
 constexpr int kFirstMoverWarp = kFirstEpiWarp + kEpiWarps;
-constexpr int kMoverGroups = 2;   // groups of four warps (one per TMEM lane quarter) taking k-tiles in turn
-constexpr int kThreads = 32 * (kFirstMoverWarp + 4 * kMoverGroups);
+constexpr int kThreads = 32 * (kFirstMoverWarp + 4);
 constexpr int kSfBufs = 3;
 constexpr int kKbPerTile = 4;  // MMAs per k-tile
 
 constexpr int kSmemA = BM * 128;            // 16 KB
-constexpr int kSmemB = BN * 128;            // 32 KB
-constexpr int kStageBytes = kSmemA + kSmemB;   // 48 KB
-constexpr int kSmemOut = kEpiWarps * 4096;   // per-epilogue-warp staging: 32 rows x 128 bytes, 128-byte swizzle
+constexpr int kSmemB = (BN / 2) * 128;      // 16 KB
+constexpr int kSmemSfA = 4 * 512;           // up to four 512-byte tiles (NVFP4) for this CTA's 128 rows
+constexpr int kSmemSfB = 2 * 4 * 512;       // two row tiles x four: all 256 columns
+constexpr int kStageBytes = kSmemA + kSmemB + kSmemSfA + kSmemSfB;   // 38 KB
+constexpr int kSmemOut = kEpiWarps * 2048;   // per-epilogue-warp staging: 32 rows x 64 bytes, 64-byte swizzle
 constexpr int kSmemBytes = kStages * kStageBytes + kSmemOut + 256 /*barriers*/ + 1024 /*alignment slack*/;
+static_assert(kStageBytes % 1024 == 0, "operand tiles need 1024-byte alignment");
 static_assert(kSmemBytes <= 232448, "exceeds the 227 KB of shared memory a CTA can have");
 
 constexpr uint32_t kTmemCols = 512;
@@ -74,21 +82,35 @@ __device__ __forceinline__ uint32_t tmem_sfa_col(uint32_t b) { return 256u + 48u
 __device__ __forceinline__ uint32_t tmem_sfb_col(uint32_t b) { return 272u + 48u * b; }
 
 #ifndef CK_GEMM_PROBE
-#define CK_GEMM_PROBE 0   // timing experiments only: 1 = no scale moves, 2 = no TMA payload, 4 = no MMA, 8 = timestamps, 16 = no epilogue work
+#define CK_GEMM_PROBE 0   // timing experiments only: 1 = no scale moves, 8 = timestamps, 16 = no epilogue work
 #endif
 
 constexpr uint32_t kSpinLimit = 1u << 22;   // polls of mbarrier.try_wait before giving up (a fraction of a second)
 
-__device__ int g_gemm_status = 0;
+__device__ int g_gemm_status = 0;           // 0 ok; otherwise (code << 16 | CTA) of the first failure
 #if CK_GEMM_PROBE & 8
-__device__ long long g_probe_ts[4 * 256];   // MMA warp of CTA 0, per k-tile: before wait, after wait, after issue
-#endif           // 0 ok; otherwise (code << 16 | detail) of the first failure
+__device__ long long g_probe_ts[5 * 4 * 256];   // pair 0, per role and k-tile: timestamps (role 0 MMA, 1/2 movers, 3/4 producers of CTA 0/1)
+#define CK_TS(role, it, k) do { if (pair == 0 && lane == 0 && (it) < 256) g_probe_ts[(role) * 1024 + 4 * (it) + (k)] = clock64(); } while (0)
+#else
+#define CK_TS(role, it, k) do { } while (0)
+#endif
 
 enum : int { kTimeoutFull = 1, kTimeoutEmpty = 2, kTimeoutTmemFull = 3, kTimeoutTmemEmpty = 4, kTimeoutSfFull = 5 };
 
 // ------------------------------------------------------------------ PTX wrappers
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+// All threads of both CTAs.
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
 
 __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
@@ -99,6 +121,16 @@ __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
+// Arrive on the same barrier in CTA `rank` of the cluster (which may be this CTA).
+__device__ __forceinline__ void mbar_arrive_cluster(uint64_t* bar, uint32_t rank) {
+    asm volatile(
+        "{ .reg .b32 ra; mapa.shared::cluster.u32 ra, %0, %1;\n"
+        "mbarrier.arrive.shared::cluster.b64 _, [ra]; }"
+        ::"r"(smem_u32(bar)), "r"(rank) : "memory");
+}
+// Plain (CTA-scope) waits also serve the barriers that the peer CTA's warps arrive on: what those arrivals
+// publish is TMEM content and TMA-written shared memory, ordered by the tcgen05 fences around them, not
+// generic-proxy data.  (A cluster-scope release/acquire pair here measured ~1000 clocks per arrival.)
 __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
     uint32_t ok;
     asm volatile(
@@ -143,6 +175,11 @@ __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, i
         "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
         ::"r"(smem_u32(dst)), "l"(map), "r"(c0), "r"(c1), "r"(smem_u32(bar)) : "memory");
 }
+__device__ __forceinline__ void bulk_load(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+        ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
+}
 // Shared -> global tile store (clipped at the tensor's edges), tracked by the issuing thread's bulk groups.
 __device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, const void* src, int c0, int c1) {
     asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
@@ -158,9 +195,12 @@ __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::
 
 // The tcgen05 issue wrappers below are called by all 32 lanes of the issuing warp with identical
 // arguments; one elected lane executes the instruction.
-__device__ __forceinline__ void tc_commit(uint64_t* bar) {
+// Arrives (once the MMAs issued so far have completed) on the barrier at this shared-memory offset in
+// both CTAs of the pair.
+__device__ __forceinline__ void tc_commit_pair(uint64_t* bar) {
     if (elect_one())
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                 ::"r"(smem_u32(bar)), "h"((uint16_t)3) : "memory");
 }
 // Shared-memory descriptors are built from a 32-bit low word (start address >> 4, plus the
 // leading-offset field for the swizzled form) and a constant high word:
@@ -172,19 +212,18 @@ constexpr uint32_t kDescLoLbo1 = 1u << 16;
 template <bool kFp4>
 __device__ __forceinline__ void tc_mma(uint32_t d, uint32_t a_lo, uint32_t b_lo, uint32_t idesc, uint32_t accumulate,
                                        uint32_t sfa, uint32_t sfb) {
-    if (CK_GEMM_PROBE & 4) return;
     if (!elect_one()) return;
     if (kFp4) {
         asm volatile(
             "{ .reg .pred p; .reg .b64 da, db; setp.ne.b32 p, %4, 0;\n"
             "mov.b64 da, {%1, %7}; mov.b64 db, {%2, %7};\n"
-            "tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.block16 [%0], da, db, %3, [%5], [%6], p; }"
+            "tcgen05.mma.cta_group::2.kind::mxf4nvf4.block_scale.block16 [%0], da, db, %3, [%5], [%6], p; }"
             ::"r"(d), "r"(a_lo), "r"(b_lo), "r"(idesc), "r"(accumulate), "r"(sfa), "r"(sfb), "n"(kDescHiOperand) : "memory");
     } else {
         asm volatile(
             "{ .reg .pred p; .reg .b64 da, db; setp.ne.b32 p, %4, 0;\n"
             "mov.b64 da, {%1, %7}; mov.b64 db, {%2, %7};\n"
-            "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale [%0], da, db, %3, [%5], [%6], p; }"
+            "tcgen05.mma.cta_group::2.kind::mxf8f6f4.block_scale [%0], da, db, %3, [%5], [%6], p; }"
             ::"r"(d), "r"(a_lo), "r"(b_lo), "r"(idesc), "r"(accumulate), "r"(sfa), "r"(sfb), "n"(kDescHiOperand) : "memory");
     }
 }
@@ -221,14 +260,14 @@ __device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sy
 struct GemmParams {
     const uint8_t* sfa;
     const uint8_t* sfb;
-    void* out;
     const void* bias;
     const float* alpha;   // device scalar or null (1.0)
     int M, N, K;          // K in elements
     int sf_tiles_k;       // 512-byte scale tiles along K (= padded scale columns / 4)
+    int sf_row_tiles_a;   // 128-row scale tiles of A
     int sf_row_tiles_b;   // 128-row scale tiles of W
     int out_code, bias_code;
-    int tiles_m, tiles_n;
+    int tiles_m, tiles_n; // pair tiles (256 x 256)
 };
 
 template <typename T16>
@@ -244,40 +283,28 @@ __device__ __forceinline__ uint32_t pack_pair<__half>(float a, float b) {
     return *reinterpret_cast<const uint32_t*>(&v);
 }
 
-template <typename TO>
-__device__ __forceinline__ void store_row32(TO* dst, const float (&v)[32], int valid) {
-    // 32 consecutive outputs of one row; `valid` (multiple of 8) of them are inside the matrix
-#pragma unroll
-    for (int g = 0; g < 4; ++g) {
-        if (g * 8 < valid) {
-            float t[8];
-#pragma unroll
-            for (int j = 0; j < 8; ++j) t[j] = v[g * 8 + j];
-            store8<TO>(dst + g * 8, t);
-        }
-    }
-}
-
 template <bool kFp4>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
 gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                         const __grid_constant__ CUtensorMap map_out, const GemmParams p) {
     extern __shared__ uint8_t smem_raw[];
-    // 1024-byte alignment for the swizzled operand tiles
+    // 1024-byte alignment for the swizzled tiles (the same offset in both CTAs of the pair)
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* stage_base = smem;
-    uint8_t* s_out = smem + kStages * kStageBytes;   // 1024-byte aligned: kStageBytes is a multiple of 1024
+    uint8_t* s_out = smem + kStages * kStageBytes;
     uint64_t* bars = reinterpret_cast<uint64_t*>(s_out + kSmemOut);
-    uint64_t* full = bars;                    // [kStages]  TMA landed -> scale movers (and, through sf_full, the MMA issuer)
-    uint64_t* empty = bars + kStages;         // [kStages]  movers have read the scales + MMAs of the k-tile done
-                                              //            -> TMA producer (stage free), movers (scale buffer free)
-    uint64_t* sf_full = bars + 2 * kStages;   // [kSfBufs]  scales in TMEM -> MMA issuer
+    uint64_t* full = bars;                    // [kStages]  this CTA's TMA copies landed -> its scale movers
+    uint64_t* empty = bars + kStages;         // [kStages]  movers have read the scales + the pair's MMAs of the k-tile are
+                                              //            done -> TMA producer (stage free), movers (scale buffer free)
+    uint64_t* sf_full = empty + kStages;      // [kSfBufs]  (leader's) both CTAs' scales in TMEM -> MMA issuer
     uint64_t* tmem_full = sf_full + kSfBufs;  //            accumulator complete -> epilogue
-    uint64_t* tmem_empty = tmem_full + 1;     //            accumulator copied to registers -> MMA issuer
+    uint64_t* tmem_empty = tmem_full + 1;     //            (leader's) both CTAs' accumulators copied out -> MMA issuer
     uint32_t* s_tmem_base = reinterpret_cast<uint32_t*>(tmem_empty + 1);
     volatile int* s_abort = reinterpret_cast<volatile int*>(s_tmem_base + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();              // 0 = leader
+    const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
     constexpr int kElemsPerTile = kFp4 ? 256 : 128;       // K elements per k-tile (128 bytes per row)
     constexpr int kMmaK = kFp4 ? 64 : 32;
     constexpr int kSfTilesPerStage = kFp4 ? 4 : 1;        // 512-byte tiles per 128 rows per k-tile
@@ -285,20 +312,20 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
     const int num_tiles = p.tiles_m * p.tiles_n;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < kStages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
-        for (int b = 0; b < kSfBufs; ++b) mbar_init(&sf_full[b], 4);
+        for (int s = 0; s < kStages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 5); }
+        for (int b = 0; b < kSfBufs; ++b) mbar_init(&sf_full[b], 8);
         mbar_init(tmem_full, 1);
-        mbar_init(tmem_empty, kEpiWarps);
+        mbar_init(tmem_empty, 2 * kEpiWarps);
         *s_abort = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
     if (warp == 1) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(s_tmem_base)), "r"(kTmemCols) : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(s_tmem_base)), "r"(kTmemCols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
     }
     tc_fence_before();
-    __syncthreads();
+    cluster_sync_all();   // barriers of both CTAs initialised, TMEM of both allocated
     tc_fence_after();
     const uint32_t tmem_base = *s_tmem_base;
 
@@ -306,24 +333,38 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
         // ------------------------------------------------------------ TMA producer
         uint32_t it = 0;  // k-tiles issued so far (ring position)
         bool ok = true;
-        for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        const size_t sf_row_pitch = (size_t)p.sf_tiles_k * 512;
+        for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
             const int tm = tile % p.tiles_m, tn = tile / p.tiles_m;
+            const int row_tile_a = tm * 2 + (int)rank;     // this CTA's 128 rows of A
+            const bool have_a = row_tile_a < p.sf_row_tiles_a;
+            const int row_tile_b = tn * 2;                 // first of the two 128-row scale tiles of the W tile
+            const int b_tiles = (row_tile_b + 1 < p.sf_row_tiles_b) ? 2 : 1;
+            const uint8_t* sfa_src = p.sfa + (size_t)row_tile_a * sf_row_pitch;
+            const uint8_t* sfb_src = p.sfb + (size_t)row_tile_b * sf_row_pitch;
             for (int kt = 0; kt < k_tiles && ok; ++kt, ++it) {
                 const int s = it % kStages;
                 const uint32_t round = it / kStages;
+                CK_TS(3 + rank, it, 0);
                 if (round > 0) ok = mbar_wait(&empty[s], (round - 1) & 1, s_abort, kTimeoutEmpty);
                 if (!ok) break;
+                CK_TS(3 + rank, it, 1);
                 // operands are computed by the whole warp; one elected lane issues the copies
                 uint8_t* st = stage_base + s * kStageBytes;
-                const uint32_t tx_bytes = kSmemA + kSmemB;
+                int n_sf = p.sf_tiles_k - kt * kSfTilesPerStage;  // scale tiles valid in this k-tile (the last may be short)
+                if (n_sf > kSfTilesPerStage) n_sf = kSfTilesPerStage;
+                const uint32_t sf_bytes = (uint32_t)n_sf * 512u;
+                const size_t sf_off = (size_t)kt * (kSfTilesPerStage * 512);
+                const uint32_t tx_bytes = kSmemA + kSmemB + sf_bytes * ((have_a ? 1 : 0) + b_tiles);
                 if (elect_one()) {
-                    if (CK_GEMM_PROBE & 2) {
-                        mbar_arrive(&full[s]);
-                    } else {
-                        mbar_expect_tx(&full[s], tx_bytes);
-                        tma_load_2d(st, &map_a, kt * 128, tm * BM, &full[s]);
-                        tma_load_2d(st + kSmemA, &map_b, kt * 128, tn * BN, &full[s]);
-                    }
+                    mbar_expect_tx(&full[s], tx_bytes);
+                    tma_load_2d(st, &map_a, kt * 128, tm * 256 + (int)rank * BM, &full[s]);
+                    tma_load_2d(st + kSmemA, &map_b, kt * 128, tn * BN + (int)rank * (BN / 2), &full[s]);
+                    if (have_a) bulk_load(st + kSmemA + kSmemB, sfa_src + sf_off, sf_bytes, &full[s]);
+                    bulk_load(st + kSmemA + kSmemB + kSmemSfA, sfb_src + sf_off, sf_bytes, &full[s]);
+                    if (b_tiles == 2)
+                        bulk_load(st + kSmemA + kSmemB + kSmemSfA + kSmemSfB / 2, sfb_src + sf_row_pitch + sf_off,
+                                  sf_bytes, &full[s]);
                 }
                 __syncwarp();
             }
@@ -335,106 +376,99 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
             (void)mbar_wait(&full[s], (j / kStages) & 1, s_abort, kTimeoutFull);
         }
     } else if (warp >= kFirstMoverWarp) {
-        // ------------------------------------------------------------ scale movers (global -> registers -> TMEM)
+        // ------------------------------------------------------------ scale movers (smem -> registers -> TMEM)
         // A 512-byte scale tile is 32 rows x 16 bytes: row i holds, for the four 32-row groups g of a
         // 128-row tile, the scale bytes of row 32g + i.  The MMA wants it in TMEM as 32 lanes x 4 columns
         // (column g), the same in each 32-lane quarter.  Each mover warp owns one quarter: lane i reads row
-        // i of every tile of the k-tile with 128-bit loads (512 contiguous bytes per warp and load; the four
-        // warps read the same lines, which L1 serves) and stores the words to TMEM lane i.  Two groups of four
-        // warps take the k-tiles in turn, so a group's loads have two k-tiles' time to arrive.  k-tile `it`
-        // uses scale buffer it % 3, last read by the MMAs of k-tile it - 3, whose completion empty[] reports.
+        // i with one 128-bit load per tile and stores its words to TMEM lane i.  k-tile `it` uses scale
+        // buffer it % 3, last read by the MMAs of k-tile it - 3, whose completion empty[] reports.
         const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
-        constexpr int kNa = kFp4 ? 16 : 4, kNb = kFp4 ? 32 : 8;   // words per lane: A scales, W scales
-        const size_t sf_row_pitch = (size_t)p.sf_tiles_k * 512;
-        uint32_t nxt_a[kNa], nxt_b[kNb];
-        auto fetch = [&](int tile, int kt) {
-            const int tm = tile % p.tiles_m, tn = tile / p.tiles_m;
-            const int row_tile_b = tn * (BN / 128);   // first of the two 128-row scale tiles of this W tile
-            const bool second = row_tile_b + 1 < p.sf_row_tiles_b;
-            const uint8_t* a_src = p.sfa + (size_t)tm * sf_row_pitch + (size_t)kt * (kSfTilesPerStage * 512) + lane * 16;
-            const uint8_t* b_src = p.sfb + (size_t)row_tile_b * sf_row_pitch + (size_t)kt * (kSfTilesPerStage * 512) + lane * 16;
-            const int n_sf = p.sf_tiles_k - kt * kSfTilesPerStage;   // tiles that exist in this k-tile (the last may be short)
-#pragma unroll
-            for (int t = 0; t < kSfTilesPerStage; ++t) {   // k-block t: A columns 4t.., W columns 8t.. (first, then second row tile)
-                uint4 va = make_uint4(0, 0, 0, 0), v0 = va, v1 = va;
-                if (t < n_sf && !(CK_GEMM_PROBE & 1)) {
-                    va = __ldg(reinterpret_cast<const uint4*>(a_src + t * 512));
-                    v0 = __ldg(reinterpret_cast<const uint4*>(b_src + t * 512));
-                    if (second) v1 = __ldg(reinterpret_cast<const uint4*>(b_src + sf_row_pitch + t * 512));
-                }
-                nxt_a[4 * t] = va.x; nxt_a[4 * t + 1] = va.y; nxt_a[4 * t + 2] = va.z; nxt_a[4 * t + 3] = va.w;
-                nxt_b[8 * t + 0] = v0.x; nxt_b[8 * t + 1] = v0.y; nxt_b[8 * t + 2] = v0.z; nxt_b[8 * t + 3] = v0.w;
-                nxt_b[8 * t + 4] = v1.x; nxt_b[8 * t + 5] = v1.y; nxt_b[8 * t + 6] = v1.z; nxt_b[8 * t + 7] = v1.w;
-            }
-        };
-        const uint32_t group = (uint32_t)(warp - kFirstMoverWarp) >> 2;
-        const uint32_t my_tiles = blockIdx.x < (uint32_t)num_tiles ? (num_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
-        const uint32_t total = my_tiles * (uint32_t)k_tiles;   // k-tiles this CTA works through, in order
-        auto fetch_nth = [&](uint32_t j) { fetch((int)(blockIdx.x + (j / k_tiles) * gridDim.x), (int)(j % k_tiles)); };
+        uint32_t it = 0;
         bool ok = true;
-        if (group < total) fetch_nth(group);
-        for (uint32_t it = group; it < total && ok; it += kMoverGroups) {
-            const int s = it % kStages;
-            const uint32_t b = it % kSfBufs;
-            if (it >= (uint32_t)kSfBufs) {
-                const uint32_t prev = it - kSfBufs;
-                ok = mbar_wait(&empty[prev % kStages], (prev / kStages) & 1, s_abort, kTimeoutEmpty);
+        for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
+            for (int kt = 0; kt < k_tiles && ok; ++kt, ++it) {
+                const int s = it % kStages;
+                const uint32_t b = it % kSfBufs;
+                if (warp == kFirstMoverWarp) CK_TS(1 + rank, it, 0);
+                ok = mbar_wait(&full[s], (it / kStages) & 1, s_abort, kTimeoutFull);
                 if (!ok) break;
+                if (warp == kFirstMoverWarp) CK_TS(1 + rank, it, 1);
+                const uint8_t* sfa_s = stage_base + s * kStageBytes + kSmemA + kSmemB + lane * 16;
+                const uint8_t* sfb_s = sfa_s + kSmemSfA;
+                constexpr int kNa = kFp4 ? 16 : 4, kNb = kFp4 ? 32 : 8;   // words per lane: A scales, W scales
+                uint32_t ra[kNa], rb[kNb];
+                if constexpr ((CK_GEMM_PROBE & 1) != 0) {
+                } else {
+#pragma unroll
+                    for (int t = 0; t < kSfTilesPerStage; ++t) {  // k-block t: A columns 4t.., W columns 8t.. (first, then second row tile)
+                        const uint4 v = *reinterpret_cast<const uint4*>(sfa_s + t * 512);
+                        ra[4 * t] = v.x; ra[4 * t + 1] = v.y; ra[4 * t + 2] = v.z; ra[4 * t + 3] = v.w;
+                        const uint4 v0 = *reinterpret_cast<const uint4*>(sfb_s + t * 512);
+                        const uint4 v1 = *reinterpret_cast<const uint4*>(sfb_s + kSmemSfB / 2 + t * 512);
+                        rb[8 * t + 0] = v0.x; rb[8 * t + 1] = v0.y; rb[8 * t + 2] = v0.z; rb[8 * t + 3] = v0.w;
+                        rb[8 * t + 4] = v1.x; rb[8 * t + 5] = v1.y; rb[8 * t + 6] = v1.z; rb[8 * t + 7] = v1.w;
+                    }
+                    // make sure the loads have returned before the stage's scale area is handed back
+                    asm volatile("" ::"r"(ra[0]), "r"(rb[0]), "r"(rb[4]) : "memory");
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&empty[s]);
+                if (it >= (uint32_t)kSfBufs) {
+                    const uint32_t prev = it - kSfBufs;
+                    ok = mbar_wait(&empty[prev % kStages], (prev / kStages) & 1, s_abort, kTimeoutEmpty);
+                    if (!ok) break;
+                }
+                tc_fence_after();
+                if (warp == kFirstMoverWarp) CK_TS(1 + rank, it, 2);
+                const uint32_t t_sfa = tmem_base + lane_base + tmem_sfa_col(b);
+                const uint32_t t_sfb = tmem_base + lane_base + tmem_sfb_col(b);
+                if constexpr ((CK_GEMM_PROBE & 1) != 0) {
+                } else if constexpr (kFp4) {
+                    tc_st16(t_sfa, ra);
+                    tc_st16(t_sfb, rb);
+                    tc_st16(t_sfb + 16, rb + 16);
+                } else {
+                    tc_st4(t_sfa, ra);
+                    tc_st8(t_sfb, rb);
+                }
+                tc_wait_st();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive_cluster(&sf_full[b], 0);   // the leader's barrier
+                if (warp == kFirstMoverWarp) CK_TS(1 + rank, it, 3);
             }
-            tc_fence_after();
-            const uint32_t t_sfa = tmem_base + lane_base + tmem_sfa_col(b);
-            const uint32_t t_sfb = tmem_base + lane_base + tmem_sfb_col(b);
-            if constexpr ((CK_GEMM_PROBE & 1) != 0) {
-            } else if constexpr (kFp4) {
-                tc_st16(t_sfa, nxt_a);
-                tc_st16(t_sfb, nxt_b);
-                tc_st16(t_sfb + 16, nxt_b + 16);
-            } else {
-                tc_st4(t_sfa, nxt_a);
-                tc_st8(t_sfb, nxt_b);
-            }
-            tc_wait_st();
-            tc_fence_before();
-            // the registers are free again: start this group's next k-tile's loads
-            if (it + kMoverGroups < total) fetch_nth(it + kMoverGroups);
-            // sf_full tells the MMA issuer that this k-tile can go: scales in TMEM and operands in shared memory
-            ok = mbar_wait(&full[s], (it / kStages) & 1, s_abort, kTimeoutFull);
-            if (!ok) break;
-            if (lane == 0) mbar_arrive(&sf_full[b]);
         }
     } else if (warp == 1) {
-        // ------------------------------------------------------------ MMA issuer
-#ifdef CK_PROBE_N
-        constexpr int kInstrN = CK_PROBE_N;   // timing experiment: instruction N differs from the tile (wrong results)
-#else
-        constexpr int kInstrN = BN;
-#endif
-        const uint32_t idesc_base = (kFp4 ? ((1u << 7) | (1u << 10)) : 0u) | ((uint32_t)(kInstrN >> 3) << 17) |
-                                    (kFp4 ? 0u : (1u << 23)) | ((uint32_t)(BM >> 4) << 24);
+        // ------------------------------------------------------------ MMA issuer (leader CTA only)
+        if (rank == 0) {
+        const uint32_t idesc_base = (kFp4 ? ((1u << 7) | (1u << 10)) : 0u) | ((uint32_t)(BN >> 3) << 17) |
+                                    (kFp4 ? 0u : (1u << 23)) | ((uint32_t)((2 * BM) >> 4) << 24);
         const uint32_t smem16 = (smem_u32(stage_base) & 0x3ffffu) >> 4;
         const bool tail_full = (p.K % kElemsPerTile) == 0;
         uint32_t it = 0, local_tile = 0;
         bool ok = true, ready = false;
-        for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local_tile) {
+        for (int tile = pair; tile < num_tiles && ok; tile += num_pairs, ++local_tile) {
+            CK_TS(0, 240 + local_tile, 0);
             if (local_tile > 0) ok = mbar_wait(tmem_empty, (local_tile - 1) & 1, s_abort, kTimeoutTmemEmpty);
             if (!ok) break;
             tc_fence_after();
+            CK_TS(0, 240 + local_tile, 1);
             const uint32_t d_tmem = tmem_base + kTmemAcc;
             for (int kt = 0; kt < k_tiles && ok; ++kt, ++it) {
                 const int s = it % kStages;
                 const uint32_t sb = it % kSfBufs;
 #if CK_GEMM_PROBE & 8
-                if (blockIdx.x == 0 && lane == 0 && it < 256) g_probe_ts[4 * it + 0] = clock64();
+                CK_TS(0, it, 0);
 #endif
-                // The movers publish sf_full only after they saw full[s], so this one wait covers the operands
-                // too.  `ready` is an early look at it taken while the previous k-tile was being issued.
+                // The movers of both CTAs publish sf_full only after they saw their full[s], so this one wait
+                // covers the operands too.  `ready` is an early look taken while the previous k-tile was issued.
                 if (!__all_sync(0xffffffffu, ready)) ok = mbar_wait(&sf_full[sb], (it / kSfBufs) & 1, s_abort, kTimeoutSfFull);
                 if (!ok) break;
                 tc_fence_after();
 #if CK_GEMM_PROBE & 8
-                if (blockIdx.x == 0 && lane == 0 && it < 256) g_probe_ts[4 * it + 1] = clock64();
+                CK_TS(0, it, 1);
 #endif
-                // every descriptor of this stage is "stage start >> 4" plus a constant
+                // every descriptor of this stage is "stage start >> 4" plus a constant (the same in both CTAs)
                 const uint32_t st16 = smem16 + (uint32_t)s * (kStageBytes >> 4);
                 const uint32_t a_lo = st16 | kDescLoLbo1, b_lo = (st16 + (kSmemA >> 4)) | kDescLoLbo1;
                 const uint32_t t_sfa = tmem_base + tmem_sfa_col(sb), t_sfb = tmem_base + tmem_sfb_col(sb);
@@ -452,29 +486,36 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
                     // the pipe is busy with these for a while: look at the next k-tile's barrier now
                     if (kb == 1) ready = mbar_test_wait(&sf_full[(it + 1) % kSfBufs], ((it + 1) / kSfBufs) & 1);
                 }
-                tc_commit(&empty[s]);                      // stage and scale buffer reusable once these MMAs are done
-                if (kt == k_tiles - 1) tc_commit(tmem_full);  // accumulator complete
+                tc_commit_pair(&empty[s]);                      // stage and scale buffer reusable once these MMAs are done
+                if (kt == k_tiles - 1) { tc_commit_pair(tmem_full); CK_TS(0, 240 + local_tile, 2); }  // accumulators complete
 #if CK_GEMM_PROBE & 8
-                if (blockIdx.x == 0 && lane == 0 && it < 256) g_probe_ts[4 * it + 2] = clock64();
+                CK_TS(0, it, 2);
 #endif
             }
         }
+        }
     } else {
-        // ------------------------------------------------------------ epilogue (warps 2..9)
-        const int q = warp & 3;                        // TMEM lanes 32q .. 32q+31 belong to this warp
-        const int half = (warp - kFirstEpiWarp) >> 2;  // which 128 columns of the tile
-        uint8_t* stg = s_out + (warp - kFirstEpiWarp) * 4096;
+        // ------------------------------------------------------------ epilogue (warps 2..17)
+        // Lane i of a warp owns TMEM lane 32q + i, i.e. one output row, and 64 of its columns.  The warp copies
+        // them to registers and hands the accumulator back at once; alpha, bias, the conversion and the store
+        // overlap the next tile's MMAs.  Results leave through shared memory, 64 bytes per row at a time: the
+        // lane writes 16-byte pieces placed with the 64-byte swizzle, which keeps the writes conflict-free, and
+        // a TMA store moves the 32 x 64-byte chunk to global memory, clipped at the matrix edges.  Lane 0 issues the warp's stores and waits for the previous one to have read the
+        // staging buffer before it is overwritten.
+        const int e = warp - kFirstEpiWarp;
+        const int q = warp & 3;    // TMEM lanes 32q .. 32q+31 belong to this warp
+        const int part = e >> 2;   // which 64 columns of the tile
+        uint8_t* stg = s_out + e * 2048;
         const float alpha = p.alpha ? __ldg(p.alpha) : 1.0f;
         uint32_t local_tile = 0;
         bool ok = true;
-        for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local_tile) {
+        for (int tile = pair; tile < num_tiles && ok; tile += num_pairs, ++local_tile) {
             const int tm = tile % p.tiles_m, tn = tile / p.tiles_m;
-            const int n0 = tn * BN + half * 128;
-            // bias for these 128 columns: lane l keeps columns l, l + 32, l + 64, l + 96 and the others
-            // fetch them with shuffles
-            float bias_reg[4];
+            const int n0 = tn * BN + part * 64;
+            // bias for these 64 columns: lane l keeps columns l and l + 32, the others fetch them with shuffles
+            float bias_reg[2];
 #pragma unroll
-            for (int k = 0; k < 4; ++k) {
+            for (int k = 0; k < 2; ++k) {
                 float b = 0.0f;
                 const int n = n0 + k * 32 + lane;
                 if (p.bias && n < p.N) {
@@ -488,88 +529,70 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
             ok = mbar_wait(tmem_full, local_tile & 1, s_abort, kTimeoutTmemFull);
             if (!ok) break;
             tc_fence_after();
-            const uint32_t acc = tmem_base + kTmemAcc + ((uint32_t)(q * 32) << 16) + (uint32_t)(half * 128);
-            const int row0 = tm * BM + q * 32;   // first of this warp's 32 rows
-            if (CK_GEMM_PROBE & 16) {
-                __syncwarp();
-                if (lane == 0) mbar_arrive(tmem_empty);
-                continue;
-            }
-            // Results leave through shared memory: lane i owns row i of the warp's 32 rows and writes 128 bytes of
-            // it per chunk (16-byte pieces placed with the 128-byte swizzle, which keeps the writes conflict-free);
-            // a TMA store then moves the 32 x 128-byte chunk to global memory in full lines and clips it at the
-            // matrix edges.  Lane 0 issues every store of this warp and waits for the previous one to have read
-            // the staging buffer before it is overwritten.
-            auto stage_chunk = [&](const uint32_t* w, int col) {
-                if (lane == 0) bulk_wait_read_all();
-                __syncwarp();
-#pragma unroll
-                for (int j = 0; j < 8; ++j)
-                    *reinterpret_cast<uint4*>(stg + lane * 128 + ((j ^ (lane & 7)) << 4)) =
-                        make_uint4(w[4 * j], w[4 * j + 1], w[4 * j + 2], w[4 * j + 3]);
-                fence_async_smem();
-                __syncwarp();
-                if (lane == 0 && col < p.N && !(CK_GEMM_PROBE & 32)) tma_store_2d(&map_out, stg, col, row0);
-            };
-            if (p.out_code != CK_F32) {
-                // 16-bit outputs: the first 64 columns wait in registers as packed pairs while the second 64 are
-                // read, so the accumulator goes back to the MMA issuer before any store is issued.
-                uint32_t packed[32];
-                uint32_t r[2][32];
-                if (!(CK_GEMM_PROBE & 64)) {
+            if (warp == kFirstEpiWarp) CK_TS(1 + rank, 240 + local_tile, 0);
+            const uint32_t acc = tmem_base + kTmemAcc + ((uint32_t)(q * 32) << 16) + (uint32_t)(part * 64);
+            const int row0 = tm * 256 + (int)rank * BM + q * 32;   // first of this warp's 32 rows
+            uint32_t r[2][32];
+            if (!(CK_GEMM_PROBE & 16)) {
                 tc_ld32(acc, r[0]);
                 tc_ld32(acc + 32, r[1]);
                 tc_wait_ld();
-                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(tmem_empty, 0);
+            if (warp == kFirstEpiWarp) CK_TS(1 + rank, 240 + local_tile, 2);
+            if (CK_GEMM_PROBE & 16) continue;
+            const bool store_ok = row0 < p.M;
+            // a staging chunk is 32 rows x 64 bytes: 32 columns of a 16-bit output, 16 of an fp32 one
+            const int n_chunks = p.out_code == CK_F32 ? 4 : 2;
+            const int chunk_cols = p.out_code == CK_F32 ? 16 : 32;
+            uint8_t* my_row = stg + lane * 64;
+            const int sw = (lane >> 1) & 3;   // 64-byte swizzle: 16-byte piece index ^ ((row / 2) % 4)
 #pragma unroll
-                for (int j = 0; j < 64; j += 2) {
-                    const float a = fmaf(__uint_as_float(r[j >> 5][j & 31]), alpha, bias_at(j));
-                    const float b = fmaf(__uint_as_float(r[j >> 5][(j & 31) + 1]), alpha, bias_at(j + 1));
-                    packed[j >> 1] = p.out_code == CK_BF16 ? pack_pair<__nv_bfloat16>(a, b) : pack_pair<__half>(a, b);
-                }
-                if (!(CK_GEMM_PROBE & 64)) {
-                tc_ld32(acc + 64, r[0]);
-                tc_ld32(acc + 96, r[1]);
-                tc_wait_ld();
-                }
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(tmem_empty);
-                stage_chunk(packed, n0);
+            for (int ch = 0; ch < 4; ++ch) {
+                if (ch < n_chunks) {
+                    if (lane == 0) bulk_wait_read_all();
+                    __syncwarp();
 #pragma unroll
-                for (int j = 0; j < 64; j += 2) {
-                    const float a = fmaf(__uint_as_float(r[j >> 5][j & 31]), alpha, bias_at(64 + j));
-                    const float b = fmaf(__uint_as_float(r[j >> 5][(j & 31) + 1]), alpha, bias_at(64 + j + 1));
-                    packed[j >> 1] = p.out_code == CK_BF16 ? pack_pair<__nv_bfloat16>(a, b) : pack_pair<__half>(a, b);
-                }
-                stage_chunk(packed, n0 + 64);
-            } else {
-                // fp32 output: 32 columns (128 bytes per row) at a time
+                    for (int j = 0; j < 4; ++j) {   // one 16-byte piece: 8 columns (16-bit) or 4 (fp32)
+                        uint32_t w[4];
+                        if (p.out_code != CK_F32) {
 #pragma unroll
-                for (int c = 0; c < 4; ++c) {
-                    uint32_t r[32];
-                    tc_ld32(acc + c * 32, r);
-                    tc_wait_ld();
-                    if (c == 3) {
-                        tc_fence_before();
-                        __syncwarp();
-                        if (lane == 0) mbar_arrive(tmem_empty);
+                            for (int i = 0; i < 4; ++i) {
+                                const int c = 32 * (ch & 1) + 8 * j + 2 * i;
+                                const float a = fmaf(__uint_as_float(r[c >> 5][c & 31]), alpha, bias_at(c));
+                                const float b = fmaf(__uint_as_float(r[c >> 5][(c & 31) + 1]), alpha, bias_at(c + 1));
+                                w[i] = p.out_code == CK_BF16 ? pack_pair<__nv_bfloat16>(a, b) : pack_pair<__half>(a, b);
+                            }
+                        } else {
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) {
+                                const int c = 16 * ch + 4 * j + i;
+                                w[i] = __float_as_uint(fmaf(__uint_as_float(r[c >> 5][c & 31]), alpha, bias_at(c)));
+                            }
+                        }
+                        *reinterpret_cast<uint4*>(my_row + ((j ^ sw) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
                     }
-#pragma unroll
-                    for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(fmaf(__uint_as_float(r[j]), alpha, bias_at(c * 32 + j)));
-                    stage_chunk(r, n0 + c * 32);
+                    fence_async_smem();
+                    __syncwarp();
+                    const int col = n0 + ch * chunk_cols;
+                    if (lane == 0 && store_ok && col < p.N) tma_store_2d(&map_out, stg, col, row0);
                 }
             }
+            if (warp == kFirstEpiWarp) CK_TS(1 + rank, 240 + local_tile, 3);
         }
         if (lane == 0) bulk_wait_all();   // the staging buffer must outlive the stores that read it
         __syncwarp();
     }
 
+    // Neither CTA may leave (or free its TMEM) while the other can still signal its barriers, read its
+    // shared memory or write its TMEM through a paired MMA.
     tc_fence_before();
-    __syncthreads();
+    cluster_sync_all();
     if (warp == 1) {
         tc_fence_after();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
     }
 }
 
@@ -607,17 +630,17 @@ int make_operand_map(CUtensorMap* map, const void* base, int64_t rows, int64_t r
     return CK_OK;
 }
 
-// Output [rows, cols] of 2- or 4-byte elements, box = 128 bytes x 32 rows, 128-byte swizzle (the layout the
+// Output [rows, cols] of 2- or 4-byte elements, box = 64 bytes x 32 rows, 64-byte swizzle (the layout the
 // epilogue writes into its staging buffers).
 int make_output_map(CUtensorMap* map, void* base, int64_t rows, int64_t cols, int elem_bytes) {
     EncodeFn enc = get_encode();
     if (!enc) CK_FAIL(CK_ERR_UNSUPPORTED, "scaled_mm: cuTensorMapEncodeTiled is not available from the driver");
     cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
     cuuint64_t strides[1] = {(cuuint64_t)(cols * elem_bytes)};
-    cuuint32_t box[2] = {(cuuint32_t)(128 / elem_bytes), 32u};
+    cuuint32_t box[2] = {(cuuint32_t)(64 / elem_bytes), 32u};
     cuuint32_t estr[2] = {1u, 1u};
     CUresult r = enc(map, elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_UINT16 : CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, base, dims,
-                     strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                     strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B,
                      CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) CK_FAIL(CK_ERR_UNSUPPORTED, "scaled_mm: cuTensorMapEncodeTiled (output) failed with %d", (int)r);
     return CK_OK;
@@ -653,36 +676,54 @@ int launch_gemm(const void* a, const void* sfa, const void* b, const void* sfb, 
     if (!aligned16(a) || !aligned16(b) || !aligned16(sfa) || !aligned16(sfb) || !aligned16(d) || row_bytes % 16 != 0)
         CK_FAIL(CK_ERR_ALIGN, "%s: operands, scales and output must be 16-byte aligned (row pitch too)", what);
 
-    static bool attr_set[2][64] = {};
+    // per device: shared-memory opt-in, and how many CTA pairs can be resident at once
+    static int max_pairs[2][64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
-    if (dev < 0 || dev >= 64 || !attr_set[kFp4][dev]) {
+    int pairs_cap = (dev >= 0 && dev < 64) ? max_pairs[kFp4][dev] : 0;
+    if (pairs_cap == 0) {
         cudaError_t e = cudaFuncSetAttribute(gemm_blockscaled_kernel<kFp4>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
         if (e != cudaSuccess) CK_FAIL((int)e, "%s: cannot reserve %d bytes of shared memory: %s", what, kSmemBytes, cudaGetErrorString(e));
-        if (dev >= 0 && dev < 64) attr_set[kFp4][dev] = true;
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(2 * (unsigned)(sm_count() / 2));
+        cfg.blockDim = dim3(kThreads);
+        cfg.dynamicSmemBytes = kSmemBytes;
+        cudaLaunchAttribute attr;
+        attr.id = cudaLaunchAttributeClusterDimension;
+        attr.val.clusterDim.x = 2; attr.val.clusterDim.y = 1; attr.val.clusterDim.z = 1;
+        cfg.attrs = &attr;
+        cfg.numAttrs = 1;
+        int n = 0;
+        e = cudaOccupancyMaxActiveClusters(&n, gemm_blockscaled_kernel<kFp4>, &cfg);
+        if (e != cudaSuccess || n <= 0) {
+            cudaGetLastError();
+            n = sm_count() / 2;
+        }
+        pairs_cap = n < sm_count() / 2 ? n : sm_count() / 2;
+        if (dev >= 0 && dev < 64) max_pairs[kFp4][dev] = pairs_cap;
     }
 
     CUtensorMap map_a, map_b, map_out;
     if (int rc = make_operand_map(&map_a, a, M, row_bytes, BM)) return rc;
-    if (int rc = make_operand_map(&map_b, b, N, row_bytes, BN)) return rc;
+    if (int rc = make_operand_map(&map_b, b, N, row_bytes, BN / 2)) return rc;
     if (int rc = make_output_map(&map_out, d, M, N, out_code == CK_F32 ? 4 : 2)) return rc;
 
     GemmParams p{};
     p.sfa = static_cast<const uint8_t*>(sfa);
     p.sfb = static_cast<const uint8_t*>(sfb);
-    p.out = d;
     p.bias = bias;
     p.alpha = alpha;
     p.M = (int)M; p.N = (int)N; p.K = (int)K;
     const int64_t blk = kFp4 ? 16 : 32;
     p.sf_tiles_k = (int)(round_up(K / blk, 4) / 4);
+    p.sf_row_tiles_a = (int)ceil_div(M, 128);
     p.sf_row_tiles_b = (int)ceil_div(N, 128);
     p.out_code = out_code;
     p.bias_code = bias_code;
-    p.tiles_m = (int)ceil_div(M, BM);
+    p.tiles_m = (int)ceil_div(M, 2 * BM);
     p.tiles_n = (int)ceil_div(N, BN);
     const int64_t tiles = (int64_t)p.tiles_m * p.tiles_n;
-    const int grid = (int)(tiles < sm_count() ? tiles : sm_count());
+    const int grid = 2 * (int)(tiles < pairs_cap ? tiles : pairs_cap);   // clusters of two CTAs
     gemm_blockscaled_kernel<kFp4><<<grid, kThreads, kSmemBytes, stream>>>(map_a, map_b, map_out, p);
     return launch_status(what);
 }
@@ -724,7 +765,7 @@ extern "C" int launch_cublas_gemm_blockwise_fp4_kernel(const void* B_ptr, const 
 #if CK_GEMM_PROBE & 8
 extern "C" int ck_probe_read(long long* out) {
     cudaDeviceSynchronize();
-    return (int)cudaMemcpyFromSymbol(out, ck::g_probe_ts, sizeof(long long) * 4 * 256);
+    return (int)cudaMemcpyFromSymbol(out, ck::g_probe_ts, sizeof(long long) * 5 * 4 * 256);
 }
 #endif
 
