@@ -379,6 +379,91 @@ def run_case(args) -> None:
     print(json.dumps({"case": args.case, "shape": [M, N, K], "ms": round(ms, 4), "value": round(work / ms / 1e6, 1), "unit": unit}))
 
 
+# ----------------------------------------------------------------------------- DiT stack (tensor parallel)
+
+
+def run_dit(args) -> None:
+    """One step = one forward of the synthetic Flux-like stack (19 double + 38 single blocks unless --dit-blocks
+    says otherwise) on 4608 tokens, tensor-parallel over the N ranks (strong scaling: the work is fixed)."""
+    from comfy_kitchen.dit_stack import (DiTConfig, DiTStack, TensorParallel, attention_flops_per_forward,
+                                         gemm_flops_per_forward)
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (the product path has no CPU fallback)")
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist  # type: ignore[no-redef]
+
+        dist.init_process_group("nccl", device_id=device)
+    nd, ns = (int(v) for v in args.dit_blocks.split(","))
+    cfg = DiTConfig(n_double=nd, n_single=ns)
+    stack = DiTStack(cfg, device, tp=TensorParallel())
+    g = torch.Generator().manual_seed(11)  # the same inputs on every rank
+    host = [torch.randn(cfg.img_tokens, cfg.hidden, generator=g).bfloat16().pin_memory(),
+            torch.randn(cfg.txt_tokens, cfg.hidden, generator=g).bfloat16().pin_memory(),
+            torch.randn(1, cfg.hidden, generator=g).bfloat16().pin_memory()]
+    img, txt, vec = (t.to(device) for t in host)
+    stack.calibrate(img, txt, vec)
+    for _ in range(max(args.warmup, 3)):
+        out = stack.forward(img, txt, vec)
+    torch.cuda.synchronize()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    if dist is not None:
+        dist.barrier()
+    torch.cuda.synchronize()
+    calls0 = stack.tp.all_reduce_calls
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        out = stack.forward(img, txt, vec)
+    e1.record()
+    torch.cuda.synchronize()
+    if dist is not None:
+        dist.barrier()
+    clocks = sampler.stop() if rank == 0 else None
+    elapsed_ms = max_over_ranks(e0.elapsed_time(e1), dist, device)
+    assert stack.ops.gemm_device_status() == 0, "GEMM kernel reported a device-side timeout"
+    assert torch.isfinite(out.float()).all(), "non-finite output"
+    ms = elapsed_ms / args.steps
+    # end to end: inputs from pinned host memory, output back to the host, wall clock
+    host_out = torch.empty(cfg.tokens, cfg.hidden, dtype=torch.bfloat16).pin_memory()
+    torch.cuda.synchronize()
+    if dist is not None:
+        dist.barrier()
+    t0 = time.perf_counter()
+    n_e2e = max(1, min(args.steps, 3))
+    for _ in range(n_e2e):
+        d = [t.to(device, non_blocking=True) for t in host]
+        host_out.copy_(stack.forward(*d), non_blocking=True)
+        torch.cuda.synchronize()
+    t_e2e = (time.perf_counter() - t0) / n_e2e * 1e3
+    t_e2e = max_over_ranks(t_e2e, dist, device)
+    if rank == 0:
+        gf, af = gemm_flops_per_forward(cfg), attention_flops_per_forward(cfg)
+        print(json.dumps({
+            "metric": "dit_stack_forward_ms", "value": round(ms, 3), "unit": "ms", "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": round(ms, 3), "higher_is_better": False, "scaling": "strong",
+            "vs_baseline": None, "dtype": "nvfp4 linears (fp32 accumulate), bf16 attention", "data": "synthetic",
+            "config": {"workload": "synthetic Flux-like DiT stack (configs[4])", "double_blocks": nd, "single_blocks": ns,
+                       "tokens": cfg.tokens, "hidden": cfg.hidden, "parallelism": f"tp{world}",
+                       "all_reduces_per_forward": (stack.tp.all_reduce_calls - calls0) // (args.steps + n_e2e) if world else 0,
+                       "l2": "weights (6 GB per rank at tp1) larger than L2"},
+            "linear_tflops": round(gf / (ms * 1e-3) / 1e12, 1), "attention_tflop_per_forward": round(af / 1e12, 2),
+            "e2e": {"value": round(t_e2e, 3), "unit": "ms", "h2d_bytes_per_step": int(sum(t.numel() * 2 for t in host)),
+                    "d2h_bytes_per_step": int(host_out.numel() * 2)},
+            "clocks": clocks,
+        }))
+    if dist is not None:
+        dist.destroy_process_group()
+
+
 # ----------------------------------------------------------------------------- main
 
 
@@ -392,6 +477,9 @@ def main() -> None:
     ap.add_argument("--case", default=None,
                     help="run one kernel instead of the sweep (for profiling): gemm_nvfp4, gemm_mxfp8, quantize_nvfp4, "
                          "dequantize_nvfp4, quantize_mxfp8, quantize_fp8, adaln_quantize_nvfp4, rope")
+    ap.add_argument("--workload", default="linear", choices=["linear", "dit"],
+                    help="linear: the NVFP4 linear sweep (default); dit: the tensor-parallel DiT stack, ms per forward")
+    ap.add_argument("--dit-blocks", default="19,38", help="double,single block counts for --workload dit")
     ap.add_argument("--m", type=int, default=9216)
     ap.add_argument("--n", type=int, default=9216)
     ap.add_argument("--k", type=int, default=3072)
@@ -403,6 +491,9 @@ def main() -> None:
 
     if args.impl == "reference":
         run_reference(args)
+        return
+    if args.workload == "dit":
+        run_dit(args)
         return
 
     world = int(os.environ.get("WORLD_SIZE", "1"))

@@ -49,6 +49,8 @@ class DiTConfig:
     eps: float = 1e-6
     seed: int = 0
     weight_std: float = 0.02
+    init_device: str = ""   # where the random weights are drawn ("" = the stack's device); "cpu" gives the
+                            # same weights on any device, at the cost of a slow start for the full model
 
     @property
     def img_tokens(self) -> int:
@@ -169,9 +171,10 @@ class DiTStack:
     # ------------------------------------------------------------------ weights
 
     def _randn(self, shape, layer: int, name: str, std: float) -> torch.Tensor:
-        g = torch.Generator(device=self.device)
+        dev = torch.device(self.cfg.init_device) if self.cfg.init_device else self.device
+        g = torch.Generator(device=dev)
         g.manual_seed((self.cfg.seed * 1_000_003 + layer * 101 + sum(map(ord, name))) & 0x7FFFFFFF)
-        return (std * torch.randn(shape, generator=g, device=self.device, dtype=torch.float32)).bfloat16()
+        return (std * torch.randn(shape, generator=g, device=dev, dtype=torch.float32)).bfloat16().to(self.device)
 
     def _head_rows(self, per_part_rows: int) -> torch.Tensor:
         """Row indices of this rank's heads inside one of q / k / v (each heads * head_dim rows)."""

@@ -1,0 +1,40 @@
+"""The operator set DiTStack needs, served by the CPU oracle (test infrastructure only).
+
+Same names and argument meaning as comfy_kitchen.backends.cuda, so the stack's host logic
+(sharding, scales, collectives) can run on CPU ranks."""
+import torch
+import torch.nn.functional as F
+
+from oracle import ck_oracle as orc
+
+
+def quantize_nvfp4(x, per_tensor_scale, epsilon=0.0, pad_16x=False, hi_first=True):
+    return orc.quantize_nvfp4(x, per_tensor_scale, epsilon, pad_16x, hi_first)
+
+
+def dequantize_nvfp4(qx, per_tensor_scale, block_scales, output_type=torch.bfloat16, hi_first=True):
+    return orc.dequantize_nvfp4(qx, per_tensor_scale, block_scales, output_type, hi_first)
+
+
+def scaled_mm_nvfp4(a, b, tensor_scale_a, tensor_scale_b, block_scale_a, block_scale_b, bias=None,
+                    out_dtype=torch.bfloat16, alpha=None):
+    return orc.scaled_mm_nvfp4(a, b, tensor_scale_a, tensor_scale_b, block_scale_a, block_scale_b,
+                               bias=bias, out_dtype=out_dtype, alpha=alpha)
+
+
+def adaln(x, scale, shift, eps=1e-6):
+    return orc.adaln(x, scale, shift, eps, single_rounding=True)
+
+
+def adaln_quantize_nvfp4(x, scale, shift, per_tensor_scale, eps=1e-6, hi_first=True):
+    y = adaln(x, scale, shift, eps)
+    return orc.quantize_nvfp4(y.reshape(-1, y.shape[-1]), per_tensor_scale, 0.0, False, hi_first)
+
+
+def rmsnorm(x, weight=None, eps=1e-6):
+    w = None if weight is None else weight.float()
+    return F.rms_norm(x.float(), (x.shape[-1],), w, eps).to(x.dtype)
+
+
+def apply_rope(xq, xk, freqs_cis):
+    return orc.apply_rope(xq.contiguous(), xk.contiguous(), freqs_cis.contiguous())
