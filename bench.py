@@ -409,8 +409,9 @@ def run_dit(args) -> None:
             torch.randn(1, cfg.hidden, generator=g).bfloat16().pin_memory()]
     img, txt, vec = (t.to(device) for t in host)
     stack.calibrate(img, txt, vec)
+    run = stack.forward if args.no_graph else stack.capture(img, txt, vec)
     for _ in range(max(args.warmup, 3)):
-        out = stack.forward(img, txt, vec)
+        out = run(img, txt, vec)
     torch.cuda.synchronize()
     sampler = ClockSampler(local_rank)
     if rank == 0:
@@ -418,11 +419,10 @@ def run_dit(args) -> None:
     if dist is not None:
         dist.barrier()
     torch.cuda.synchronize()
-    calls0 = stack.tp.all_reduce_calls
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for _ in range(args.steps):
-        out = stack.forward(img, txt, vec)
+        out = run(img, txt, vec)
     e1.record()
     torch.cuda.synchronize()
     if dist is not None:
@@ -441,7 +441,7 @@ def run_dit(args) -> None:
     n_e2e = max(1, min(args.steps, 3))
     for _ in range(n_e2e):
         d = [t.to(device, non_blocking=True) for t in host]
-        host_out.copy_(stack.forward(*d), non_blocking=True)
+        host_out.copy_(run(*d), non_blocking=True)
         torch.cuda.synchronize()
     t_e2e = (time.perf_counter() - t0) / n_e2e * 1e3
     t_e2e = max_over_ranks(t_e2e, dist, device)
@@ -453,7 +453,8 @@ def run_dit(args) -> None:
             "vs_baseline": None, "dtype": "nvfp4 linears (fp32 accumulate), bf16 attention", "data": "synthetic",
             "config": {"workload": "synthetic Flux-like DiT stack (configs[4])", "double_blocks": nd, "single_blocks": ns,
                        "tokens": cfg.tokens, "hidden": cfg.hidden, "parallelism": f"tp{world}",
-                       "all_reduces_per_forward": (stack.tp.all_reduce_calls - calls0) // (args.steps + n_e2e) if world else 0,
+                       "all_reduces_per_forward": stack.expected_all_reduces(),
+                       "launch": "eager" if args.no_graph else "one CUDA graph per forward",
                        "l2": "weights (6 GB per rank at tp1) larger than L2"},
             "linear_tflops": round(gf / (ms * 1e-3) / 1e12, 1), "attention_tflop_per_forward": round(af / 1e12, 2),
             "e2e": {"value": round(t_e2e, 3), "unit": "ms", "h2d_bytes_per_step": int(sum(t.numel() * 2 for t in host)),
@@ -480,6 +481,7 @@ def main() -> None:
     ap.add_argument("--workload", default="linear", choices=["linear", "dit"],
                     help="linear: the NVFP4 linear sweep (default); dit: the tensor-parallel DiT stack, ms per forward")
     ap.add_argument("--dit-blocks", default="19,38", help="double,single block counts for --workload dit")
+    ap.add_argument("--no-graph", action="store_true", help="--workload dit: launch eagerly instead of replaying a CUDA graph")
     ap.add_argument("--m", type=int, default=9216)
     ap.add_argument("--n", type=int, default=9216)
     ap.add_argument("--k", type=int, default=3072)

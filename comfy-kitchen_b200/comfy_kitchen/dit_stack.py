@@ -385,6 +385,39 @@ class DiTStack:
 
     __call__ = forward
 
+    def capture(self, img: torch.Tensor, txt: torch.Tensor, vec: torch.Tensor):
+        """Record one forward into a CUDA graph and return ``replay(img, txt, vec) -> out``.
+
+        The forward is ~50 small launches per block; replaying a graph removes their host cost.  Needs static
+        activation scales (call calibrate() first) so that no value-dependent host work is left in the forward.
+        Inputs are copied into the graph's own buffers; the returned tensor is the graph's output buffer
+        (overwritten by the next replay).  With more than one rank the all-reduces are captured too, so every
+        rank must capture and replay in step.
+        """
+        assert self.device.type == "cuda", "graph capture needs a CUDA device"
+        assert self.sites.static, "calibrate() first: capture needs static activation scales"
+        bufs = [img.clone(), txt.clone(), vec.clone()]
+        side = torch.cuda.Stream(device=self.device)
+        side.wait_stream(torch.cuda.current_stream(self.device))
+        with torch.cuda.stream(side):
+            for _ in range(2):  # warm up on the capture stream: lazy initialisation must not be recorded
+                self.forward(*bufs)
+        torch.cuda.current_stream(self.device).wait_stream(side)
+        torch.cuda.synchronize(self.device)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side):
+            out = self.forward(*bufs)
+
+        def replay(img_, txt_, vec_):
+            bufs[0].copy_(img_, non_blocking=True)
+            bufs[1].copy_(txt_, non_blocking=True)
+            bufs[2].copy_(vec_, non_blocking=True)
+            graph.replay()
+            return out
+
+        replay.graph = graph
+        return replay
+
     def expected_all_reduces(self) -> int:
         return 2 * self.cfg.n_double + self.cfg.n_single
 

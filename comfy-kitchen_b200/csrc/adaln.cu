@@ -334,7 +334,7 @@ int launch_warp(const NormArgs& a, cudaStream_t stream) {
     const bool has_mod = a.scale || a.shift;
     const int cache_mod = has_mod && (!a.scale || a.scale_group >= 32) && (!a.shift || a.shift_group >= 32);
     const size_t mod_bytes = cache_mod ? (size_t)round_up(a.D, 512) * 8 : 0;
-    const size_t budget = 208 * 1024 - mod_bytes;
+    const size_t budget = 225 * 1024 - mod_bytes;   // of the 227 KB a CTA can have; the barriers take the rest
     // warps per CTA and ring depth from the shared-memory budget: as many warps as fit with a ring of
     // two rows each, then a third row if there is room
     int warps = 0, ring = 2;
@@ -349,7 +349,7 @@ int launch_warp(const NormArgs& a, cudaStream_t stream) {
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev < 0 || dev >= 64 || !attr_set[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 216 * 1024);
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
         if (e != cudaSuccess) CK_FAIL((int)e, "adaln: cannot reserve shared memory: %s", cudaGetErrorString(e));
         if (dev >= 0 && dev < 64) attr_set[dev] = true;
     }
