@@ -22,6 +22,7 @@ SIGNATURES: dict[str, list] = {
     "ck_abi_version": [],
     "ck_check_device": [],
     "ck_gemm_device_status": [],
+    "ck_norm_device_status": [],
     "ck_set_option": [c_char_p, I],
     "launch_quantize_fp8_kernel": [P, P, P, I64, I, I, P],
     "launch_dequantize_fp8_kernel": [P, P, P, I64, I, I, P],

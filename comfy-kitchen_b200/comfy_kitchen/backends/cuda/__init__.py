@@ -482,3 +482,8 @@ def set_option(name: str, value: int) -> None:
 def gemm_device_status() -> int:
     """Synchronise and return the GEMM kernels' device status word (0 = fine)."""
     return int(_native.load().ck_gemm_device_status())
+
+
+def norm_device_status() -> int:
+    """Synchronise and return (then clear) the norm kernels' device-side status word; 0 = healthy."""
+    return int(_native.load().ck_norm_device_status())

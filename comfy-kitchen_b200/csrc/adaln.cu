@@ -460,3 +460,16 @@ extern "C" int launch_adaln_quantize_mxfp8_kernel(const void* x, const void* sca
                N, D, scale_group, shift_group, 0, eps, norm_kind != 0, 1};
     return launch_fused<kOutMxfp8>(a, dtype_code, stream);
 }
+
+// Reads and clears the device-side status word of the norm kernels (synchronises the device).
+// 0 = no bounded wait on a row copy ran out since the last call.
+extern "C" int ck_norm_device_status(void) {
+    int v = 0, zero = 0;
+    cudaError_t e = cudaDeviceSynchronize();
+    if (e != cudaSuccess) CK_FAIL((int)e, "norm status: %s", cudaGetErrorString(e));
+    e = cudaMemcpyFromSymbol(&v, ck::g_norm_status, sizeof(int));
+    if (e != cudaSuccess) CK_FAIL((int)e, "norm status: %s", cudaGetErrorString(e));
+    cudaMemcpyToSymbol(ck::g_norm_status, &zero, sizeof(int));
+    if (v != 0) ck::set_error("norm kernel: a bounded wait on a row copy ran out");
+    return v;
+}

@@ -5,8 +5,8 @@
  *
  * Conventions
  *   - every pointer is a DEVICE pointer on the current device unless stated;
- *     the library never allocates, frees or synchronises (ck_gemm_device_status
- *     excepted) and launches on the stream it is given;
+ *     the library never allocates, frees or synchronises (the two
+ *     ck_*_device_status calls excepted) and launches on the stream it is given;
  *   - dtype codes: 0 float32, 1 float16, 2 bfloat16, 5 float8_e4m3fn, 6 float8_e5m2
  *     (comfy_kitchen/backends/eager/quantization.py:33-41);
  *   - block scales use the 128x4 tiled layout of
@@ -146,6 +146,9 @@ int launch_adaln_quantize_mxfp8_kernel(const void* x, const void* scale, const v
                                        void* block_scales, int64_t N, int64_t D, int64_t scale_group,
                                        int64_t shift_group, float eps, int dtype_code, int norm_kind,
                                        ck_stream_t stream);
+/* Synchronises the device, returns and clears the norm kernels' status word
+ * (non-zero when a bounded device-side wait on a row copy ran out). */
+int ck_norm_device_status(void);
 
 #ifdef __cplusplus
 }

@@ -189,3 +189,11 @@ def test_rmsnorm_quantize(ck):
     q, sf = ck.rmsnorm_quantize_nvfp4(x, w, gs, 1e-6)
     q2, sf2 = ck.quantize_nvfp4(y, gs)
     assert torch.equal(q, q2) and torch.equal(sf.view(torch.uint8), sf2.view(torch.uint8))
+
+
+def test_norm_status_word_is_clear(ck):
+    """The norm kernels' bounded waits have not run out in anything this file launched."""
+    x = torch.randn(2, 300, 3072, device="cuda").bfloat16()
+    sc = (0.1 * torch.randn(2, 1, 3072, device="cuda")).bfloat16()
+    ck.adaln(x, sc, sc, 1e-6)
+    assert ck.norm_device_status() == 0
