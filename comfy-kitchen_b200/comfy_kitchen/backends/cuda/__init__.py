@@ -173,7 +173,10 @@ def scaled_mm_nvfp4(
     bias: torch.Tensor | None = None,
     out_dtype: torch.dtype | None = None,
     alpha: torch.Tensor | None = None,
+    out: torch.Tensor | None = None,
 ) -> torch.Tensor:
+    """``out`` (not in the reference's signature): a contiguous [M, N] tensor of ``out_dtype`` to write into,
+    e.g. a row range of a larger buffer."""
     a, b = _plain(a), _plain(b)
     block_scale_a, block_scale_b = _plain(block_scale_a), _plain(block_scale_b)
     if alpha is None:
@@ -202,7 +205,10 @@ def scaled_mm_nvfp4(
         bias_code = DTYPE_TO_CODE[bias.dtype]
     else:
         bias = None
-    out = torch.empty(m, n, dtype=out_dtype, device=a.device)
+    if out is None:
+        out = torch.empty(m, n, dtype=out_dtype, device=a.device)
+    else:
+        assert out.shape == (m, n) and out.dtype == out_dtype and out.is_contiguous() and out.device == a.device
     _native.call(
         "launch_scaled_mm_nvfp4_kernel", _ptr(a.contiguous()), _ptr(block_scale_a.contiguous().view(torch.uint8)),
         _ptr(b.contiguous()), _ptr(block_scale_b.contiguous().view(torch.uint8)), _ptr(out), _ptr(bias), bias_code,
@@ -324,6 +330,45 @@ def apply_rope_split_half(
     if xq.shape != xk.shape:
         return apply_rope_split_half1(xq, freqs_cis), apply_rope_split_half1(xk, freqs_cis)
     return _rope(xq, xk, freqs_cis, True)
+
+
+def qk_norm_rope(
+    qkv: torch.Tensor,
+    q_weight: torch.Tensor,
+    k_weight: torch.Tensor,
+    freqs_cis: torch.Tensor,
+    heads: int,
+    q_out: torch.Tensor | None = None,
+    k_out: torch.Tensor | None = None,
+    v_out: torch.Tensor | None = None,
+    token_offset: int = 0,
+    eps: float = 1e-6,
+) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """Per-head RMSNorm of q and k, RoPE of both and the relayout of q, k, v for attention in one pass.
+
+    qkv: [tokens, >= 3*heads*128], unit column stride (a column slice of a wider matrix is fine), columns
+    [q heads | k heads | v heads].  freqs_cis: fp32 [1, 1, total_tokens, 64, 2, 2].  Outputs (allocated when
+    not given): [1, heads, total_tokens, 128]; rows token_offset .. token_offset + tokens - 1 are written, so
+    two calls can fill the text and the image part of one joint sequence.
+    """
+    assert qkv.dim() == 2 and qkv.stride(1) == 1 and qkv.shape[1] >= 3 * heads * 128, "qkv must be [tokens, 3*heads*128]"
+    assert freqs_cis.dtype == torch.float32 and freqs_cis.is_contiguous() and freqs_cis.shape[-3:] == (64, 2, 2)
+    assert freqs_cis.dim() == 6 and freqs_cis.shape[0] == freqs_cis.shape[1] == 1, "freqs_cis must be [1, 1, N, 64, 2, 2]"
+    tokens, total = qkv.shape[0], freqs_cis.shape[2]
+    outs = []
+    for o in (q_out, k_out, v_out):
+        if o is None:
+            o = torch.empty((1, heads, total, 128), device=qkv.device, dtype=qkv.dtype)
+        assert o.shape == (1, heads, total, 128) and o.is_contiguous() and o.dtype == qkv.dtype
+        outs.append(o)
+    qw = q_weight.to(qkv.dtype).contiguous()
+    kw = k_weight.to(qkv.dtype).contiguous()
+    _native.call(
+        "launch_qk_norm_rope_kernel", _ptr(qkv), qkv.stride(0), _ptr(qw), _ptr(kw), _ptr(freqs_cis), _ptr(outs[0]),
+        _ptr(outs[1]), _ptr(outs[2]), tokens, heads, int(token_offset), total, float(eps), _code(qkv.dtype, "qk_norm_rope"),
+        _stream(qkv.device),
+    )
+    return outs[0], outs[1], outs[2]
 
 
 # ------------------------------------------------------------------ AdaLN / RMSNorm

@@ -6,8 +6,8 @@ the package's own operators so that one forward exercises every kernel of the pa
 
     LayerNorm + AdaLN modulation -> NVFP4   adaln_quantize_nvfp4      (fused front end)
     block-scaled GEMM, alpha and bias fused  scaled_mm_nvfp4
-    per-head RMSNorm of q and k              rmsnorm
-    rotary embedding of q and k              apply_rope
+    per-head RMSNorm of q and k, rotary      qk_norm_rope              (fused, writes the attention layout)
+    embedding, q/k/v relayout
     activation re-quantisation               quantize_nvfp4
 
 Attention itself is torch's scaled_dot_product_attention in bf16.
@@ -132,10 +132,10 @@ class QuantLinear:
         self.qdata, self.block_scales = ops.quantize_nvfp4(w.contiguous(), self.tensor_scale)
         self.bias = bias
 
-    def __call__(self, qx: torch.Tensor, sx: torch.Tensor, act_scale: torch.Tensor) -> torch.Tensor:
+    def __call__(self, qx: torch.Tensor, sx: torch.Tensor, act_scale: torch.Tensor, out=None) -> torch.Tensor:
         alpha = (act_scale * self.tensor_scale).reshape(1)
         return self.ops.scaled_mm_nvfp4(qx, self.qdata, act_scale, self.tensor_scale, sx, self.block_scales,
-                                        bias=self.bias, out_dtype=torch.bfloat16, alpha=alpha)
+                                        bias=self.bias, out_dtype=torch.bfloat16, alpha=alpha, out=out)
 
 
 def _weight_scale(w: torch.Tensor) -> torch.Tensor:
@@ -303,59 +303,52 @@ class DiTStack:
         qx, sx = self.ops.quantize_nvfp4(x.contiguous(), g)
         return qx, sx, g
 
-    def _attention(self, qkv: torch.Tensor, q_w: torch.Tensor, k_w: torch.Tensor) -> torch.Tensor:
-        """qkv [tokens, 3 * heads_local * head_dim] -> attention output [tokens, heads_local * head_dim]."""
+    def _attend(self, parts) -> torch.Tensor:
+        """parts: (qkv [tokens_i, >= 3*heads_local*head_dim], q_norm, k_norm) per segment of the joint sequence, in
+        token order.  One fused kernel per segment normalises q and k per head, applies the rotary embedding and
+        writes q, k, v in the layout attention reads; returns the attention output [tokens, heads_local*head_dim]."""
         c, hl = self.cfg, self.heads_local
-        t = qkv.shape[0]
-        q, k, v = qkv.view(t, 3, hl, c.head_dim).unbind(1)
-        q = self.ops.rmsnorm(q.contiguous(), q_w, c.eps)
-        k = self.ops.rmsnorm(k.contiguous(), k_w, c.eps)
-        q = q.permute(1, 0, 2)[None]  # [1, heads, tokens, head_dim]
-        k = k.permute(1, 0, 2)[None]
-        q, k = self.ops.apply_rope(q, k, self.freqs[:, :, :t])
-        o = F.scaled_dot_product_attention(q, k, v.permute(1, 0, 2)[None])
-        return o[0].permute(1, 0, 2).reshape(t, hl * c.head_dim)
+        total = sum(x[0].shape[0] for x in parts)
+        freqs = self.freqs if total == c.tokens else self.freqs[:, :, :total].contiguous()
+        q = k = v = None
+        off = 0
+        for qkv, q_w, k_w in parts:
+            q, k, v = self.ops.qk_norm_rope(qkv, q_w, k_w, freqs, hl, q, k, v, off, c.eps)
+            off += qkv.shape[0]
+        o = F.scaled_dot_product_attention(q, k, v)
+        return o[0].permute(1, 0, 2).reshape(total, hl * c.head_dim)   # one copy: [heads, tokens, d] -> rows
+
+    def _row_parallel(self, linears, inputs, sites) -> torch.Tensor:
+        """Row-parallel GEMMs of consecutive token segments written into one buffer, then one all-reduce."""
+        rows = [x.shape[0] for x in inputs]
+        y = torch.empty((sum(rows), self.cfg.hidden), device=inputs[0].device, dtype=torch.bfloat16)
+        off = 0
+        for lin, x, site, r in zip(linears, inputs, sites, rows):
+            qx, sx, g = self._quant(site, x)
+            lin(qx, sx, g, out=y[off:off + r])
+            off += r
+        return self.tp.all_reduce_sum(y)
 
     def _double_block(self, i: int, img: torch.Tensor, txt: torch.Tensor, vec: torch.Tensor):
         blk, tt = self.double[i], self.cfg.txt_tokens
-        mods = {s: self._modulation(blk[s], vec, 6) for s in ("img", "txt")}
+        order = ("txt", "img")   # token order of the joint sequence
+        mods = {s: self._modulation(blk[s], vec, 6) for s in order}
         xs = {"img": img, "txt": txt}
-        qkv = {}
-        for s in ("txt", "img"):
+        parts = []
+        for s in order:
             shift1, scale1 = mods[s][0], mods[s][1]
             qx, sx, g = self._norm_quant(f"d{i}.{s}.attn_in", xs[s], scale1, shift1)
-            qkv[s] = blk[s]["qkv"](qx, sx, g)
-        # joint attention over text then image tokens; q/k norms differ per stream, so normalise before joining
-        c, hl = self.cfg, self.heads_local
-        parts = {}
-        for s in ("txt", "img"):
-            t = qkv[s].shape[0]
-            q, k, v = qkv[s].view(t, 3, hl, c.head_dim).unbind(1)
-            parts[s] = (self.ops.rmsnorm(q.contiguous(), blk[s]["q_norm"], c.eps),
-                        self.ops.rmsnorm(k.contiguous(), blk[s]["k_norm"], c.eps), v)
-        q = torch.cat([parts["txt"][0], parts["img"][0]]).permute(1, 0, 2)[None]
-        k = torch.cat([parts["txt"][1], parts["img"][1]]).permute(1, 0, 2)[None]
-        v = torch.cat([parts["txt"][2], parts["img"][2]]).permute(1, 0, 2)[None]
-        q, k = self.ops.apply_rope(q, k, self.freqs)
-        o = F.scaled_dot_product_attention(q, k, v)[0].permute(1, 0, 2).reshape(c.tokens, hl * c.head_dim)
-        attn = {"txt": o[:tt], "img": o[tt:]}
-        # row-parallel projections of both streams, one all-reduce for the pair
-        ys = []
-        for s in ("txt", "img"):
-            qx, sx, g = self._quant(f"d{i}.{s}.attn_out", attn[s])
-            ys.append(blk[s]["proj"](qx, sx, g))
-        y = self.tp.all_reduce_sum(torch.cat(ys))
+            parts.append((blk[s]["qkv"](qx, sx, g), blk[s]["q_norm"], blk[s]["k_norm"]))
+        o = self._attend(parts)
+        y = self._row_parallel([blk[s]["proj"] for s in order], [o[:tt], o[tt:]], [f"d{i}.{s}.attn_out" for s in order])
         for s, ysl in (("txt", y[:tt]), ("img", y[tt:])):
             xs[s] = torch.addcmul(xs[s], mods[s][2], ysl)
-        # MLP
-        ys = []
-        for s in ("txt", "img"):
+        mids = []
+        for s in order:
             shift2, scale2 = mods[s][3], mods[s][4]
             qx, sx, g = self._norm_quant(f"d{i}.{s}.mlp_in", xs[s], scale2, shift2)
-            hmid = F.gelu(blk[s]["up"](qx, sx, g), approximate="tanh")
-            qx, sx, g = self._quant(f"d{i}.{s}.mlp_mid", hmid)
-            ys.append(blk[s]["down"](qx, sx, g))
-        y = self.tp.all_reduce_sum(torch.cat(ys))
+            mids.append(F.gelu(blk[s]["up"](qx, sx, g), approximate="tanh"))
+        y = self._row_parallel([blk[s]["down"] for s in order], mids, [f"d{i}.{s}.mlp_mid" for s in order])
         for s, ysl in (("txt", y[:tt]), ("img", y[tt:])):
             xs[s] = torch.addcmul(xs[s], mods[s][5], ysl)
         return xs["img"], xs["txt"]
@@ -364,12 +357,12 @@ class DiTStack:
         p, c, hl = self.single[i], self.cfg, self.heads_local
         shift, scale, gate = self._modulation(p, vec, 3)
         qx, sx, g = self._norm_quant(f"s{i}.in", x, scale, shift)
-        h1 = p["linear1"](qx, sx, g)
-        n_qkv = 3 * hl * c.head_dim
-        attn = self._attention(h1[:, :n_qkv], p["q_norm"], p["k_norm"])
-        mid = torch.cat([attn, F.gelu(h1[:, n_qkv:], approximate="tanh")], dim=1)
-        qx, sx, g = self._quant(f"s{i}.mid", mid)
-        y = self.tp.all_reduce_sum(p["linear2"](qx, sx, g))
+        h1 = p["linear1"](qx, sx, g)   # [tokens, q | k | v | mlp]: the fused kernel reads the first part in place
+        n_qkv, n_attn = 3 * hl * c.head_dim, hl * c.head_dim
+        mid = torch.empty((x.shape[0], n_attn + h1.shape[1] - n_qkv), device=x.device, dtype=x.dtype)
+        mid[:, :n_attn] = self._attend([(h1, p["q_norm"], p["k_norm"])])
+        torch.ops.aten.gelu.out(h1[:, n_qkv:], approximate="tanh", out=mid[:, n_attn:])
+        y = self._row_parallel([p["linear2"]], [mid], [f"s{i}.mid"])
         return torch.addcmul(x, gate, y)
 
     @torch.no_grad()

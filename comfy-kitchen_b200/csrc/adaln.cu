@@ -184,24 +184,27 @@ norm_stream_kernel(const NormArgs a, const int ring, const int64_t rows_per_cta,
 
             // statistics in one pass, shifted by the row's first element
             const float shift0 = a.rms ? 0.0f : Elem<T>::to_f32(xs[0]);
-            float s1a = 0.0f, s1b = 0.0f, s2a = 0.0f, s2b = 0.0f;
+            // two accumulator pairs, updated with sm_100's packed fp32 instructions (two IEEE operations each)
+            float2 s1 = make_float2(0.0f, 0.0f), s2 = s1;
+            const float2 nshift = make_float2(-shift0, -shift0);
 #pragma unroll 2
             for (int c = lane; c < nchunk; c += 32) {
                 float f[16];
                 lds16<T, false>(xs + c * 16, lane, f);
 #pragma unroll
-                for (int j = 0; j < 8; ++j) {
-                    const float d0 = f[j] - shift0, d1 = f[8 + j] - shift0;
-                    s1a += d0; s1b += d1;
-                    s2a = fmaf(d0, d0, s2a); s2b = fmaf(d1, d1, s2b);
+                for (int j = 0; j < 16; j += 2) {
+                    const float2 d = __fadd2_rn(make_float2(f[j], f[j + 1]), nshift);
+                    s1 = __fadd2_rn(s1, d);
+                    s2 = __ffma2_rn(d, d, s2);
                 }
             }
-            const float m1 = warp_sum(s1a + s1b) * inv_d;   // mean - shift0
-            const float m2 = warp_sum(s2a + s2b) * inv_d;   // E[(x - shift0)^2]
+            const float m1 = warp_sum(s1.x + s1.y) * inv_d;   // mean - shift0
+            const float m2 = warp_sum(s2.x + s2.y) * inv_d;   // E[(x - shift0)^2]
             const float mean = a.rms ? 0.0f : shift0 + m1;
             const float var = a.rms ? m2 : fmaxf(m2 - m1 * m1, 0.0f);
             const float rstd = rsqrtf(var + a.eps);
             const float nmr = -mean * rstd;
+            const float2 rstd2 = make_float2(rstd, rstd), nmr2 = make_float2(nmr, nmr);
 
             const T* __restrict__ sc = (!cache_mod && scale_g) ? scale_g + (row / a.scale_group) * D : nullptr;
             const T* __restrict__ sh = (!cache_mod && shift_g) ? shift_g + (row / a.shift_group) * D : nullptr;
@@ -222,10 +225,11 @@ norm_stream_kernel(const NormArgs a, const int ring, const int64_t rows_per_cta,
                         for (int j4 = 0; j4 < 4; ++j4) {
                             const float4 mu = *reinterpret_cast<const float4*>(s_mul + mod_pos(c, j4 * 4));
                             const float4 ad = *reinterpret_cast<const float4*>(s_add + mod_pos(c, j4 * 4));
-                            y[4 * j4 + 0] = fmaf(fmaf(f[4 * j4 + 0], rstd, nmr), mu.x, ad.x);
-                            y[4 * j4 + 1] = fmaf(fmaf(f[4 * j4 + 1], rstd, nmr), mu.y, ad.y);
-                            y[4 * j4 + 2] = fmaf(fmaf(f[4 * j4 + 2], rstd, nmr), mu.z, ad.z);
-                            y[4 * j4 + 3] = fmaf(fmaf(f[4 * j4 + 3], rstd, nmr), mu.w, ad.w);
+                            const float2 ya = __ffma2_rn(__ffma2_rn(make_float2(f[4 * j4 + 0], f[4 * j4 + 1]), rstd2, nmr2),
+                                                         make_float2(mu.x, mu.y), make_float2(ad.x, ad.y));
+                            const float2 yb = __ffma2_rn(__ffma2_rn(make_float2(f[4 * j4 + 2], f[4 * j4 + 3]), rstd2, nmr2),
+                                                         make_float2(mu.z, mu.w), make_float2(ad.z, ad.w));
+                            y[4 * j4 + 0] = ya.x; y[4 * j4 + 1] = ya.y; y[4 * j4 + 2] = yb.x; y[4 * j4 + 3] = yb.y;
                         }
                     } else {
                         float m[16], b[16];

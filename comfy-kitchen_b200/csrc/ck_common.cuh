@@ -322,8 +322,16 @@ __device__ __forceinline__ uint32_t nvfp4_codes8(const float (&v)[8], const Nvfp
     if (b.tot == 0.0f) return 0u;
     float q[8];
     if (b.fast) {
+        // div_by_reciprocal on pairs: sm_100's packed fp32 instructions do two IEEE operations each
+        const float2 r2 = make_float2(b.rtot, b.rtot), b2 = make_float2(b.tot, b.tot);
 #pragma unroll
-        for (int i = 0; i < 8; ++i) q[i] = div_by_reciprocal(v[i], b.tot, b.rtot);
+        for (int i = 0; i < 8; i += 2) {
+            const float2 a2 = make_float2(v[i], v[i + 1]);
+            const float2 q0 = __fmul2_rn(a2, r2);
+            const float2 e = __ffma2_rn(b2, q0, make_float2(-a2.x, -a2.y));
+            const float2 qq = __ffma2_rn(make_float2(-e.x, -e.y), r2, q0);
+            q[i] = qq.x; q[i + 1] = qq.y;
+        }
     } else {
 #pragma unroll
         for (int i = 0; i < 8; ++i) q[i] = __fdiv_rn(v[i], b.tot);

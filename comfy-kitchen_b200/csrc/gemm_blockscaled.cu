@@ -299,7 +299,8 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
     uint64_t* sf_full = empty + kStages;      // [kSfBufs]  (leader's) both CTAs' scales in TMEM -> MMA issuer
     uint64_t* tmem_full = sf_full + kSfBufs;  //            accumulator complete -> epilogue
     uint64_t* tmem_empty = tmem_full + 1;     //            (leader's) both CTAs' accumulators copied out -> MMA issuer
-    uint32_t* s_tmem_base = reinterpret_cast<uint32_t*>(tmem_empty + 1);
+    uint64_t* probe_bar = tmem_empty + 1;     //            timing experiments only
+    uint32_t* s_tmem_base = reinterpret_cast<uint32_t*>(probe_bar + 1);
     volatile int* s_abort = reinterpret_cast<volatile int*>(s_tmem_base + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -316,6 +317,7 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
         for (int b = 0; b < kSfBufs; ++b) mbar_init(&sf_full[b], 8);
         mbar_init(tmem_full, 1);
         mbar_init(tmem_empty, 2 * kEpiWarps);
+        mbar_init(probe_bar, 1u << 20);
         *s_abort = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -486,6 +488,7 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
                     // the pipe is busy with these for a while: look at the next k-tile's barrier now
                     if (kb == 1) ready = mbar_test_wait(&sf_full[(it + 1) % kSfBufs], ((it + 1) / kSfBufs) & 1);
                 }
+                if (CK_GEMM_PROBE & 256) tc_commit_pair(probe_bar);   // timing experiment: what one more commit costs
                 tc_commit_pair(&empty[s]);                      // stage and scale buffer reusable once these MMAs are done
                 if (kt == k_tiles - 1) { tc_commit_pair(tmem_full); CK_TS(0, 240 + local_tile, 2); }  // accumulators complete
 #if CK_GEMM_PROBE & 8

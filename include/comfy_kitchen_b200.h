@@ -112,7 +112,18 @@ int ck_gemm_device_status(void);
 /* ---- RoPE ----
  * Replaces launch_apply_rope_kernel (dlpack_bindings.cpp:75-101,
  * ops/apply_rope.cu:358-404).  x is [batch, dim1, dim2, head_dim] with the given
- * element strides (used for input and output alike); freqs is
+ * element strides (used for input and output alike);
+
+/* Per-head RMSNorm of q and k + RoPE of both + relayout of q, k, v for attention, one pass.
+ * No single counterpart in the reference: it composes apply_rope (backends/eager/rope.py:9-32)
+ * with torch's rms_norm and the caller's permutes.  qkv: [tokens, >= 3*heads*128] with row_stride
+ * elements between tokens, columns [q heads | k heads | v heads]; q_weight, k_weight: [128] in
+ * qkv's dtype (bf16 or fp16); freqs: fp32 [total_tokens, 64, 2, 2]; q_out, k_out, v_out:
+ * [heads, total_tokens, 128]; rows token_offset .. token_offset+tokens-1 of every head are written. */
+int launch_qk_norm_rope_kernel(const void* qkv, int64_t row_stride, const void* q_weight, const void* k_weight,
+                               const float* freqs, void* q_out, void* k_out, void* v_out, int64_t tokens,
+                               int64_t heads, int64_t token_offset, int64_t total_tokens, float eps,
+                               int dtype_code, ck_stream_t stream); freqs is
  * [freqs_batch, freqs_dim1, freqs_dim2, head_dim/2, 2, 2], each leading dim 1
  * (broadcast) or >= x's.  xk / xk_out may both be NULL.
  * Arithmetic: backends/eager/rope.py:9-32. */

@@ -17,9 +17,13 @@ def dequantize_nvfp4(qx, per_tensor_scale, block_scales, output_type=torch.bfloa
 
 
 def scaled_mm_nvfp4(a, b, tensor_scale_a, tensor_scale_b, block_scale_a, block_scale_b, bias=None,
-                    out_dtype=torch.bfloat16, alpha=None):
-    return orc.scaled_mm_nvfp4(a, b, tensor_scale_a, tensor_scale_b, block_scale_a, block_scale_b,
-                               bias=bias, out_dtype=out_dtype, alpha=alpha)
+                    out_dtype=torch.bfloat16, alpha=None, out=None):
+    y = orc.scaled_mm_nvfp4(a, b, tensor_scale_a, tensor_scale_b, block_scale_a, block_scale_b,
+                            bias=bias, out_dtype=out_dtype, alpha=alpha)
+    if out is not None:
+        out.copy_(y)
+        return out
+    return y
 
 
 def adaln(x, scale, shift, eps=1e-6):
@@ -38,3 +42,21 @@ def rmsnorm(x, weight=None, eps=1e-6):
 
 def apply_rope(xq, xk, freqs_cis):
     return orc.apply_rope(xq.contiguous(), xk.contiguous(), freqs_cis.contiguous())
+
+
+def qk_norm_rope(qkv, q_weight, k_weight, freqs_cis, heads, q_out=None, k_out=None, v_out=None, token_offset=0,
+                 eps=1e-6):
+    """rms_norm (fp32, one rounding) of q and k per head, then the oracle's rope, then the attention layout."""
+    t, total = qkv.shape[0], freqs_cis.shape[2]
+    q, k, v = qkv[:, :3 * heads * 128].reshape(t, 3, heads, 128).unbind(1)
+    q = rmsnorm(q, q_weight, eps).permute(1, 0, 2)[None].contiguous()
+    k = rmsnorm(k, k_weight, eps).permute(1, 0, 2)[None].contiguous()
+    f = freqs_cis[:, :, token_offset:token_offset + t].contiguous()
+    q, k = orc.apply_rope(q, k, f)
+    outs = []
+    for o, val in ((q_out, q), (k_out, k), (v_out, v.permute(1, 0, 2)[None])):
+        if o is None:
+            o = torch.zeros((1, heads, total, 128), dtype=qkv.dtype)
+        o[:, :, token_offset:token_offset + t] = val
+        outs.append(o)
+    return tuple(outs)

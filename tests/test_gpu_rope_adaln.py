@@ -197,3 +197,30 @@ def test_norm_status_word_is_clear(ck):
     sc = (0.1 * torch.randn(2, 1, 3072, device="cuda")).bfloat16()
     ck.adaln(x, sc, sc, 1e-6)
     assert ck.norm_device_status() == 0
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_qk_norm_rope_matches_composition(ck, dtype):
+    """Fused per-head RMSNorm + RoPE + relayout against rms_norm (fp32) -> oracle rope -> permute; two calls fill a
+    joint sequence (text then image tokens); the qkv of the second call is a column slice of a wider matrix."""
+    from tests import dit_oracle_ops as ops
+
+    g = torch.Generator().manual_seed(3)
+    heads, t_txt, t_img = 3, 37, 210
+    total = t_txt + t_img
+    ang = torch.rand(total, 64, generator=g) * 6.28
+    f = torch.stack([torch.stack([ang.cos(), -ang.sin()], -1), torch.stack([ang.sin(), ang.cos()], -1)], -2)[None, None].contiguous()
+    qkv_txt = (2 * torch.randn(t_txt, 3 * heads * 128, generator=g)).to(dtype)
+    wide = (2 * torch.randn(t_img, 3 * heads * 128 + 256, generator=g)).to(dtype)
+    qw = (1 + 0.1 * torch.randn(128, generator=g)).to(dtype)
+    kw = (1 + 0.1 * torch.randn(128, generator=g)).to(dtype)
+    want = ops.qk_norm_rope(qkv_txt, qw, kw, f, heads, None, None, None, 0, 1e-6)
+    want = ops.qk_norm_rope(wide[:, :3 * heads * 128], qw, kw, f, heads, *want, t_txt, 1e-6)
+    got = ck.qk_norm_rope(qkv_txt.cuda(), qw.cuda(), kw.cuda(), f.cuda(), heads, None, None, None, 0, 1e-6)
+    wide_d = wide.cuda()
+    got = ck.qk_norm_rope(wide_d[:, :3 * heads * 128], qw.cuda(), kw.cuda(), f.cuda(), heads, *got, t_txt, 1e-6)
+    assert got[0].shape == (1, heads, total, 128)
+    assert torch.equal(got[2].cpu(), want[2])                       # v is a copy
+    for a, b in zip(got[:2], want[:2]):
+        # the norm's rounding to the 16-bit dtype can differ by one ulp between summation orders and is then rotated
+        torch.testing.assert_close(a.float().cpu(), b.float(), rtol=2e-2, atol=2e-2)
