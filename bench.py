@@ -359,6 +359,11 @@ def run_case(args) -> None:
         sc = (0.1 * torch.randn(1, 1, K, device=dev, generator=g)).bfloat16()
         sh = (0.1 * torch.randn(1, 1, K, device=dev, generator=g)).bfloat16()
         work, fn = 2.5625 * M * K, (lambda: ck.adaln_quantize_nvfp4(xs, sc, sh, gx, 1e-6))
+    elif args.case == "adaln":
+        xs = x.view(1, M, K)
+        sc = (0.1 * torch.randn(1, 1, K, device=dev, generator=g)).bfloat16()
+        sh = (0.1 * torch.randn(1, 1, K, device=dev, generator=g)).bfloat16()
+        work, fn = 4.0 * M * K, (lambda: ck.adaln(xs, sc, sh, 1e-6))
     elif args.case == "rope":
         q = torch.randn(M // 4608 or 1, 24, 4608, 128, device=dev, generator=g).bfloat16()
         k = torch.randn_like(q)
@@ -380,6 +385,32 @@ def run_case(args) -> None:
 
 
 # ----------------------------------------------------------------------------- DiT stack (tensor parallel)
+
+
+def dit_forward_ms(device, steps: int = 3) -> dict:
+    """ms per forward of the full synthetic stack on one GPU (one CUDA graph per forward), for the default line."""
+    from comfy_kitchen.dit_stack import DiTConfig, DiTStack, gemm_flops_per_forward
+
+    cfg = DiTConfig()
+    stack = DiTStack(cfg, device)
+    g = torch.Generator().manual_seed(11)
+    img = torch.randn(cfg.img_tokens, cfg.hidden, generator=g).bfloat16().to(device)
+    txt = torch.randn(cfg.txt_tokens, cfg.hidden, generator=g).bfloat16().to(device)
+    vec = torch.randn(1, cfg.hidden, generator=g).bfloat16().to(device)
+    stack.calibrate(img, txt, vec)
+    run = stack.capture(img, txt, vec)
+    for _ in range(3):
+        run(img, txt, vec)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        run(img, txt, vec)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / steps
+    return {"ms_per_forward": round(ms, 2), "tp": 1, "blocks": [cfg.n_double, cfg.n_single], "tokens": cfg.tokens,
+            "linear_tflops": round(gemm_flops_per_forward(cfg) / (ms * 1e-3) / 1e12, 1), "launch": "CUDA graph"}
 
 
 def run_dit(args) -> None:
@@ -477,10 +508,11 @@ def main() -> None:
     ap.add_argument("--no-extras", action="store_true", help="skip the quantizer sweep, e2e and CPU legs")
     ap.add_argument("--case", default=None,
                     help="run one kernel instead of the sweep (for profiling): gemm_nvfp4, gemm_mxfp8, quantize_nvfp4, "
-                         "dequantize_nvfp4, quantize_mxfp8, quantize_fp8, adaln_quantize_nvfp4, rope")
+                         "dequantize_nvfp4, quantize_mxfp8, quantize_fp8, adaln, adaln_quantize_nvfp4, rope")
     ap.add_argument("--workload", default="linear", choices=["linear", "dit"],
                     help="linear: the NVFP4 linear sweep (default); dit: the tensor-parallel DiT stack, ms per forward")
     ap.add_argument("--dit-blocks", default="19,38", help="double,single block counts for --workload dit")
+    ap.add_argument("--no-dit", action="store_true", help="skip the DiT-stack leg of the default line")
     ap.add_argument("--no-graph", action="store_true", help="--workload dit: launch eagerly instead of replaying a CUDA graph")
     ap.add_argument("--m", type=int, default=9216)
     ap.add_argument("--n", type=int, default=9216)
@@ -555,7 +587,10 @@ def main() -> None:
         "gpu_launches": 24 * args.steps,
         "clocks": clocks,
         "roofline": {"bound": "tensor", "achieved": round(achieved, 1), "peak": round(peak, 1), "unit": "TFLOP/s",
-                     "frac": round(achieved / peak, 4), "traffic": None,
+                     "frac": round(achieved / peak, 4),
+                     # dram__bytes_read + write of one launch under ncu (profiles/gemm_blockscaled_nvfp4_4608x9216x3072.md)
+                     "traffic": 59.6e6, "traffic_case": "M4608 N9216 K3072: 24.0 MB read (= operands + scales), 35.6 MB "
+                     "written of the 84.9 MB output (the rest still in L2 at kernel end)",
                      "kernel": "gemm_blockscaled_kernel<fp4>", "peak_source": f"4 x bf16_tflops_sustained ({peaks['_source']})"},
     }
 
@@ -575,6 +610,9 @@ def main() -> None:
         del wl.host_in, wl.host_out
         # ---- memory-bound kernels, largest sweep shape
         line["quantizers"] = {"shape": [65536, 12288], "unit": "GB/s", "hbm_peak": peaks["hbm_gbs"], **quantizer_sweep(device)}
+        # ---- the DiT stack of configs[4] on this GPU (tp1; `--workload dit` runs it tensor-parallel)
+        if not args.no_dit:
+            line["dit_stack"] = dit_forward_ms(device, steps=3)
         # ---- CPU oracle on a bounded sample
         threads = os.cpu_count() or 1
         cpu_sample_step(512, threads)

@@ -142,6 +142,52 @@ def quantize_nvfp4(
     return qx, sx.view(torch.float8_e4m3fn)
 
 
+def _segment(t: torch.Tensor, what: str):
+    """(tensor, cols, group, group_stride, row_stride, rows) of one gather-quantizer segment."""
+    if t.dim() == 2:      # [rows, cols], unit column stride, any row pitch
+        assert t.stride(1) == 1, f"{what}: 2-D segments need unit column stride"
+        return t, t.shape[1], t.shape[1], 0, t.stride(0), t.shape[0]
+    if t.dim() == 3:      # [groups, rows, d] read as [rows, groups * d]  (attention's [heads, tokens, head_dim])
+        assert t.stride(2) == 1, f"{what}: 3-D segments need unit stride in the last dim"
+        return t, t.shape[0] * t.shape[2], t.shape[2], t.stride(0), t.stride(1), t.shape[1]
+    raise ValueError(f"{what}: segments are 2-D [rows, cols] or 3-D [groups, rows, d]")
+
+
+def quantize_nvfp4_gather(
+    segments, per_tensor_scale: torch.Tensor, hi_first: bool = True
+) -> tuple[torch.Tensor, torch.Tensor]:
+    """quantize_nvfp4 of the column concatenation of one or two segments, without materialising it.
+
+    segments: [(tensor, activation), ...] with activation None or "gelu_tanh"; a tensor is 2-D [rows, cols] with
+    unit column stride (any row pitch: a column slice is fine) or 3-D [groups, rows, d], read as [rows, groups*d].
+    Widths and strides must be multiples of 16 elements.  With no activation the result equals
+    quantize_nvfp4(torch.cat(...)) byte for byte.
+    """
+    assert 1 <= len(segments) <= 2, "one or two segments"
+    segs = []
+    for t, act in segments:
+        assert act in (None, "gelu_tanh"), f"unknown activation {act!r}"
+        segs.append((*_segment(t, "quantize_nvfp4_gather"), 0 if act is None else 1))
+    rows = segs[0][5]
+    assert all(sg[5] == rows for sg in segs), "segments must have the same number of rows"
+    dtype, device = segs[0][0].dtype, segs[0][0].device
+    assert all(sg[0].dtype == dtype for sg in segs)
+    cols = sum(sg[1] for sg in segs)
+    qx = torch.empty((rows, cols // 2), device=device, dtype=torch.uint8)
+    sx = torch.empty((roundup(rows, 128), roundup(cols // 16, 4)), device=device, dtype=torch.uint8)
+    g = _scalar_on(per_tensor_scale, device)
+    flat = []
+    for i in range(2):
+        if i < len(segs):
+            t, c, grp, gs, rs, _, act = segs[i]
+            flat += [_ptr(t), c, grp, gs, rs, act]
+        else:
+            flat += [None, 0, 16, 0, 16, 0]
+    _native.call("launch_quantize_nvfp4_gather_kernel", *flat, _ptr(g), _ptr(qx), _ptr(sx), rows,
+                 _code(dtype, "quantize_nvfp4_gather"), bool(hi_first), _stream(device))
+    return qx, sx.view(torch.float8_e4m3fn)
+
+
 def dequantize_nvfp4(
     qx: torch.Tensor,
     per_tensor_scale: torch.Tensor,

@@ -8,7 +8,8 @@ the package's own operators so that one forward exercises every kernel of the pa
     block-scaled GEMM, alpha and bias fused  scaled_mm_nvfp4
     per-head RMSNorm of q and k, rotary      qk_norm_rope              (fused, writes the attention layout)
     embedding, q/k/v relayout
-    activation re-quantisation               quantize_nvfp4
+    activation re-quantisation               quantize_nvfp4_gather     (reads attention's layout / a column
+                                                                       slice in place, GELU fused)
 
 Attention itself is torch's scaled_dot_product_attention in bf16.
 
@@ -298,9 +299,19 @@ class DiTStack:
         qx, sx = self.ops.adaln_quantize_nvfp4(x[None], scale, shift, g, self.cfg.eps)
         return qx, sx, g
 
-    def _quant(self, site: str, x: torch.Tensor):
-        g = self._act_scale(site, x)
-        qx, sx = self.ops.quantize_nvfp4(x.contiguous(), g)
+    def _quant(self, site: str, segments):
+        """NVFP4 of the column concatenation of the segments ((tensor, activation) pairs: see
+        quantize_nvfp4_gather), read in place.  Without a static scale the maximum is taken from the
+        materialised activation first (calibration only)."""
+        if self.sites.recording or site not in self.sites.static:
+            cols = []
+            for t, act in segments:
+                m = t if t.dim() == 2 else t.permute(1, 0, 2).reshape(t.shape[1], -1)
+                cols.append(F.gelu(m, approximate="tanh") if act == "gelu_tanh" else m)
+            g = self._act_scale(site, amax=torch.stack([c.float().abs().max() for c in cols]).max())
+        else:
+            g = self.sites.static[site]
+        qx, sx = self.ops.quantize_nvfp4_gather(segments, g)
         return qx, sx, g
 
     def _attend(self, parts) -> torch.Tensor:
@@ -315,16 +326,16 @@ class DiTStack:
         for qkv, q_w, k_w in parts:
             q, k, v = self.ops.qk_norm_rope(qkv, q_w, k_w, freqs, hl, q, k, v, off, c.eps)
             off += qkv.shape[0]
-        o = F.scaled_dot_product_attention(q, k, v)
-        return o[0].permute(1, 0, 2).reshape(total, hl * c.head_dim)   # one copy: [heads, tokens, d] -> rows
+        return F.scaled_dot_product_attention(q, k, v)[0]   # [heads_local, tokens, head_dim]; the quantizer reads it in place
 
     def _row_parallel(self, linears, inputs, sites) -> torch.Tensor:
-        """Row-parallel GEMMs of consecutive token segments written into one buffer, then one all-reduce."""
-        rows = [x.shape[0] for x in inputs]
-        y = torch.empty((sum(rows), self.cfg.hidden), device=inputs[0].device, dtype=torch.bfloat16)
+        """Row-parallel GEMMs of consecutive token ranges written into one buffer, then one all-reduce.
+        inputs: per range the list of (tensor, activation) segments that make up the GEMM's input columns."""
+        rows = [segs[0][0].shape[-2] for segs in inputs]
+        y = torch.empty((sum(rows), self.cfg.hidden), device=inputs[0][0][0].device, dtype=torch.bfloat16)
         off = 0
-        for lin, x, site, r in zip(linears, inputs, sites, rows):
-            qx, sx, g = self._quant(site, x)
+        for lin, segs, site, r in zip(linears, inputs, sites, rows):
+            qx, sx, g = self._quant(site, segs)
             lin(qx, sx, g, out=y[off:off + r])
             off += r
         return self.tp.all_reduce_sum(y)
@@ -340,14 +351,15 @@ class DiTStack:
             qx, sx, g = self._norm_quant(f"d{i}.{s}.attn_in", xs[s], scale1, shift1)
             parts.append((blk[s]["qkv"](qx, sx, g), blk[s]["q_norm"], blk[s]["k_norm"]))
         o = self._attend(parts)
-        y = self._row_parallel([blk[s]["proj"] for s in order], [o[:tt], o[tt:]], [f"d{i}.{s}.attn_out" for s in order])
+        y = self._row_parallel([blk[s]["proj"] for s in order], [[(o[:, :tt], None)], [(o[:, tt:], None)]],
+                               [f"d{i}.{s}.attn_out" for s in order])
         for s, ysl in (("txt", y[:tt]), ("img", y[tt:])):
             xs[s] = torch.addcmul(xs[s], mods[s][2], ysl)
         mids = []
         for s in order:
             shift2, scale2 = mods[s][3], mods[s][4]
             qx, sx, g = self._norm_quant(f"d{i}.{s}.mlp_in", xs[s], scale2, shift2)
-            mids.append(F.gelu(blk[s]["up"](qx, sx, g), approximate="tanh"))
+            mids.append([(blk[s]["up"](qx, sx, g), "gelu_tanh")])   # GELU happens inside the quantizer
         y = self._row_parallel([blk[s]["down"] for s in order], mids, [f"d{i}.{s}.mlp_mid" for s in order])
         for s, ysl in (("txt", y[:tt]), ("img", y[tt:])):
             xs[s] = torch.addcmul(xs[s], mods[s][5], ysl)
@@ -358,11 +370,10 @@ class DiTStack:
         shift, scale, gate = self._modulation(p, vec, 3)
         qx, sx, g = self._norm_quant(f"s{i}.in", x, scale, shift)
         h1 = p["linear1"](qx, sx, g)   # [tokens, q | k | v | mlp]: the fused kernel reads the first part in place
-        n_qkv, n_attn = 3 * hl * c.head_dim, hl * c.head_dim
-        mid = torch.empty((x.shape[0], n_attn + h1.shape[1] - n_qkv), device=x.device, dtype=x.dtype)
-        mid[:, :n_attn] = self._attend([(h1, p["q_norm"], p["k_norm"])])
-        torch.ops.aten.gelu.out(h1[:, n_qkv:], approximate="tanh", out=mid[:, n_attn:])
-        y = self._row_parallel([p["linear2"]], [mid], [f"s{i}.mid"])
+        n_qkv = 3 * hl * c.head_dim
+        o = self._attend([(h1, p["q_norm"], p["k_norm"])])
+        # linear2's input columns: [attention output | GELU(mlp part of h1)], both read where they are
+        y = self._row_parallel([p["linear2"]], [[(o, None), (h1[:, n_qkv:], "gelu_tanh")]], [f"s{i}.mid"])
         return torch.addcmul(x, gate, y)
 
     @torch.no_grad()

@@ -102,6 +102,94 @@ quantize_nvfp4_kernel(const T* __restrict__ x, const float* __restrict__ global_
     }
 }
 
+// ---- quantizer with a gathered source and an optional activation ------------------------------
+// The logical [rows, cols] input is the concatenation along columns of up to two segments.  Element
+// (row, c) of a segment lives at  base + (c / group) * group_stride + row * row_stride + c % group
+// (elements): group = the segment's width and group_stride = 0 describe a row-major matrix with any row
+// pitch (a column slice of a wider matrix, say); group = head_dim, group_stride = tokens * head_dim,
+// row_stride = head_dim describe attention's [heads, tokens, head_dim] output read as [tokens,
+// heads * head_dim].  A segment may pass through GELU (tanh form) first; the activation is rounded to the
+// input dtype before it is quantized, as if it had been stored.  Same tiling and the same block encoder as
+// quantize_nvfp4_kernel, so without an activation the bytes equal a gather followed by that kernel.
+struct QuantSegment {
+    const void* base;
+    int64_t cols, group, group_stride, row_stride;
+    int act;   // 0 none, 1 gelu(tanh)
+};
+
+__device__ __forceinline__ float gelu_tanh(float x) {
+    const float kBeta = 0.7978845608028654f, kKappa = 0.044715f;   // sqrt(2/pi)
+    const float inner = kBeta * (x + kKappa * (x * x * x));
+    return 0.5f * x * (1.0f + tanhf(inner));
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kThreads)
+quantize_nvfp4_gather_kernel(const QuantSegment s0, const QuantSegment s1, const float* __restrict__ global_scale,
+                             uint8_t* __restrict__ q, uint8_t* __restrict__ sf, int64_t rows, int64_t cols,
+                             int64_t sf_cpad, bool hi_first) {
+    __shared__ __align__(16) uint8_t s_sf[kSfTiles * 512];
+    const int tid = threadIdx.x;
+    const int blk = tid & 15, sub = tid >> 4;
+    const int64_t row0 = (int64_t)blockIdx.y * kTileRows;
+    const int64_t col = (int64_t)blockIdx.x * kTileCols + blk * 16;
+    const Nvfp4Ctx ctx = nvfp4_ctx(__ldg(global_scale));
+    reinterpret_cast<uint2*>(s_sf)[tid] = make_uint2(0u, 0u);
+    __syncthreads();
+
+    const bool col_ok = col < cols;
+    // which segment this thread's blocks come from, and where they start in it (a block never straddles
+    // segments or groups: all widths are multiples of 16)
+    const bool second = col >= s0.cols;
+    const QuantSegment& sg = second ? s1 : s0;
+    const int64_t c = second ? col - s0.cols : col;
+    const T* src = nullptr;
+    int64_t row_stride = 0;
+    int act = 0;
+    if (col_ok) {
+        src = static_cast<const T*>(sg.base) + (c / sg.group) * sg.group_stride + c % sg.group;
+        row_stride = sg.row_stride;
+        act = sg.act;
+    }
+    constexpr int kUnroll = 4;
+#pragma unroll 1
+    for (int it = 0; it < kTileRows / kRowsPerStep; it += kUnroll) {
+        Raw16<T> raw[kUnroll];
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u) {
+            const int64_t row = row0 + (it + u) * kRowsPerStep + sub;
+            if (col_ok && row < rows) load_raw16<T>(src + row * row_stride, raw[u]);
+            else zero_raw16<T>(raw[u]);
+        }
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u) {
+            const int r_in_tile = (it + u) * kRowsPerStep + sub;
+            const int64_t row = row0 + r_in_tile;
+            float v[16];
+            unpack16(raw[u], v);
+            if (act == 1) {
+#pragma unroll
+                for (int i = 0; i < 16; ++i) v[i] = Elem<T>::round(gelu_tanh(v[i]));
+            }
+            uint32_t s8;
+            const uint2 packed = nvfp4_encode_block<false>(v, ctx, hi_first, s8);
+            if (col_ok && row < rows) {
+                *reinterpret_cast<uint2*>(q + row * (cols >> 1) + (col >> 1)) = packed;
+                s_sf[(blk >> 2) * 512 + sf_tile_offset(r_in_tile, blk & 3)] = (uint8_t)s8;
+            }
+        }
+    }
+    __syncthreads();
+    if (tid < kSfTiles * 32) {
+        const int t = tid >> 5;
+        const int64_t tile_col = ((int64_t)blockIdx.x * kTileCols >> 6) + t;
+        if (tile_col < (sf_cpad >> 2)) {
+            uint8_t* dst = sf + ((int64_t)blockIdx.y * (sf_cpad >> 2) + tile_col) * 512 + (tid & 31) * 16;
+            *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(s_sf + t * 512 + (tid & 31) * 16);
+        }
+    }
+}
+
 // Dequantize: lut[code] * (g * s8), each product rounded to the output dtype as
 // the eager reference does (backends/eager/quantization.py:213-219).  Same tiling
 // as the quantizer: a thread expands one block (8 bytes in, one 256-bit store out).
@@ -237,4 +325,46 @@ extern "C" int launch_dequantize_nvfp4_kernel(const void* input, const void* glo
     case CK_BF16: return launch_dequantize<__nv_bfloat16>(q, g, sf, output, num_rows, num_cols, hi_first, stream);
     default: CK_FAIL(CK_ERR_DTYPE, "dequantize_nvfp4: unsupported output dtype code %d", output_dtype_code);
     }
+}
+
+// NVFP4 quantize of [seg0 | seg1] (seg1 optional: cols1 = 0), each segment addressed as
+//   base + (c / group) * group_stride + row * row_stride + c % group   (elements of the input dtype)
+// and optionally passed through GELU(tanh) (act = 1) first.  No counterpart in the reference: it replaces a
+// gather / concatenation / activation kernel followed by launch_quantize_nvfp4_kernel.  Widths, groups and
+// strides must be multiples of 16 elements and the bases 32-byte aligned; rows are not padded.
+extern "C" int launch_quantize_nvfp4_gather_kernel(const void* base0, int64_t cols0, int64_t group0, int64_t group_stride0,
+                                                   int64_t row_stride0, int act0, const void* base1, int64_t cols1,
+                                                   int64_t group1, int64_t group_stride1, int64_t row_stride1, int act1,
+                                                   const void* global_scale, void* output, void* block_scales,
+                                                   int64_t num_rows, int input_dtype_code, bool hi_first,
+                                                   cudaStream_t stream) {
+    using namespace ck;
+    if (!base0 || !global_scale || !output || !block_scales || (cols1 > 0 && !base1))
+        CK_FAIL(CK_ERR_NULL, "quantize_nvfp4_gather: null pointer");
+    const int64_t cols = cols0 + (cols1 > 0 ? cols1 : 0);
+    auto seg_ok = [](const void* b, int64_t c, int64_t g, int64_t gs, int64_t rs, int act) {
+        return c > 0 && g > 0 && c % 16 == 0 && g % 16 == 0 && c % g == 0 && gs % 16 == 0 && rs % 16 == 0 && gs >= 0 &&
+               rs > 0 && (act == 0 || act == 1) && (reinterpret_cast<uintptr_t>(b) & 31u) == 0;
+    };
+    if (num_rows <= 0 || !seg_ok(base0, cols0, group0, group_stride0, row_stride0, act0) ||
+        (cols1 > 0 && !seg_ok(base1, cols1, group1, group_stride1, row_stride1, act1)))
+        CK_FAIL(CK_ERR_SHAPE, "quantize_nvfp4_gather: widths, groups and strides must be positive multiples of 16 elements, "
+                              "bases 32-byte aligned, act 0 or 1");
+    if (ceil_div(num_rows, 128) > 65535) CK_FAIL(CK_ERR_SHAPE, "quantize_nvfp4_gather: more than 65535*128 rows");
+    if (!aligned16(block_scales) || (reinterpret_cast<uintptr_t>(output) & 7u))
+        CK_FAIL(CK_ERR_ALIGN, "quantize_nvfp4_gather: outputs must be 16-byte (scales) / 8-byte (codes) aligned");
+    if (input_dtype_code != CK_BF16 && input_dtype_code != CK_F16)
+        CK_FAIL(CK_ERR_DTYPE, "quantize_nvfp4_gather: dtype code %d (bf16 or fp16)", input_dtype_code);
+    const QuantSegment s0{base0, cols0, group0, group_stride0, row_stride0, act0};
+    const QuantSegment s1{base1, cols1 > 0 ? cols1 : 0, cols1 > 0 ? group1 : 16, group_stride1, row_stride1, act1};
+    const int64_t sf_cpad = round_up(cols / 16, 4);
+    dim3 grid((unsigned)ceil_div(sf_cpad * 16, kTileCols), (unsigned)ceil_div(num_rows, kTileRows));
+    auto* g = static_cast<const float*>(global_scale);
+    auto* q = static_cast<uint8_t*>(output);
+    auto* sf = static_cast<uint8_t*>(block_scales);
+    if (input_dtype_code == CK_BF16)
+        quantize_nvfp4_gather_kernel<__nv_bfloat16><<<grid, kThreads, 0, stream>>>(s0, s1, g, q, sf, num_rows, cols, sf_cpad, hi_first);
+    else
+        quantize_nvfp4_gather_kernel<__half><<<grid, kThreads, 0, stream>>>(s0, s1, g, q, sf, num_rows, cols, sf_cpad, hi_first);
+    return launch_status("quantize_nvfp4_gather");
 }

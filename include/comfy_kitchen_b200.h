@@ -62,7 +62,21 @@ int launch_dequantize_fp8_kernel(const void* input, void* output, const void* sc
 /* ---- NVFP4 ----
  * Replaces launch_quantize_nvfp4_kernel / launch_dequantize_nvfp4_kernel
  * (dlpack_bindings.cpp:102-124, ops/quantize_nvfp4.cu:323-435).
- * input [orig_rows, orig_cols]; output bytes [num_rows, num_cols/2]; block_scales
+ * input [orig_rows, orig_cols];
+
+/* NVFP4 quantize of the column concatenation [seg0 | seg1] (seg1 optional: cols1 = 0).  Element (row, c) of a
+ * segment is read at  base + (c / group) * group_stride + row * row_stride + c % group  (elements of the input
+ * dtype, bf16 or fp16), so a column slice of a wider matrix or attention's [heads, tokens, head_dim] output can be
+ * quantized in place; act = 1 applies GELU (tanh form), rounded to the input dtype, first.  No counterpart in
+ * the reference: it stands for gather / concatenate / activation kernels followed by
+ * launch_quantize_nvfp4_kernel (whose bytes it reproduces when act = 0).  Widths, groups and strides are
+ * multiples of 16 elements, bases 32-byte aligned; output and block_scales as for launch_quantize_nvfp4_kernel
+ * with num_cols = cols0 + cols1 and no row padding. */
+int launch_quantize_nvfp4_gather_kernel(const void* base0, int64_t cols0, int64_t group0, int64_t group_stride0,
+                                        int64_t row_stride0, int act0, const void* base1, int64_t cols1,
+                                        int64_t group1, int64_t group_stride1, int64_t row_stride1, int act1,
+                                        const void* global_scale, void* output, void* block_scales,
+                                        int64_t num_rows, int input_dtype_code, bool hi_first, ck_stream_t stream); output bytes [num_rows, num_cols/2]; block_scales
  * tiled [roundup(num_rows,128), roundup(num_cols/16,4)]; num_* >= orig_* (the
  * excess reads as zero; pad_16x of the Python API).  epsilon is accepted and
  * ignored, as in the reference.  Arithmetic: backends/eager/quantization.py:117-221. */

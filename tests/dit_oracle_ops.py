@@ -60,3 +60,17 @@ def qk_norm_rope(qkv, q_weight, k_weight, freqs_cis, heads, q_out=None, k_out=No
         o[:, :, token_offset:token_offset + t] = val
         outs.append(o)
     return tuple(outs)
+
+
+def _gathered(segments):
+    cols = []
+    for t, act in segments:
+        m = t if t.dim() == 2 else t.permute(1, 0, 2).reshape(t.shape[1], -1)
+        if act == "gelu_tanh":
+            m = F.gelu(m.float(), approximate="tanh").to(t.dtype)
+        cols.append(m)
+    return torch.cat(cols, dim=1).contiguous()
+
+
+def quantize_nvfp4_gather(segments, per_tensor_scale, hi_first=True):
+    return orc.quantize_nvfp4(_gathered(segments), per_tensor_scale, 0.0, False, hi_first)

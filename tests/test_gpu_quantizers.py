@@ -258,3 +258,37 @@ def test_argument_errors(ck):
         _native.call("launch_quantize_nvfp4_kernel", ctypes.c_void_p(x.data_ptr()), ctypes.c_void_p(x.data_ptr()),
                      ctypes.c_void_p(x.data_ptr()), ctypes.c_void_p(x.data_ptr()), 16, 24, 16, 24, 0.0, 2, True,
                      ctypes.c_void_p(0))
+
+
+def test_quantize_nvfp4_gather_matches_concatenation():
+    """Gathered source (attention layout + column slice) without activation: bytes equal cat -> quantize_nvfp4;
+    with GELU on the second segment: equal to the oracle on torch's gelu except where the two tanh
+    implementations round a bf16 value differently (a handful of blocks)."""
+    from comfy_kitchen.backends import cuda as ck
+    from tests import dit_oracle_ops as ops
+
+    g = torch.Generator().manual_seed(5)
+    heads, rows, d = 3, 300, 128
+    o_full = torch.randn(heads, rows + 50, d, generator=g).bfloat16()       # a token range of a longer sequence
+    wide = (1.5 * torch.randn(rows, 3 * heads * d + 512, generator=g)).bfloat16()
+    seg0, seg1 = o_full[:, 50:], wide[:, 3 * heads * d:]
+    gs = torch.tensor(4.0 / (6 * 448))
+    o_d, wide_d = o_full.cuda(), wide.cuda()
+    seg0_d, seg1_d = o_d[:, 50:], wide_d[:, 3 * heads * d:]
+    # no activation: exact
+    q, sf = ck.quantize_nvfp4_gather([(seg0_d, None), (seg1_d, None)], gs.cuda())
+    q_ref, sf_ref = ops.quantize_nvfp4_gather([(seg0, None), (seg1, None)], gs)
+    assert q.shape == (rows, (heads * d + 512) // 2)
+    assert torch.equal(q.cpu(), q_ref) and torch.equal(sf.view(torch.uint8).cpu(), sf_ref.view(torch.uint8))
+    # one segment only
+    q1, sf1 = ck.quantize_nvfp4_gather([(seg0_d, None)], gs.cuda())
+    q1_ref, sf1_ref = ops.quantize_nvfp4_gather([(seg0, None)], gs)
+    assert torch.equal(q1.cpu(), q1_ref) and torch.equal(sf1.view(torch.uint8).cpu(), sf1_ref.view(torch.uint8))
+    # GELU on the second segment
+    q2, sf2 = ck.quantize_nvfp4_gather([(seg0_d, None), (seg1_d, "gelu_tanh")], gs.cuda())
+    q2_ref, sf2_ref = ops.quantize_nvfp4_gather([(seg0, None), (seg1, "gelu_tanh")], gs)
+    n0 = heads * d // 2
+    assert torch.equal(q2.cpu()[:, :n0], q2_ref[:, :n0])                     # the plain segment stays exact
+    bad_codes = (q2.cpu() != q2_ref).float().mean().item()
+    bad_scales = (sf2.view(torch.uint8).cpu() != sf2_ref.view(torch.uint8)).float().mean().item()
+    assert bad_codes < 2e-3 and bad_scales < 2e-3, (bad_codes, bad_scales)
