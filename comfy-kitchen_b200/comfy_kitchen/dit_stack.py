@@ -164,10 +164,12 @@ class DiTStack:
         self.tp = tp or TensorParallel()
         cfg.validate(self.tp.world)
         self.sites = _Sites()
+        self._mods = None   # all blocks' modulation vectors during a forward
         self.heads_local = cfg.heads // self.tp.world
         self.freqs = rope_freqs(cfg, self.device)
         self.double = [self._make_double(i) for i in range(cfg.n_double)]
         self.single = [self._make_single(i) for i in range(cfg.n_single)]
+        self._pack_modulation()
 
     # ------------------------------------------------------------------ weights
 
@@ -252,6 +254,22 @@ class DiTStack:
                                     bias_full=self._randn((h,), L, "linear2_b", c.weight_std), row_parallel=True)
         return p
 
+    def _pack_modulation(self) -> None:
+        """Every block's modulation is a linear of the same conditioning vector: stack all of them into one
+        weight so that a forward computes them with one matrix-vector product instead of one per block."""
+        owners = [blk[s] for blk in self.double for s in ("img", "txt")] + list(self.single)
+        if not owners:
+            self.mod_w = self.mod_b = None
+            return
+        self.mod_w = torch.cat([p["mod_w"] for p in owners])
+        self.mod_b = torch.cat([p["mod_b"] for p in owners])
+        off = 0
+        for p in owners:
+            n = p["mod_w"].shape[0]
+            p["mod_slice"] = (off, off + n)
+            p["mod_w"], p["mod_b"] = self.mod_w[off:off + n], self.mod_b[off:off + n]   # views: no second copy
+            off += n
+
     # ------------------------------------------------------------------ activation scales
 
     def _act_scale(self, site: str, x: torch.Tensor | None = None, amax: torch.Tensor | None = None) -> torch.Tensor:
@@ -285,8 +303,11 @@ class DiTStack:
     # ------------------------------------------------------------------ pieces of the forward
 
     def _modulation(self, p: dict, vec: torch.Tensor, n: int):
-        m = F.linear(F.silu(vec), p["mod_w"], p["mod_b"])  # [1, n * hidden], replicated on every rank
-        return m.chunk(n, dim=-1)
+        """This block's (shift, scale, gate, ...) vectors, each [1, hidden], replicated on every rank."""
+        if self._mods is not None:
+            lo, hi = p["mod_slice"]
+            return self._mods[:, lo:hi].chunk(n, dim=-1)
+        return F.linear(F.silu(vec), p["mod_w"], p["mod_b"]).chunk(n, dim=-1)
 
     def _norm_quant(self, site: str, x: torch.Tensor, scale: torch.Tensor, shift: torch.Tensor):
         """LayerNorm + modulation + NVFP4 quantise in one kernel.  Without a static scale the maximum comes
@@ -380,11 +401,15 @@ class DiTStack:
     def forward(self, img: torch.Tensor, txt: torch.Tensor, vec: torch.Tensor) -> torch.Tensor:
         """img [img_tokens, hidden], txt [txt_tokens, hidden], vec [1, hidden] (bf16) -> [tokens, hidden],
         text tokens first.  Every rank receives the same inputs and returns the same (replicated) output."""
-        for i in range(self.cfg.n_double):
-            img, txt = self._double_block(i, img, txt, vec)
-        x = torch.cat([txt, img])
-        for i in range(self.cfg.n_single):
-            x = self._single_block(i, x, vec)
+        self._mods = F.linear(F.silu(vec), self.mod_w, self.mod_b) if self.mod_w is not None else None
+        try:
+            for i in range(self.cfg.n_double):
+                img, txt = self._double_block(i, img, txt, vec)
+            x = torch.cat([txt, img])
+            for i in range(self.cfg.n_single):
+                x = self._single_block(i, x, vec)
+        finally:
+            self._mods = None
         return x
 
     __call__ = forward
@@ -392,12 +417,14 @@ class DiTStack:
     def capture(self, img: torch.Tensor, txt: torch.Tensor, vec: torch.Tensor):
         """Record one forward into a CUDA graph and return ``replay(img, txt, vec) -> out``.
 
-        The forward is ~50 small launches per block; replaying a graph removes their host cost.  Needs static
+        The forward is ~40 small launches per block; replaying a graph removes their host cost.  Needs static
         activation scales (call calibrate() first) so that no value-dependent host work is left in the forward.
         Inputs are copied into the graph's own buffers; the returned tensor is the graph's output buffer
-        (overwritten by the next replay).  With more than one rank the all-reduces are captured too, so every
-        rank must capture and replay in step.
+        (overwritten by the next replay).  Single rank only: capturing the NCCL all-reduces of a tensor-parallel
+        forward did not complete on the test machines (both ranks waited in the capture), so tensor-parallel
+        runs launch eagerly.
         """
+        assert self.tp.world == 1, "graph capture is for a single rank; tensor-parallel forwards launch eagerly"
         assert self.device.type == "cuda", "graph capture needs a CUDA device"
         assert self.sites.static, "calibrate() first: capture needs static activation scales"
         bufs = [img.clone(), txt.clone(), vec.clone()]
