@@ -421,8 +421,8 @@ class DiTStack:
         activation scales (call calibrate() first) so that no value-dependent host work is left in the forward.
         Inputs are copied into the graph's own buffers; the returned tensor is the graph's output buffer
         (overwritten by the next replay).  Single rank only: capturing the NCCL all-reduces of a tensor-parallel
-        forward did not complete on the test machines (both ranks waited in the capture), so tensor-parallel
-        runs launch eagerly.
+        forward did not complete on the test machines (NCCL 2.28, two ranks, with the default and with the
+        thread-local capture error mode alike), so tensor-parallel runs launch eagerly.
         """
         assert self.tp.world == 1, "graph capture is for a single rank; tensor-parallel forwards launch eagerly"
         assert self.device.type == "cuda", "graph capture needs a CUDA device"
