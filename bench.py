@@ -440,8 +440,9 @@ def run_dit(args) -> None:
             torch.randn(1, cfg.hidden, generator=g).bfloat16().pin_memory()]
     img, txt, vec = (t.to(device) for t in host)
     stack.calibrate(img, txt, vec)
-    eager = args.no_graph or world > 1   # the all-reduces of a tensor-parallel forward are not captured
-    run = stack.forward if eager else stack.capture(img, txt, vec)
+    eager = args.no_graph
+    # one graph on a single rank; with tensor parallelism a chain of graphs with the all-reduces between them
+    run = stack.forward if eager else (stack.capture(img, txt, vec) if world == 1 else stack.capture_segments(img, txt, vec))
     for _ in range(max(args.warmup, 3)):
         out = run(img, txt, vec)
     torch.cuda.synchronize()
@@ -486,7 +487,7 @@ def run_dit(args) -> None:
             "config": {"workload": "synthetic Flux-like DiT stack (configs[4])", "double_blocks": nd, "single_blocks": ns,
                        "tokens": cfg.tokens, "hidden": cfg.hidden, "parallelism": f"tp{world}",
                        "all_reduces_per_forward": stack.expected_all_reduces(),
-                       "launch": "eager" if eager else "one CUDA graph per forward",
+                       "launch": "eager" if eager else ("one CUDA graph per forward" if world == 1 else "CUDA graphs between all-reduces"),
                        "l2": "weights (6 GB per rank at tp1) larger than L2"},
             "linear_tflops": round(gf / (ms * 1e-3) / 1e12, 1), "attention_tflop_per_forward": round(af / 1e12, 2),
             "e2e": {"value": round(t_e2e, 3), "unit": "ms", "h2d_bytes_per_step": int(sum(t.numel() * 2 for t in host)),

@@ -88,9 +88,12 @@ class TensorParallel:
         else:
             self.group, self.rank, self.world = None, 0, 1
         self.all_reduce_calls = 0
+        self.on_all_reduce = None   # set while a forward is being recorded in segments (DiTStack.capture_segments)
 
     def all_reduce_sum(self, t: torch.Tensor) -> torch.Tensor:
         self.all_reduce_calls += 1
+        if self.on_all_reduce is not None:
+            return self.on_all_reduce(t)
         if self.world > 1:
             self._dist.all_reduce(t, op=self._dist.ReduceOp.SUM, group=self.group)
         return t
@@ -447,6 +450,67 @@ class DiTStack:
             return out
 
         replay.graph = graph
+        return replay
+
+    def capture_segments(self, img: torch.Tensor, txt: torch.Tensor, vec: torch.Tensor):
+        """Tensor-parallel variant of capture(): the forward is recorded as a chain of CUDA graphs that ends at
+        every all-reduce; ``replay`` launches graph, all-reduce, graph, ... so the collectives stay ordinary NCCL
+        calls between graph launches and the host issues ~2 calls per all-reduce instead of ~40 per block.
+        All graphs share one memory pool and are replayed in the order they were captured.  Every rank must
+        call this, and later ``replay``, in step.  Also valid on a single rank (the all-reduces are no-ops)."""
+        assert self.device.type == "cuda", "graph capture needs a CUDA device"
+        assert self.sites.static, "calibrate() first: capture needs static activation scales"
+        bufs = [img.clone(), txt.clone(), vec.clone()]
+        side = torch.cuda.Stream(device=self.device)
+        side.wait_stream(torch.cuda.current_stream(self.device))
+        with torch.cuda.stream(side):
+            for _ in range(2):   # warm up (with real all-reduces) on the capture stream
+                self.forward(*bufs)
+        torch.cuda.current_stream(self.device).wait_stream(side)
+        torch.cuda.synchronize(self.device)
+        if self.tp.world > 1:
+            self.tp._dist.barrier(group=self.tp.group)   # no collective in flight while captures are open
+            torch.cuda.synchronize(self.device)
+        pool = torch.cuda.graph_pool_handle()
+        graphs, reduces = [], []
+        current = [None]
+
+        def begin():
+            g = torch.cuda.CUDAGraph()
+            g.capture_begin(pool=pool, capture_error_mode="thread_local")
+            current[0] = g
+
+        def split(t: torch.Tensor) -> torch.Tensor:
+            current[0].capture_end()
+            graphs.append(current[0])
+            reduces.append(t)
+            begin()
+            return t
+
+        with torch.cuda.stream(side):
+            self.tp.on_all_reduce = split
+            try:
+                begin()
+                out = self.forward(*bufs)
+                current[0].capture_end()
+                graphs.append(current[0])
+            finally:
+                self.tp.on_all_reduce = None
+        torch.cuda.current_stream(self.device).wait_stream(side)
+        torch.cuda.synchronize(self.device)
+        tp = self.tp
+
+        def replay(img_, txt_, vec_):
+            bufs[0].copy_(img_, non_blocking=True)
+            bufs[1].copy_(txt_, non_blocking=True)
+            bufs[2].copy_(vec_, non_blocking=True)
+            for k, g in enumerate(graphs):
+                g.replay()
+                if k < len(reduces) and tp.world > 1:
+                    tp._dist.all_reduce(reduces[k], op=tp._dist.ReduceOp.SUM, group=tp.group)
+            return out
+
+        replay.graphs = graphs
         return replay
 
     def expected_all_reduces(self) -> int:

@@ -77,3 +77,20 @@ def test_graph_replay_equals_eager_forward():
     img2 = (img.float() * 0.5).bfloat16()
     want2 = stack.forward(img2, txt, vec).clone()
     assert torch.equal(replay(img2, txt, vec), want2)   # new inputs reach the captured kernels
+
+
+def test_segmented_graph_replay_equals_eager_forward():
+    """The chain of graphs that ends at every all-reduce (the tensor-parallel launch path) on one rank."""
+    from comfy_kitchen.dit_stack import DiTConfig, DiTStack
+
+    cfg = DiTConfig(hidden=1024, heads=8, n_double=1, n_single=2, txt_tokens=64, img_grid=(16, 16))
+    stack = DiTStack(cfg, "cuda")
+    img, txt, vec = _inputs(cfg, "cuda")
+    stack.calibrate(img, txt, vec)
+    want = stack.forward(img, txt, vec).clone()
+    replay = stack.capture_segments(img, txt, vec)
+    assert len(replay.graphs) == stack.expected_all_reduces() + 1
+    assert torch.equal(replay(img, txt, vec), want)
+    txt2 = (txt.float() * 0.25).bfloat16()
+    want2 = stack.forward(img, txt2, vec).clone()
+    assert torch.equal(replay(img, txt2, vec), want2)
