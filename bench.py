@@ -187,18 +187,34 @@ class Workload:
         return h2d, d2h
 
     def step_e2e(self):
+        """Every linear is an independent call whose input crosses the bus and whose output goes back.  Three
+        streams (host-to-device copies, kernels, device-to-host copies) chained by events, so the copy of the
+        next input and of the previous output overlap the kernels of the current linear."""
+        if not hasattr(self, "s_in"):
+            self.s_in, self.s_out = torch.cuda.Stream(self.device), torch.cuda.Stream(self.device)
+        cur = torch.cuda.current_stream(self.device)
+        self.s_in.wait_stream(cur)
         for b in BATCHES:
             _, shift, scale, _, gx, gh = self.acts[b]
             hx, hh = self.host_in[b]
             for name, _, k in LAYERS:
-                # each linear is an independent call: its input crosses the bus, its output goes back
+                with torch.cuda.stream(self.s_in):
+                    dev_in = (hx if k == HIDDEN else hh).to(self.device, non_blocking=True)
+                    ready = torch.cuda.Event()
+                    ready.record(self.s_in)
+                cur.wait_event(ready)
+                dev_in.record_stream(cur)
                 if k == HIDDEN:
-                    x = hx.to(self.device, non_blocking=True)
-                    out = self.linear(b, name, x, shift, scale, None, gx, gh, False)
+                    out = self.linear(b, name, dev_in, shift, scale, None, gx, gh, False)
                 else:
-                    h = hh.to(self.device, non_blocking=True)
-                    out = self.linear(b, name, None, shift, scale, h, gx, gh, False)
-                self.host_out[b][name].copy_(out, non_blocking=True)
+                    out = self.linear(b, name, None, shift, scale, dev_in, gx, gh, False)
+                done = torch.cuda.Event()
+                done.record(cur)
+                self.s_out.wait_event(done)
+                with torch.cuda.stream(self.s_out):
+                    self.host_out[b][name].copy_(out, non_blocking=True)
+                out.record_stream(self.s_out)
+        cur.wait_stream(self.s_out)
 
 
 def quantizer_sweep(device) -> dict:
