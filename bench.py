@@ -253,6 +253,48 @@ def quantizer_sweep(device) -> dict:
     return {k: round(v, 1) for k, v in res.items()}
 
 
+def mxfp8_and_rope(device) -> dict:
+    """configs[3] on this GPU: the MXFP8 GEMM on the four layer shapes (M = 9216) and RoPE on q, k
+    [2, 24, 4608, 128] with an fp32 table (CUDA events, L2 flushed between launches by the 0.5 GB of
+    outputs the GEMM loop cycles through; RoPE inputs exceed L2)."""
+    from comfy_kitchen.backends import cuda as ck
+
+    g = torch.Generator(device=device).manual_seed(3)
+    m = 2 * TOKENS
+    ev = lambda: torch.cuda.Event(enable_timing=True)  # noqa: E731
+    flops, ms = 0.0, 0.0
+    for _, n, k in LAYERS:
+        x = torch.randn(m, k, device=device, generator=g).bfloat16()
+        w = (0.02 * torch.randn(n, k, device=device, generator=g)).bfloat16()
+        bias = (0.02 * torch.randn(n, device=device, generator=g)).float()
+        qx, sx = ck.quantize_mxfp8(x)
+        qw, sw = ck.quantize_mxfp8(w)
+        for _ in range(3):
+            ck.scaled_mm_mxfp8(qx, qw, sx, sw, bias=bias, out_dtype=torch.bfloat16)
+        a, b = ev(), ev()
+        a.record()
+        for _ in range(5):
+            ck.scaled_mm_mxfp8(qx, qw, sx, sw, bias=bias, out_dtype=torch.bfloat16)
+        b.record()
+        torch.cuda.synchronize()
+        ms += a.elapsed_time(b) / 5
+        flops += 2.0 * m * n * k
+    q = torch.randn(2, 24, TOKENS, 128, device=device, generator=g).bfloat16()
+    kk = torch.randn(2, 24, TOKENS, 128, device=device, generator=g).bfloat16()
+    fr = torch.randn(2, 1, TOKENS, 64, 2, 2, device=device, generator=g)
+    for _ in range(3):
+        ck.apply_rope(q, kk, fr)
+    a, b = ev(), ev()
+    a.record()
+    for _ in range(10):
+        ck.apply_rope(q, kk, fr)
+    b.record()
+    torch.cuda.synchronize()
+    rope_bytes = 8.0 * q.numel() + 4.0 * fr.numel()
+    return {"mxfp8_gemm_tflops": round(flops / (ms * 1e-3) / 1e12, 1), "mxfp8_gemm_shapes": f"M={m} x the four layers",
+            "rope_gbs": round(rope_bytes / (a.elapsed_time(b) / 10 * 1e-3) / 1e9, 1), "rope_shape": list(q.shape)}
+
+
 # ----------------------------------------------------------------------------- CPU arm
 
 
@@ -605,7 +647,7 @@ def main() -> None:
         "gpu_launches": 24 * args.steps,
         "clocks": clocks,
         "roofline": {"bound": "tensor", "achieved": round(achieved, 1), "peak": round(peak, 1), "unit": "TFLOP/s",
-                     "frac": round(achieved / peak, 4),
+                     "frac": round(achieved / peak, 4), "frac_of_nominal_dense_fp4": round(achieved / 9000.0, 4),
                      # dram__bytes_read + write of one launch under ncu (profiles/gemm_blockscaled_nvfp4_4608x9216x3072.md)
                      "traffic": 59.6e6, "traffic_case": "M4608 N9216 K3072: 24.0 MB read (= operands + scales), 35.6 MB "
                      "written of the 84.9 MB output (the rest still in L2 at kernel end)",
@@ -628,6 +670,8 @@ def main() -> None:
         del wl.host_in, wl.host_out
         # ---- memory-bound kernels, largest sweep shape
         line["quantizers"] = {"shape": [65536, 12288], "unit": "GB/s", "hbm_peak": peaks["hbm_gbs"], **quantizer_sweep(device)}
+        # ---- configs[3]: MXFP8 GEMM and RoPE
+        line["mxfp8_rope"] = mxfp8_and_rope(device)
         # ---- the DiT stack of configs[4] on this GPU (tp1; `--workload dit` runs it tensor-parallel)
         if not args.no_dit:
             line["dit_stack"] = dit_forward_ms(device, steps=3)
