@@ -41,7 +41,7 @@ def _operands(M, N, K, seed):
 
 
 NVFP4_SHAPES = [(128, 192, 256), (256, 384, 512), (128, 192, 64), (200, 264, 320), (129, 200, 96), (512, 1024, 2048),
-                (77, 8, 32), (1024, 3072, 3072)]
+                (77, 8, 32), (1024, 3072, 3072), (300, 520, 192), (513, 264, 3104), (257, 256, 288)]
 
 
 @pytest.mark.parametrize("M,N,K", NVFP4_SHAPES)
@@ -131,7 +131,7 @@ def test_linearity_at_full_size(ck):
 
 
 MXFP8_SHAPES = [(128, 192, 128), (256, 384, 512), (128, 192, 32), (200, 264, 160), (129, 200, 96), (512, 1024, 2048),
-                (1024, 3072, 3072)]
+                (1024, 3072, 3072), (300, 520, 160), (513, 264, 3104), (257, 256, 288)]
 
 
 @pytest.mark.parametrize("M,N,K", MXFP8_SHAPES)
