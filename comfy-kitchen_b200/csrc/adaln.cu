@@ -19,6 +19,7 @@
 #include "ck_common.cuh"
 
 namespace ck {
+extern int g_norm_warps;   // 0 = the launcher chooses; > 0 forces the warps per CTA (tuning runs)
 namespace {
 
 enum OutMode { kOutPlain = 0, kOutNvfp4 = 1, kOutMxfp8 = 2 };
@@ -83,8 +84,8 @@ constexpr uint32_t kRowWaitLimit = 1u << 22;
 // as fp32 and reloaded only where the range crosses a modulation group.  Per row: one pass for the
 // statistics (shifted by the row's first element, so a large common offset does not cancel), one
 // pass for the output; a lane owns whole 16-element chunks.
-template <typename T, int kMode>
-__global__ void __launch_bounds__(512)
+template <typename T, int kMode, int kMaxThreads>
+__global__ void __launch_bounds__(kMaxThreads)
 norm_stream_kernel(const NormArgs a, const int ring, const int64_t rows_per_cta, const int cache_mod) {
     extern __shared__ __align__(128) uint8_t smem[];
     const int warps = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -340,22 +341,30 @@ int launch_warp(const NormArgs& a, cudaStream_t stream) {
     const size_t mod_bytes = cache_mod ? (size_t)round_up(a.D, 512) * 8 : 0;
     const size_t budget = 225 * 1024 - mod_bytes;   // of the 227 KB a CTA can have; the barriers take the rest
     // warps per CTA and ring depth from the shared-memory budget: as many warps as fit with a ring of
-    // two rows each, then a third row if there is room
+    // two rows each, then a third row if there is room.  (g_norm_warps > 0 forces the warp count, with one
+    // row buffer per warp when two do not fit: up to 24 warps, for tuning runs.)
     int warps = 0, ring = 2;
-    for (int w : {16, 12, 8, 6, 4, 2, 1})
-        if ((size_t)w * 2 * row_bytes <= budget) { warps = w; break; }
-    if (warps == 0)
-        CK_FAIL(CK_ERR_SHAPE, "adaln: a row of %lld bytes does not fit the staging ring", (long long)row_bytes);
-    if ((size_t)warps * 3 * row_bytes <= budget) ring = 3;
+    if (g_norm_warps > 0) {
+        warps = g_norm_warps > 24 ? 24 : g_norm_warps;
+        ring = (size_t)warps * 2 * row_bytes <= budget ? 2 : 1;
+        if ((size_t)warps * ring * row_bytes > budget) CK_FAIL(CK_ERR_SHAPE, "adaln: forced warp count does not fit");
+    } else {
+        for (int w : {16, 12, 8, 6, 4, 2, 1})
+            if ((size_t)w * 2 * row_bytes <= budget) { warps = w; break; }
+        if (warps == 0)
+            CK_FAIL(CK_ERR_SHAPE, "adaln: a row of %lld bytes does not fit the staging ring", (long long)row_bytes);
+        if ((size_t)warps * 3 * row_bytes <= budget) ring = 3;
+    }
     const size_t smem = mod_bytes + (size_t)warps * ring * row_bytes + (size_t)warps * ring * 8;
-    auto kern = norm_stream_kernel<T, kMode>;
-    static bool attr_set[64] = {};
+    // two builds of the kernel: up to 16 warps with 128 registers per thread, up to 24 with 80
+    auto kern = warps > 16 ? norm_stream_kernel<T, kMode, 768> : norm_stream_kernel<T, kMode, 512>;
+    static bool attr_set[2][64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
-    if (dev < 0 || dev >= 64 || !attr_set[dev]) {
+    if (dev < 0 || dev >= 64 || !attr_set[warps > 16][dev]) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
         if (e != cudaSuccess) CK_FAIL((int)e, "adaln: cannot reserve shared memory: %s", cudaGetErrorString(e));
-        if (dev >= 0 && dev < 64) attr_set[dev] = true;
+        if (dev >= 0 && dev < 64) attr_set[warps > 16][dev] = true;
     }
     const int64_t rows = kMode == kOutPlain ? a.N : round_up(a.N, 128);
     int sms = 148;
