@@ -18,7 +18,7 @@ from .registry import registry
 __version__ = "0.2.18+b200"
 
 __all__ = [
-    "adaln", "rmsnorm", "adaln_quantize_nvfp4", "adaln_quantize_mxfp8",
+    "adaln", "rmsnorm", "adaln_quantize_nvfp4", "adaln_quantize_mxfp8", "qk_norm_rope", "quantize_nvfp4_gather",
     "quantize_per_tensor_fp8", "dequantize_per_tensor_fp8", "quantize_nvfp4", "dequantize_nvfp4",
     "quantize_mxfp8", "dequantize_mxfp8", "scaled_mm_nvfp4", "scaled_mm_mxfp8",
     "apply_rope", "apply_rope1", "apply_rope_split_half", "apply_rope_split_half1",
@@ -51,6 +51,22 @@ def adaln_quantize_nvfp4(x, scale, shift, per_tensor_scale, eps: float = 1e-6, h
 def adaln_quantize_mxfp8(x, scale, shift, eps: float = 1e-6):
     """``quantize_mxfp8(adaln(x, scale, shift, eps).reshape(-1, D))`` in one pass over x."""
     return _ops_ns.adaln_quantize_mxfp8(x, scale, shift, eps)
+
+
+def qk_norm_rope(qkv: torch.Tensor, q_weight: torch.Tensor, k_weight: torch.Tensor, freqs_cis: torch.Tensor, heads: int,
+                 eps: float = 1e-6):
+    """Per-head RMSNorm of q and k, RoPE of both, and q, k, v in attention's [1, heads, tokens, 128] layout, from
+    the output of a fused QKV projection ([tokens, 3 * heads * 128]) in one pass.  The backend function of the same
+    name also takes output buffers and a token offset (two segments of one joint sequence)."""
+    return _ops_ns.qk_norm_rope(qkv, q_weight, k_weight, freqs_cis, heads, eps)
+
+
+def quantize_nvfp4_gather(segments, per_tensor_scale: torch.Tensor, hi_first: bool = True):
+    """quantize_nvfp4 of the column concatenation of one or two (tensor, activation) segments read in place;
+    see the backend function for the accepted layouts."""
+    first = segments[0][0]
+    impl = registry.get_implementation("quantize_nvfp4_gather", kwargs={"x": first, "per_tensor_scale": per_tensor_scale})
+    return impl(segments, per_tensor_scale, hi_first)
 
 
 # ------------------------------------------------------------------ quantize / dequantize

@@ -206,3 +206,16 @@ def _(x, scale, shift, eps):
     n = x.numel() // d
     return (torch.empty((n, d), dtype=torch.float8_e4m3fn, device=x.device),
             torch.empty((roundup(n, 128), roundup(d // 32, 4)), dtype=torch.float8_e8m0fnu, device=x.device))
+
+
+@torch.library.custom_op("comfy_kitchen::qk_norm_rope", mutates_args=())
+def _op_qk_norm_rope(qkv: torch.Tensor, q_weight: torch.Tensor, k_weight: torch.Tensor, freqs_cis: torch.Tensor,
+                     heads: int, eps: float) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    return _dispatch("qk_norm_rope", qkv=qkv, q_weight=q_weight, k_weight=k_weight, freqs_cis=freqs_cis, heads=heads,
+                     eps=eps)
+
+
+@_op_qk_norm_rope.register_fake
+def _(qkv, q_weight, k_weight, freqs_cis, heads, eps):
+    shape = (1, heads, freqs_cis.shape[2], 128)
+    return tuple(torch.empty(shape, dtype=qkv.dtype, device=qkv.device) for _ in range(3))

@@ -562,6 +562,9 @@ def build_constraints() -> dict:
         "rmsnorm": fc(x=ParamConstraint(dtypes=floats), weight=ParamConstraint(dtypes=floats)),
         "adaln_quantize_nvfp4": fc(**norm, per_tensor_scale=ParamConstraint(dtypes=frozenset({torch.float32}))),
         "adaln_quantize_mxfp8": fc(**norm),
+        "qk_norm_rope": fc(qkv=ParamConstraint(dtypes=frozenset({torch.bfloat16, torch.float16})),
+                           freqs_cis=ParamConstraint(dtypes=frozenset({torch.float32}))),
+        "quantize_nvfp4_gather": fc(per_tensor_scale=ParamConstraint(dtypes=frozenset({torch.float32}))),
     }
 
 

@@ -100,6 +100,7 @@ rope_vec_kernel(const TX* __restrict__ xq, const TX* __restrict__ xk, const TF* 
     const int64_t col = kSplit ? (int64_t)v * 8 : (int64_t)v * 8;
     const int64_t half = p.D / 2;
 
+#pragma unroll 4
     for (; j < j_end; ++j) {
         const int64_t off = xoff + idx[0] * p.sx[0] + idx[1] * p.sx[1] + idx[2] * p.sx[2] + col;
 #pragma unroll

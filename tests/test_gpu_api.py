@@ -133,3 +133,23 @@ def test_torch_compile_through_fake_kernels(ck):
     want = f(x)
     got = torch.compile(f, fullgraph=True)(x)
     torch.testing.assert_close(got.float(), want.float(), rtol=1e-3, atol=1e-3)
+
+
+def test_public_api_new_fused_ops():
+    """The public entry points of the two fused operators reach the CUDA backend through the registry."""
+    import comfy_kitchen as ck
+    from comfy_kitchen.backends import cuda as be
+
+    g = torch.Generator(device="cuda").manual_seed(0)
+    heads, t = 2, 96
+    qkv = torch.randn(t, 3 * heads * 128, device="cuda", generator=g).bfloat16()
+    w = torch.ones(128, device="cuda").bfloat16()
+    ang = torch.rand(t, 64, device="cuda", generator=g)
+    f = torch.stack([torch.stack([ang.cos(), -ang.sin()], -1), torch.stack([ang.sin(), ang.cos()], -1)], -2)[None, None].contiguous()
+    q, k, v = ck.qk_norm_rope(qkv, w, w, f, heads)
+    q2, k2, v2 = be.qk_norm_rope(qkv, w, w, f, heads)
+    assert torch.equal(q, q2) and torch.equal(k, k2) and torch.equal(v, v2)
+    gs = torch.tensor(0.01, device="cuda")
+    a = ck.quantize_nvfp4_gather([(v[0], None)], gs)
+    b = be.quantize_nvfp4(v[0].permute(1, 0, 2).reshape(t, heads * 128).contiguous(), gs)
+    assert torch.equal(a[0], b[0]) and torch.equal(a[1].view(torch.uint8), b[1].view(torch.uint8))
