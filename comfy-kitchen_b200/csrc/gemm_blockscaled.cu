@@ -575,12 +575,13 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
                                 w[i] = __float_as_uint(fmaf(__uint_as_float(r[c >> 5][c & 31]), alpha, bias_at(c)));
                             }
                         }
+                        if (!(CK_GEMM_PROBE & 1024) || w[0] == 0x12345678u)   // 1024: timing experiment without the staging writes
                         *reinterpret_cast<uint4*>(my_row + ((j ^ sw) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
                     }
-                    fence_async_smem();
+                    if (!(CK_GEMM_PROBE & 512)) fence_async_smem();   // 512: timing experiment without the proxy fence
                     __syncwarp();
                     const int col = n0 + ch * chunk_cols;
-                    if (lane == 0 && store_ok && col < p.N) tma_store_2d(&map_out, stg, col, row0);
+                    if (lane == 0 && store_ok && col < p.N && !(CK_GEMM_PROBE & 32)) tma_store_2d(&map_out, stg, col, row0);
                 }
             }
             if (warp == kFirstEpiWarp) CK_TS(1 + rank, 240 + local_tile, 3);
