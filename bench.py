@@ -15,8 +15,9 @@ inference.
 Printed JSON (one line, rank 0):
   value     TFLOP/s of the whole job (2*M*N*K per linear), inputs resident in HBM
   e2e       the same metric with the activations starting in pinned host memory and the
-            outputs read back to the host inside the timed region
-  roofline  the NVFP4 GEMM kernel against the tensor peak (see DESIGN.md for the denominator)
+            outputs read back to the host inside the timed region (copies and kernels overlap on three streams)
+  roofline  the NVFP4 GEMM kernel against the tensor peak (4 x the measured sustained bf16 GEMM rate: dense FP4 is
+            4 x dense bf16 on this part)
   cpu_baseline  the CPU oracle (a port of the reference's eager arithmetic) on a bounded sample
   quantizers    GB/s of the memory-bound kernels at the largest sweep shape
 With --impl reference the CPU oracle is what is timed (the reference's own path for this

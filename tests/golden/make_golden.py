@@ -38,7 +38,7 @@ def _inputs(shape, dtype, seed, kind):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", required=True, help="path of a checkout of the reference repository")
     args = ap.parse_args()
     sys.dont_write_bytecode = True
     sys.path.insert(0, args.reference)
