@@ -357,10 +357,12 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
                 if (n_sf > kSfTilesPerStage) n_sf = kSfTilesPerStage;
                 const uint32_t sf_bytes = (uint32_t)n_sf * 512u;
                 const size_t sf_off = (size_t)kt * (kSfTilesPerStage * 512);
-                const uint32_t tx_bytes = kSmemA + kSmemB + sf_bytes * ((have_a ? 1 : 0) + b_tiles);
+                // 2048: timing experiment — A is loaded for every other k-tile only (what sharing A between pairs would save)
+                const bool skip_a = (CK_GEMM_PROBE & 2048) && (kt & 1);
+                const uint32_t tx_bytes = (skip_a ? 0 : kSmemA) + kSmemB + sf_bytes * ((have_a ? 1 : 0) + b_tiles);
                 if (elect_one()) {
                     mbar_expect_tx(&full[s], tx_bytes);
-                    tma_load_2d(st, &map_a, kt * 128, tm * 256 + (int)rank * BM, &full[s]);
+                    if (!skip_a) tma_load_2d(st, &map_a, kt * 128, tm * 256 + (int)rank * BM, &full[s]);
                     tma_load_2d(st + kSmemA, &map_b, kt * 128, tn * BN + (int)rank * (BN / 2), &full[s]);
                     if (have_a) bulk_load(st + kSmemA + kSmemB, sfa_src + sf_off, sf_bytes, &full[s]);
                     bulk_load(st + kSmemA + kSmemB + kSmemSfA, sfb_src + sf_off, sf_bytes, &full[s]);
