@@ -19,7 +19,7 @@ __version__ = "0.2.18+b200"
 
 __all__ = [
     "adaln", "rmsnorm", "adaln_quantize_nvfp4", "adaln_quantize_mxfp8", "qk_norm_rope", "quantize_nvfp4_gather",
-    "quantize_per_tensor_fp8", "dequantize_per_tensor_fp8", "quantize_nvfp4", "dequantize_nvfp4",
+    "quantize_per_tensor_fp8", "dequantize_per_tensor_fp8", "stochastic_rounding_fp8", "quantize_nvfp4", "dequantize_nvfp4",
     "quantize_mxfp8", "dequantize_mxfp8", "scaled_mm_nvfp4", "scaled_mm_mxfp8",
     "apply_rope", "apply_rope1", "apply_rope_split_half", "apply_rope_split_half1",
     "swap_nibbles", "to_blocked", "from_blocked",
@@ -70,6 +70,12 @@ def quantize_nvfp4_gather(segments, per_tensor_scale: torch.Tensor, hi_first: bo
 
 
 # ------------------------------------------------------------------ quantize / dequantize
+
+
+def stochastic_rounding_fp8(x: torch.Tensor, rng: torch.Tensor,
+                            output_type: torch.dtype = torch.float8_e4m3fn) -> torch.Tensor:
+    """Stochastically round ``x`` (via fp16) to FP8; ``rng`` is a uint8 tensor of x's shape."""
+    return _ops_ns.stochastic_rounding_fp8(x, rng, output_type)
 
 
 def quantize_per_tensor_fp8(x: torch.Tensor, scale: torch.Tensor,

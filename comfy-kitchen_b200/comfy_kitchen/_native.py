@@ -34,6 +34,7 @@ SIGNATURES: dict[str, list] = {
     "launch_scaled_mm_nvfp4_kernel": [P, P, P, P, P, P, I, I64, I64, I64, P, I, P],
     "launch_scaled_mm_mxfp8_kernel": [P, P, P, P, P, P, I, I64, I64, I64, I, P],
     "launch_apply_rope_kernel": [P, P, P, P, P] + [I64] * 17 + [I, I, B, P],
+    "launch_stochastic_rounding_fp8_kernel": [P, P, P, I64, I, I, P],
     "launch_quantize_nvfp4_gather_kernel": [P, I64, I64, I64, I64, I, P, I64, I64, I64, I64, I, P, P, P, I64, I, B, P],
     "launch_qk_norm_rope_kernel": [P, I64, P, P, P, P, P, P, I64, I64, I64, I64, F, I, P],
     "launch_adaln_kernel": [P, P, P, P, I64, I64, I64, I64, F, I, P],

@@ -219,3 +219,13 @@ def _op_qk_norm_rope(qkv: torch.Tensor, q_weight: torch.Tensor, k_weight: torch.
 def _(qkv, q_weight, k_weight, freqs_cis, heads, eps):
     shape = (1, heads, freqs_cis.shape[2], 128)
     return tuple(torch.empty(shape, dtype=qkv.dtype, device=qkv.device) for _ in range(3))
+
+
+@torch.library.custom_op("comfy_kitchen::stochastic_rounding_fp8", mutates_args=())
+def _op_stochastic_rounding_fp8(x: torch.Tensor, rng: torch.Tensor, output_type: torch.dtype) -> torch.Tensor:
+    return _dispatch("stochastic_rounding_fp8", x=x, rng=rng, output_type=output_type)
+
+
+@_op_stochastic_rounding_fp8.register_fake
+def _(x, rng, output_type):
+    return torch.empty(x.shape, dtype=output_type, device=x.device)

@@ -91,6 +91,23 @@ def dequantize_per_tensor_fp8(
     return out
 
 
+def stochastic_rounding_fp8(
+    x: torch.Tensor, rng: torch.Tensor, output_type: torch.dtype = torch.float8_e4m3fn
+) -> torch.Tensor:
+    """x.half() rounded to FP8 up or down according to one random byte per element (same bytes as the
+    reference's eager function)."""
+    if output_type not in (torch.float8_e4m3fn, torch.float8_e5m2):
+        raise ValueError(f"Unsupported output_type: {output_type}. Expected torch.float8_e4m3fn or torch.float8_e5m2")
+    x = _plain(x)
+    assert rng.dtype == torch.uint8 and rng.shape == x.shape, "rng must be uint8 with x's shape"
+    xc = x if x.is_contiguous() else x.contiguous()
+    rc = rng if rng.is_contiguous() else rng.contiguous()
+    out = torch.empty(x.shape, device=x.device, dtype=torch.uint8)
+    _native.call("launch_stochastic_rounding_fp8_kernel", _ptr(xc), _ptr(rc), _ptr(out), xc.numel(),
+                 _code(x.dtype, "stochastic_rounding_fp8"), DTYPE_TO_CODE[output_type], _stream(x.device))
+    return out.view(output_type)
+
+
 def _scalar_on(s, device) -> torch.Tensor:
     """fp32 one-element device tensor without a host round trip when it already is one."""
     s = _plain(s)
@@ -562,6 +579,7 @@ def build_constraints() -> dict:
         "rmsnorm": fc(x=ParamConstraint(dtypes=floats), weight=ParamConstraint(dtypes=floats)),
         "adaln_quantize_nvfp4": fc(**norm, per_tensor_scale=ParamConstraint(dtypes=frozenset({torch.float32}))),
         "adaln_quantize_mxfp8": fc(**norm),
+        "stochastic_rounding_fp8": fc(x=ParamConstraint(dtypes=floats), rng=ParamConstraint(dtypes=frozenset({torch.uint8}))),
         "qk_norm_rope": fc(qkv=ParamConstraint(dtypes=frozenset({torch.bfloat16, torch.float16})),
                            freqs_cis=ParamConstraint(dtypes=frozenset({torch.float32}))),
         "quantize_nvfp4_gather": fc(per_tensor_scale=ParamConstraint(dtypes=frozenset({torch.float32}))),

@@ -56,6 +56,13 @@ int ck_set_option(const char* name, int value);
  * scale: one device float.  Arithmetic: backends/eager/quantization.py:43-63. */
 int launch_quantize_fp8_kernel(const void* input, void* output, const void* scale, int64_t numel,
                                int input_dtype_code, int output_dtype_code, ck_stream_t stream);
+
+/* stochastic_rounding_fp8 (comfy_kitchen/backends/eager/quantization.py:66-114; reference kernel
+ * backends/cuda/ops/per_tensor_quantize.cu:121-161, which overwrites the random bytes in place): input rounded
+ * to fp16, then to FP8 with one random byte per element deciding the direction.  Byte-identical to the eager
+ * function.  rng: numel bytes; output: numel bytes (E4M3 or E5M2 codes). */
+int launch_stochastic_rounding_fp8_kernel(const void* input, const void* rng, void* output, int64_t numel,
+                                          int input_dtype_code, int output_dtype_code, ck_stream_t stream);
 int launch_dequantize_fp8_kernel(const void* input, void* output, const void* scale, int64_t numel,
                                  int input_dtype_code, int output_dtype_code, ck_stream_t stream);
 

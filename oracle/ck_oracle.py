@@ -270,6 +270,18 @@ def apply_rope_split_half(xq, xk, freqs_cis):
     return _rope(xq, freqs_cis, True), _rope(xk, freqs_cis, True)
 
 
+def stochastic_rounding_fp8(x, rng, output_type=torch.float8_e4m3fn):
+    """backends/eager/quantization.py:77-114: x.half() rounded to FP8 with one random byte per element."""
+    assert output_type in (torch.float8_e4m3fn, torch.float8_e5m2)
+    x = x.contiguous()
+    rng = rng.contiguous()
+    assert rng.dtype == torch.uint8 and rng.numel() == x.numel()
+    out = torch.empty(x.shape, dtype=torch.uint8)
+    _check(lib().ck_oracle_stochastic_rounding_fp8(_p(x), _p(rng), _p(out), ctypes.c_int64(x.numel()), DTYPE_TO_CODE[x.dtype],
+                                                   int(output_type == torch.float8_e4m3fn)), "stochastic_rounding_fp8")
+    return out.view(output_type)
+
+
 # ------------------------------------------------------------------- AdaLN
 
 

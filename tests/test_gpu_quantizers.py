@@ -292,3 +292,25 @@ def test_quantize_nvfp4_gather_matches_concatenation():
     bad_codes = (q2.cpu() != q2_ref).float().mean().item()
     bad_scales = (sf2.view(torch.uint8).cpu() != sf2_ref.view(torch.uint8)).float().mean().item()
     assert bad_codes < 2e-3 and bad_scales < 2e-3, (bad_codes, bad_scales)
+
+
+@pytest.mark.parametrize("ot", [torch.float8_e4m3fn, torch.float8_e5m2])
+def test_stochastic_rounding_exhaustive(ck, orc, ot):
+    """All 65536 fp16 inputs x all 256 random bytes against the oracle (which the reference fixtures pin), and
+    bf16 / fp32 / ragged inputs through the public API."""
+    import comfy_kitchen as api
+
+    h = torch.arange(65536, dtype=torch.int32).to(torch.int16).view(torch.float16)
+    x = h.repeat(256)
+    r = torch.arange(256, dtype=torch.uint8).repeat_interleave(65536)
+    want = orc.stochastic_rounding_fp8(x, r, ot).view(torch.uint8)
+    got = ck.stochastic_rounding_fp8(x.cuda(), r.cuda(), ot).view(torch.uint8).cpu()
+    bad = (got != want).nonzero().flatten()
+    assert bad.numel() == 0, (bad[:8].tolist(), got[bad[:8]].tolist(), want[bad[:8]].tolist())
+    g = torch.Generator().manual_seed(9)
+    for dtype, n in ((torch.bfloat16, 4099), (torch.float32, 12345), (torch.float16, 7)):
+        v = (torch.randn(n, generator=g) * torch.exp2(torch.randint(-18, 17, (n,), generator=g).float())).to(dtype)
+        rb = torch.randint(0, 256, (n,), generator=g, dtype=torch.uint8)
+        want = orc.stochastic_rounding_fp8(v, rb, ot).view(torch.uint8)
+        got = api.stochastic_rounding_fp8(v.cuda(), rb.cuda(), ot)
+        assert got.dtype == ot and torch.equal(got.view(torch.uint8).cpu(), want)

@@ -165,3 +165,22 @@ def test_adaln_matches_reference(golden):
         torch.testing.assert_close(y.float(), c["y"].float(), rtol=tol, atol=tol)
         y1 = orc.adaln(c["x"], c["scale"], c["shift"], c["eps"], single_rounding=True)
         torch.testing.assert_close(y1.float(), c["y_fp32"].to(dt).float(), rtol=tol, atol=tol)
+
+
+def test_stochastic_rounding_golden():
+    """Every fp16 input against six random-byte choices, both formats, plus bf16 / fp32 inputs: byte-exact."""
+    import os
+
+    import torch
+    from oracle import ck_oracle as orc
+
+    d = torch.load(os.path.join(os.path.dirname(__file__), "golden", "stochastic_rounding_golden.pt"))
+    h = d["fp16_bits"].view(torch.float16)
+    for (fmt, src, rname), want in d["cases"].items():
+        ot = torch.float8_e4m3fn if fmt == "e4m3" else torch.float8_e5m2
+        if src == "fp16":
+            got = orc.stochastic_rounding_fp8(h, d["rng"][rname], ot)
+        else:
+            got = orc.stochastic_rounding_fp8(d["extra"][src], d["extra_rng"], ot)
+        bad = (got.view(torch.uint8) != want).nonzero().flatten()
+        assert bad.numel() == 0, (fmt, src, rname, bad[:8].tolist())
