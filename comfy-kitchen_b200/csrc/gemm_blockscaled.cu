@@ -61,7 +61,8 @@ constexpr int BN = 256;            // columns per pair tile; each CTA stages 128
 constexpr int kStages = CK_GEMM_STAGES;
 constexpr int kFirstEpiWarp = 2, kEpiWarps = 16;  // four warps per TMEM lane quarter, 64 columns each
 constexpr int kFirstMoverWarp = kFirstEpiWarp + kEpiWarps;
-constexpr int kThreads = 32 * (kFirstMoverWarp + 4);
+constexpr int kSecondMmaWarp = kFirstMoverWarp + 4;   // issues the odd k-tiles; warp 1 the even ones
+constexpr int kThreads = 32 * (kSecondMmaWarp + 1);
 constexpr int kSfBufs = 3;
 constexpr int kKbPerTile = 4;  // MMAs per k-tile
 
@@ -89,7 +90,7 @@ constexpr uint32_t kSpinLimit = 1u << 22;   // polls of mbarrier.try_wait before
 
 __device__ int g_gemm_status = 0;           // 0 ok; otherwise (code << 16 | CTA) of the first failure
 #if CK_GEMM_PROBE & 8
-__device__ long long g_probe_ts[5 * 4 * 256];   // pair 0, per role and k-tile: timestamps (role 0 MMA, 1/2 movers, 3/4 producers of CTA 0/1)
+__device__ long long g_probe_ts[7 * 4 * 256];   // pair 0, per role and k-tile: timestamps (role 0 MMA, 1/2 movers, 3/4 producers of CTA 0/1)
 #define CK_TS(role, it, k) do { if (pair == 0 && lane == 0 && (it) < 256) g_probe_ts[(role) * 1024 + 4 * (it) + (k)] = clock64(); } while (0)
 #else
 #define CK_TS(role, it, k) do { } while (0)
@@ -182,8 +183,15 @@ __device__ __forceinline__ void bulk_load(void* dst, const void* src, uint32_t b
 }
 // Shared -> global tile store (clipped at the tensor's edges), tracked by the issuing thread's bulk groups.
 __device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, const void* src, int c0, int c1) {
+#if CK_GEMM_PROBE & 16384   // timing experiment: output lines marked evict-first in L2
+    uint64_t policy;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(policy));
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group.L2::cache_hint [%0, {%2, %3}], [%1], %4;"
+                 ::"l"(map), "r"(smem_u32(src)), "r"(c0), "r"(c1), "l"(policy) : "memory");
+#else
     asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
                  ::"l"(map), "r"(smem_u32(src)), "r"(c0), "r"(c1) : "memory");
+#endif
     asm volatile("cp.async.bulk.commit_group;" ::: "memory");
 }
 __device__ __forceinline__ void bulk_wait_read_all() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
@@ -299,7 +307,8 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
     uint64_t* sf_full = empty + kStages;      // [kSfBufs]  (leader's) both CTAs' scales in TMEM -> MMA issuer
     uint64_t* tmem_full = sf_full + kSfBufs;  //            accumulator complete -> epilogue
     uint64_t* tmem_empty = tmem_full + 1;     //            (leader's) both CTAs' accumulators copied out -> MMA issuer
-    uint64_t* probe_bar = tmem_empty + 1;     //            timing experiments only
+    uint64_t* tile_open = tmem_empty + 1;     //            first MMA of a tile issued -> the second MMA issuer
+    uint64_t* probe_bar = tile_open + 1;      //            timing experiments only
     uint32_t* s_tmem_base = reinterpret_cast<uint32_t*>(probe_bar + 1);
     volatile int* s_abort = reinterpret_cast<volatile int*>(s_tmem_base + 1);
 
@@ -315,7 +324,8 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 5); }
         for (int b = 0; b < kSfBufs; ++b) mbar_init(&sf_full[b], 8);
-        mbar_init(tmem_full, 1);
+        mbar_init(tmem_full, 2);   // one commit per tile from each MMA issuer
+        mbar_init(tile_open, 1);
         mbar_init(tmem_empty, 2 * kEpiWarps);
         mbar_init(probe_bar, 1u << 20);
         *s_abort = 0;
@@ -379,7 +389,7 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
             const int s = j % kStages;
             (void)mbar_wait(&full[s], (j / kStages) & 1, s_abort, kTimeoutFull);
         }
-    } else if (warp >= kFirstMoverWarp) {
+    } else if (warp >= kFirstMoverWarp && warp < kSecondMmaWarp) {
         // ------------------------------------------------------------ scale movers (smem -> registers -> TMEM)
         // A 512-byte scale tile is 32 rows x 16 bytes: row i holds, for the four 32-row groups g of a
         // 128-row tile, the scale bytes of row 32g + i.  The MMA wants it in TMEM as 32 lanes x 4 columns
@@ -442,8 +452,15 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
                 if (warp == kFirstMoverWarp) CK_TS(1 + rank, it, 3);
             }
         }
-    } else if (warp == 1) {
-        // ------------------------------------------------------------ MMA issuer (leader CTA only)
+    } else if (warp == 1 || warp == kSecondMmaWarp) {
+        // ------------------------------------------------------------ MMA issuers (leader CTA only)
+        // Issuing one block-scaled MMA keeps a thread ~100 clocks and the bookkeeping of a k-tile (barrier
+        // look-ahead, commit) another ~150, while the tensor cores need 128 clocks per MMA: a single issuer
+        // cannot keep them fed.  Two warps therefore take the k-tiles in turn (warp 1 the even ones).  The
+        // accumulation order does not matter except for the first MMA of a tile, which overwrites: the second
+        // issuer waits (tile_open) until the first has issued it.  A commit covers the committing thread's own
+        // MMAs, so each issuer releases the stages it consumed and both commit to tmem_full.
+        const uint32_t which = warp == 1 ? 0u : 1u;
         if (rank == 0) {
         const uint32_t idesc_base = (kFp4 ? ((1u << 7) | (1u << 10)) : 0u) | ((uint32_t)(BN >> 3) << 17) |
                                     (kFp4 ? 0u : (1u << 23)) | ((uint32_t)((2 * BM) >> 4) << 24);
@@ -452,17 +469,21 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
         uint32_t it = 0, local_tile = 0;
         bool ok = true, ready = false;
         for (int tile = pair; tile < num_tiles && ok; tile += num_pairs, ++local_tile) {
-            CK_TS(0, 240 + local_tile, 0);
+            ready = false;
             if (local_tile > 0) ok = mbar_wait(tmem_empty, (local_tile - 1) & 1, s_abort, kTimeoutTmemEmpty);
             if (!ok) break;
             tc_fence_after();
-            CK_TS(0, 240 + local_tile, 1);
             const uint32_t d_tmem = tmem_base + kTmemAcc;
+            if (which == 1 && k_tiles > 1) {   // the overwriting MMA must be in the pipe before any of mine
+                ok = mbar_wait(tile_open, local_tile & 1, s_abort, kTimeoutTmemEmpty);
+                if (!ok) break;
+            }
             for (int kt = 0; kt < k_tiles && ok; ++kt, ++it) {
+                if ((uint32_t)(kt & 1) != which) continue;
                 const int s = it % kStages;
                 const uint32_t sb = it % kSfBufs;
 #if CK_GEMM_PROBE & 8
-                CK_TS(0, it, 0);
+                if (which == 0) CK_TS(0, it, 0);
 #endif
                 // The movers of both CTAs publish sf_full only after they saw their full[s], so this one wait
                 // covers the operands too.  `ready` is an early look taken while the previous k-tile was issued.
@@ -470,7 +491,7 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
                 if (!ok) break;
                 tc_fence_after();
 #if CK_GEMM_PROBE & 8
-                CK_TS(0, it, 1);
+                if (which == 0) CK_TS(0, it, 1);
 #endif
                 // every descriptor of this stage is "stage start >> 4" plus a constant (the same in both CTAs)
                 const uint32_t st16 = smem16 + (uint32_t)s * (kStageBytes >> 4);
@@ -486,17 +507,27 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
                         if (kFp4) { sfa += 4 * kb; sfb += 8 * kb; }
                         else { idesc |= ((uint32_t)kb << 29) | ((uint32_t)kb << 4); }
                         tc_mma<kFp4>(d_tmem, a_lo + 2 * kb, b_lo + 2 * kb, idesc, (kt > 0 || kb > 0) ? 1u : 0u, sfa, sfb);
+#if (CK_GEMM_PROBE & 4104) == 4104   // fine-grained issue trace: role 5 = after each MMA issue
+                        if (which == 0) CK_TS(5, it, kb);
+#endif
+                        if (kt == 0 && kb == 0 && lane == 0) mbar_arrive(tile_open);   // which == 0 here
                     }
-                    // the pipe is busy with these for a while: look at the next k-tile's barrier now
-                    if (kb == 1) ready = mbar_test_wait(&sf_full[(it + 1) % kSfBufs], ((it + 1) / kSfBufs) & 1);
+                    // the pipe is busy with these for a while: look at my next k-tile's barrier now
+                    if (kb == 1) ready = kt + 2 < k_tiles &&
+                                         mbar_test_wait(&sf_full[(it + 2) % kSfBufs], ((it + 2) / kSfBufs) & 1);
                 }
                 if (CK_GEMM_PROBE & 256) tc_commit_pair(probe_bar);   // timing experiment: what one more commit costs
                 tc_commit_pair(&empty[s]);                      // stage and scale buffer reusable once these MMAs are done
-                if (kt == k_tiles - 1) { tc_commit_pair(tmem_full); CK_TS(0, 240 + local_tile, 2); }  // accumulators complete
+#if (CK_GEMM_PROBE & 4104) == 4104
+                if (which == 0) CK_TS(6, it, 0);   // after the stage commit
+#endif
 #if CK_GEMM_PROBE & 8
-                CK_TS(0, it, 2);
+                if (which == 0) CK_TS(0, it, 2);
 #endif
             }
+            // the accumulator is complete when both issuers' MMAs are (an issuer that had no k-tile in this tile
+            // commits nothing and arrives at once)
+            if (ok) tc_commit_pair(tmem_full);
         }
         }
     } else {
@@ -583,7 +614,8 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
                     if (!(CK_GEMM_PROBE & 512)) fence_async_smem();   // 512: timing experiment without the proxy fence
                     __syncwarp();
                     const int col = n0 + ch * chunk_cols;
-                    if (lane == 0 && store_ok && col < p.N && !(CK_GEMM_PROBE & 32)) tma_store_2d(&map_out, stg, col, row0);
+                    if (lane == 0 && store_ok && col < p.N && !(CK_GEMM_PROBE & 32))
+                        tma_store_2d(&map_out, stg, (CK_GEMM_PROBE & 8192) ? (e & 3) * 32 : col, (CK_GEMM_PROBE & 8192) ? (e >> 2) * 32 : row0);   // 8192: timing experiment, every store lands on the same 16 KB
                 }
             }
             if (warp == kFirstEpiWarp) CK_TS(1 + rank, 240 + local_tile, 3);
@@ -771,7 +803,7 @@ extern "C" int launch_cublas_gemm_blockwise_fp4_kernel(const void* B_ptr, const 
 #if CK_GEMM_PROBE & 8
 extern "C" int ck_probe_read(long long* out) {
     cudaDeviceSynchronize();
-    return (int)cudaMemcpyFromSymbol(out, ck::g_probe_ts, sizeof(long long) * 5 * 4 * 256);
+    return (int)cudaMemcpyFromSymbol(out, ck::g_probe_ts, sizeof(long long) * 7 * 4 * 256);
 }
 #endif
 
