@@ -278,6 +278,22 @@ struct GemmParams {
     int tiles_m, tiles_n; // pair tiles (256 x 256)
 };
 
+// Tile order: bands of kGroupM tile rows, walked column by column inside a band, so that the ~74 tiles in
+// flight at any time cover a compact block of the output (about kGroupM x 9 tiles) and re-use the same few A and
+// W tiles from L2 while the much larger output streams through it.
+#ifndef CK_GEMM_GROUP_M
+#define CK_GEMM_GROUP_M 8
+#endif
+__device__ __forceinline__ void tile_coords(int tile, const GemmParams& p, int& tm, int& tn) {
+    constexpr int kGroupM = CK_GEMM_GROUP_M;
+    const int per_band = kGroupM * p.tiles_n;
+    const int band = tile / per_band, in_band = tile - band * per_band;
+    const int first = band * kGroupM;
+    const int rows = min(kGroupM, p.tiles_m - first);
+    tn = in_band / rows;
+    tm = first + (in_band - tn * rows);
+}
+
 template <typename T16>
 __device__ __forceinline__ uint32_t pack_pair(float a, float b);
 template <>
@@ -347,7 +363,8 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
         bool ok = true;
         const size_t sf_row_pitch = (size_t)p.sf_tiles_k * 512;
         for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
-            const int tm = tile % p.tiles_m, tn = tile / p.tiles_m;
+            int tm, tn;
+            tile_coords(tile, p, tm, tn);
             const int row_tile_a = tm * 2 + (int)rank;     // this CTA's 128 rows of A
             const bool have_a = row_tile_a < p.sf_row_tiles_a;
             const int row_tile_b = tn * 2;                 // first of the two 128-row scale tiles of the W tile
@@ -546,7 +563,8 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
         uint32_t local_tile = 0;
         bool ok = true;
         for (int tile = pair; tile < num_tiles && ok; tile += num_pairs, ++local_tile) {
-            const int tm = tile % p.tiles_m, tn = tile / p.tiles_m;
+            int tm, tn;
+            tile_coords(tile, p, tm, tn);
             const int n0 = tn * BN + part * 64;
             // bias for these 64 columns: lane l keeps columns l and l + 32, the others fetch them with shuffles
             float bias_reg[2];
