@@ -151,6 +151,8 @@ __device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
 // Bounded wait, called by all 32 lanes of a warp.  Returns false (to every lane alike)
 // when the limit ran out or another role already gave up.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int code) {
+    // Phase already complete (seen by every lane): skip try_wait, which costs ~150 clocks even then.
+    if (__all_sync(0xffffffffu, mbar_test_wait(bar, parity))) return true;
     bool done = false;
     for (uint32_t i = 0; i < kSpinLimit; ++i) {
         if (mbar_try_wait(bar, parity)) { done = true; break; }
@@ -398,6 +400,7 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
                                   sf_bytes, &full[s]);
                 }
                 __syncwarp();
+                CK_TS(3 + rank, it, 2);   // copies of this k-tile issued
             }
         }
         // drain: every copy this warp issued must have landed before the CTA may exit
@@ -487,9 +490,15 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
         bool ok = true, ready = false;
         for (int tile = pair; tile < num_tiles && ok; tile += num_pairs, ++local_tile) {
             ready = false;
+#if CK_GEMM_PROBE & 8
+            if (which == 0) CK_TS(0, 240 + local_tile, 0);
+#endif
             if (local_tile > 0) ok = mbar_wait(tmem_empty, (local_tile - 1) & 1, s_abort, kTimeoutTmemEmpty);
             if (!ok) break;
             tc_fence_after();
+#if CK_GEMM_PROBE & 8
+            if (which == 0) CK_TS(0, 240 + local_tile, 1);
+#endif
             const uint32_t d_tmem = tmem_base + kTmemAcc;
             if (which == 1 && k_tiles > 1) {   // the overwriting MMA must be in the pipe before any of mine
                 ok = mbar_wait(tile_open, local_tile & 1, s_abort, kTimeoutTmemEmpty);
