@@ -20,6 +20,7 @@
 
 namespace ck {
 extern int g_norm_warps;   // 0 = the launcher chooses; > 0 forces the warps per CTA (tuning runs)
+extern int g_norm_cache;   // -1 = the launcher chooses; 0 = no modulation cache (tuning runs)
 namespace {
 
 enum OutMode { kOutPlain = 0, kOutNvfp4 = 1, kOutMxfp8 = 2 };
@@ -84,7 +85,9 @@ constexpr uint32_t kRowWaitLimit = 1u << 22;
 // as fp32 and reloaded only where the range crosses a modulation group.  Per row: one pass for the
 // statistics (shifted by the row's first element, so a large common offset does not cancel), one
 // pass for the output; a lane owns whole 16-element chunks.
-template <typename T, int kMode, int kMaxThreads>
+// kIters > 0: the row is exactly kIters x 512 elements (known at compile time, so both passes unroll fully and
+// no lane is ever past the row's end); 0: any row length.
+template <typename T, int kMode, int kMaxThreads, int kIters>
 __global__ void __launch_bounds__(kMaxThreads)
 norm_stream_kernel(const NormArgs a, const int ring, const int64_t rows_per_cta, const int cache_mod) {
     extern __shared__ __align__(128) uint8_t smem[];
@@ -97,7 +100,7 @@ norm_stream_kernel(const NormArgs a, const int ring, const int64_t rows_per_cta,
     uint8_t* rows_base = smem + (cache_mod ? (size_t)mod_elems * 8 : 0);
     uint8_t* my_rows = rows_base + (size_t)warp * ring * row_bytes;
     uint64_t* my_bars = reinterpret_cast<uint64_t*>(rows_base + (size_t)warps * ring * row_bytes) + warp * ring;
-    const int nchunk = (int)(D >> 4);  // 16-element chunks per row
+    const int nchunk = kIters > 0 ? kIters * 32 : (int)(D >> 4);  // 16-element chunks per row
 
     if (lane == 0) {
         for (int s = 0; s < ring; ++s)
@@ -188,7 +191,7 @@ norm_stream_kernel(const NormArgs a, const int ring, const int64_t rows_per_cta,
             // two accumulator pairs, updated with sm_100's packed fp32 instructions (two IEEE operations each)
             float2 s1 = make_float2(0.0f, 0.0f), s2 = s1;
             const float2 nshift = make_float2(-shift0, -shift0);
-#pragma unroll 2
+#pragma unroll(kIters > 0 ? kIters : 2)
             for (int c = lane; c < nchunk; c += 32) {
                 float f[16];
                 lds16<T, false>(xs + c * 16, lane, f);
@@ -210,14 +213,21 @@ norm_stream_kernel(const NormArgs a, const int ring, const int64_t rows_per_cta,
             const T* __restrict__ sc = (!cache_mod && scale_g) ? scale_g + (row / a.scale_group) * D : nullptr;
             const T* __restrict__ sh = (!cache_mod && shift_g) ? shift_g + (row / a.shift_group) * D : nullptr;
 
-            // whole-warp steps so the shuffles inside the block encoders see all 32 lanes
-#pragma unroll 2
+            // whole-warp steps: the MXFP8 block encoder shuffles between lane pairs
+#pragma unroll(kIters > 0 ? kIters : 2)
             for (int c0 = 0; c0 < nchunk; c0 += 32) {
                 const int c = c0 + lane;
-                const bool ok = c < nchunk;
+                const bool ok = kIters > 0 || c < nchunk;
                 float y[16];
+                if (kMode == kOutMxfp8) {
+                    // its block encoder shuffles between lane pairs: lanes past the row's end take part with zeros
 #pragma unroll
-                for (int j = 0; j < 16; ++j) y[j] = 0.0f;
+                    for (int j = 0; j < 16; ++j) y[j] = 0.0f;
+                } else if (!ok) {
+                    // scale columns that pad the row to a multiple of 4
+                    if (kMode == kOutNvfp4 && c < a.sf_cpad) a.sf[sf_offset(row, c, a.sf_cpad)] = 0;
+                    continue;
+                }
                 if (ok) {
                     float f[16];
                     lds16<T, true>(xs + c * 16, lane, f);
@@ -248,16 +258,12 @@ norm_stream_kernel(const NormArgs a, const int ring, const int64_t rows_per_cta,
                 } else {
                     // the quantizers see the activation as it would have been stored
 #pragma unroll
-                    for (int j = 0; j < 16; ++j) y[j] = Elem<T>::round(y[j]);
+                    for (int j = 0; j < 16; j += 2) Elem<T>::round2(y[j], y[j + 1]);
                     if (kMode == kOutNvfp4) {
                         uint32_t s8;
                         const uint2 packed = nvfp4_encode_block(y, ctx, a.hi_first != 0, s8);
-                        if (ok) {
-                            *reinterpret_cast<uint2*>(static_cast<uint8_t*>(a.out) + row * (D >> 1) + (int64_t)c * 8) = packed;
-                            a.sf[sf_offset(row, c, a.sf_cpad)] = (uint8_t)s8;
-                        } else if (c < a.sf_cpad) {
-                            a.sf[sf_offset(row, c, a.sf_cpad)] = 0;  // scale columns that pad the row to a multiple of 4
-                        }
+                        *reinterpret_cast<uint2*>(static_cast<uint8_t*>(a.out) + row * (D >> 1) + (int64_t)c * 8) = packed;
+                        a.sf[sf_offset(row, c, a.sf_cpad)] = (uint8_t)s8;
                     } else {
                         // 32-element block = this lane's chunk and its neighbour's (lane ^ 1)
                         uint32_t e;
@@ -337,34 +343,56 @@ int launch_warp(const NormArgs& a, cudaStream_t stream) {
     const size_t row_bytes = (size_t)a.D * sizeof(T);
     // the modulation cache pays when a modulation row serves many rows (AdaLN: one per batch entry)
     const bool has_mod = a.scale || a.shift;
-    const int cache_mod = has_mod && (!a.scale || a.scale_group >= 32) && (!a.shift || a.shift_group >= 32);
-    const size_t mod_bytes = cache_mod ? (size_t)round_up(a.D, 512) * 8 : 0;
-    const size_t budget = 225 * 1024 - mod_bytes;   // of the 227 KB a CTA can have; the barriers take the rest
-    // warps per CTA and ring depth from the shared-memory budget: as many warps as fit with a ring of
-    // two rows each, then a third row if there is room.  (g_norm_warps > 0 forces the warp count, with one
-    // row buffer per warp when two do not fit: up to 24 warps, for tuning runs.)
-    int warps = 0, ring = 2;
-    if (g_norm_warps > 0) {
-        warps = g_norm_warps > 24 ? 24 : g_norm_warps;
-        ring = (size_t)warps * 2 * row_bytes <= budget ? 2 : 1;
-        if ((size_t)warps * ring * row_bytes > budget) CK_FAIL(CK_ERR_SHAPE, "adaln: forced warp count does not fit");
-    } else {
-        for (int w : {16, 12, 8, 6, 4, 2, 1})
-            if ((size_t)w * 2 * row_bytes <= budget) { warps = w; break; }
+    int cache_mod = has_mod && (!a.scale || a.scale_group >= 32) && (!a.shift || a.shift_group >= 32);
+    if (g_norm_cache == 0) cache_mod = 0;
+    // Warps per CTA, ring depth and whether to cache the modulation, from the shared-memory budget (225 KB of
+    // the 227 a CTA can have; the barriers take the rest).  Throughput grows almost linearly with the warps
+    // per SM up to 16 (each warp walks its rows serially), a second row buffer per warp adds a few percent,
+    // and the modulation cache is worth about a quarter: so take the most warps whose rows fit once, give
+    // them a second (third) buffer if there is room, and give up the cache where that doubles the warps
+    // (rows of 16 KB and more).  g_norm_warps > 0 forces the warp count (up to 24, for tuning runs).
+    int warps = 0, ring = 1;
+    size_t mod_bytes = 0;
+    {
+        const size_t cache_bytes = (size_t)round_up(a.D, 512) * 8;
+        double best = 0.0;
+        int best_cache = 0;
+        for (int cache = cache_mod ? 1 : 0; cache >= 0; --cache) {
+            const size_t mb = cache ? cache_bytes : 0;
+            if (mb + row_bytes > 225 * 1024) continue;
+            const size_t budget = 225 * 1024 - mb;
+            int w = 0;
+            if (g_norm_warps > 0) {
+                w = g_norm_warps > 24 ? 24 : g_norm_warps;
+                if ((size_t)w * row_bytes > budget) w = 0;
+            } else {
+                for (int cand : {16, 12, 8, 6, 4, 2, 1})
+                    if ((size_t)cand * row_bytes <= budget) { w = cand; break; }
+            }
+            if (w == 0) continue;
+            const int r = (size_t)w * 3 * row_bytes <= budget ? 3 : ((size_t)w * 2 * row_bytes <= budget ? 2 : 1);
+            const double score = w * (cache ? 1.0 : 0.75) * (r >= 2 ? 1.0 : 0.93);
+            if (score > best) { best = score; warps = w; ring = r; best_cache = cache; mod_bytes = mb; }
+        }
         if (warps == 0)
             CK_FAIL(CK_ERR_SHAPE, "adaln: a row of %lld bytes does not fit the staging ring", (long long)row_bytes);
-        if ((size_t)warps * 3 * row_bytes <= budget) ring = 3;
+        cache_mod = best_cache;
     }
     const size_t smem = mod_bytes + (size_t)warps * ring * row_bytes + (size_t)warps * ring * 8;
     // two builds of the kernel: up to 16 warps with 128 registers per thread, up to 24 with 80
-    auto kern = warps > 16 ? norm_stream_kernel<T, kMode, 768> : norm_stream_kernel<T, kMode, 512>;
-    static bool attr_set[2][64] = {};
+    // rows of 3072 and 4096 elements (the common hidden sizes) get fully unrolled builds
+    const int iters = (a.D == 3072) ? 6 : (a.D == 4096 ? 8 : 0);
+    auto kern = warps > 16 ? norm_stream_kernel<T, kMode, 768, 0>
+                           : (iters == 6 ? norm_stream_kernel<T, kMode, 512, 6>
+                                         : (iters == 8 ? norm_stream_kernel<T, kMode, 512, 8> : norm_stream_kernel<T, kMode, 512, 0>));
+    const int attr_idx = warps > 16 ? 3 : (iters == 6 ? 1 : (iters == 8 ? 2 : 0));
+    static bool attr_set[4][64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
-    if (dev < 0 || dev >= 64 || !attr_set[warps > 16][dev]) {
+    if (dev < 0 || dev >= 64 || !attr_set[attr_idx][dev]) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
         if (e != cudaSuccess) CK_FAIL((int)e, "adaln: cannot reserve shared memory: %s", cudaGetErrorString(e));
-        if (dev >= 0 && dev < 64) attr_set[warps > 16][dev] = true;
+        if (dev >= 0 && dev < 64) attr_set[attr_idx][dev] = true;
     }
     const int64_t rows = kMode == kOutPlain ? a.N : round_up(a.N, 128);
     int sms = 148;

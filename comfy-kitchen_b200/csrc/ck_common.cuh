@@ -59,18 +59,29 @@ template <> struct Elem<float> {
     __device__ static float to_f32(float v) { return v; }
     __device__ static float from_f32(float v) { return v; }
     __device__ static float round(float v) { return v; }
+    __device__ static void round2(float&, float&) {}
 };
 template <> struct Elem<__half> {
     static constexpr int code = CK_F16;
     __device__ static float to_f32(__half v) { return __half2float(v); }
     __device__ static __half from_f32(float v) { return __float2half_rn(v); }
     __device__ static float round(float v) { return __half2float(__float2half_rn(v)); }
+    // both values rounded to the type and back with one packed conversion each way
+    __device__ static void round2(float& a, float& b) {
+        const float2 f = __half22float2(__floats2half2_rn(a, b));
+        a = f.x; b = f.y;
+    }
 };
 template <> struct Elem<__nv_bfloat16> {
     static constexpr int code = CK_BF16;
     __device__ static float to_f32(__nv_bfloat16 v) { return __bfloat162float(v); }
     __device__ static __nv_bfloat16 from_f32(float v) { return __float2bfloat16_rn(v); }
     __device__ static float round(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
+    __device__ static void round2(float& a, float& b) {
+        const __nv_bfloat162 h = __floats2bfloat162_rn(a, b);   // .x = a in the low half
+        const uint32_t w = *reinterpret_cast<const uint32_t*>(&h);
+        a = __uint_as_float(w << 16); b = __uint_as_float(w & 0xffff0000u);
+    }
 };
 
 // 8 consecutive elements as fp32, loaded with 128-bit accesses.
@@ -353,6 +364,52 @@ __device__ __forceinline__ uint32_t nvfp4_codes8(const float (&v)[8], const Nvfp
     return out;
 }
 
+// A whole block -> eight bytes of codes.  The reciprocal sequence runs for every block (its operands are
+// harmless where it does not apply: rtot is 0 there) and a single branch replaces the quotients of the rare
+// blocks that need the IEEE division or have a zero scale, so the common path has no divergence region.
+__device__ __forceinline__ uint2 nvfp4_codes16(const float (&v)[16], const Nvfp4Block& b, bool hi_first) {
+    float q[16];
+    const float2 r2 = make_float2(b.rtot, b.rtot), b2 = make_float2(b.tot, b.tot);
+#pragma unroll
+    for (int i = 0; i < 16; i += 2) {
+        const float2 a2 = make_float2(v[i], v[i + 1]);
+        const float2 q0 = __fmul2_rn(a2, r2);
+        const float2 e = __ffma2_rn(b2, q0, make_float2(-a2.x, -a2.y));
+        const float2 qq = __ffma2_rn(make_float2(-e.x, -e.y), r2, q0);
+        q[i] = qq.x; q[i + 1] = qq.y;
+    }
+    if (!b.fast) {
+        if (b.tot == 0.0f) return make_uint2(0u, 0u);
+#pragma unroll
+        for (int i = 0; i < 16; ++i) q[i] = __fdiv_rn(v[i], b.tot);
+    }
+    uint2 out;
+    if (hi_first) {
+        asm("{ .reg .b8 t0, t1, t2, t3;\n"
+            "cvt.rn.satfinite.e2m1x2.f32 t0, %1, %2; cvt.rn.satfinite.e2m1x2.f32 t1, %3, %4;\n"
+            "cvt.rn.satfinite.e2m1x2.f32 t2, %5, %6; cvt.rn.satfinite.e2m1x2.f32 t3, %7, %8;\n"
+            "mov.b32 %0, {t0, t1, t2, t3}; }"
+            : "=r"(out.x) : "f"(q[0]), "f"(q[1]), "f"(q[2]), "f"(q[3]), "f"(q[4]), "f"(q[5]), "f"(q[6]), "f"(q[7]));
+        asm("{ .reg .b8 t0, t1, t2, t3;\n"
+            "cvt.rn.satfinite.e2m1x2.f32 t0, %1, %2; cvt.rn.satfinite.e2m1x2.f32 t1, %3, %4;\n"
+            "cvt.rn.satfinite.e2m1x2.f32 t2, %5, %6; cvt.rn.satfinite.e2m1x2.f32 t3, %7, %8;\n"
+            "mov.b32 %0, {t0, t1, t2, t3}; }"
+            : "=r"(out.y) : "f"(q[8]), "f"(q[9]), "f"(q[10]), "f"(q[11]), "f"(q[12]), "f"(q[13]), "f"(q[14]), "f"(q[15]));
+    } else {
+        asm("{ .reg .b8 t0, t1, t2, t3;\n"
+            "cvt.rn.satfinite.e2m1x2.f32 t0, %2, %1; cvt.rn.satfinite.e2m1x2.f32 t1, %4, %3;\n"
+            "cvt.rn.satfinite.e2m1x2.f32 t2, %6, %5; cvt.rn.satfinite.e2m1x2.f32 t3, %8, %7;\n"
+            "mov.b32 %0, {t0, t1, t2, t3}; }"
+            : "=r"(out.x) : "f"(q[0]), "f"(q[1]), "f"(q[2]), "f"(q[3]), "f"(q[4]), "f"(q[5]), "f"(q[6]), "f"(q[7]));
+        asm("{ .reg .b8 t0, t1, t2, t3;\n"
+            "cvt.rn.satfinite.e2m1x2.f32 t0, %2, %1; cvt.rn.satfinite.e2m1x2.f32 t1, %4, %3;\n"
+            "cvt.rn.satfinite.e2m1x2.f32 t2, %6, %5; cvt.rn.satfinite.e2m1x2.f32 t3, %8, %7;\n"
+            "mov.b32 %0, {t0, t1, t2, t3}; }"
+            : "=r"(out.y) : "f"(q[8]), "f"(q[9]), "f"(q[10]), "f"(q[11]), "f"(q[12]), "f"(q[13]), "f"(q[14]), "f"(q[15]));
+    }
+    return out;
+}
+
 // This lane holds 8 of the 16 elements of a block (its partner is lane^1).  Returns 4 bytes of
 // codes and the block's scale byte.  Must be called by all 32 lanes.
 template <bool kExactDiv = false>
@@ -375,10 +432,7 @@ __device__ __forceinline__ uint2 nvfp4_encode_block(const float (&v)[16], const 
     for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(v[i]));
     const Nvfp4Block b = nvfp4_block_scale<kExactDiv>(amax, c);
     s8 = b.s8;
-    float lo[8], hi[8];
-#pragma unroll
-    for (int i = 0; i < 8; ++i) { lo[i] = v[i]; hi[i] = v[8 + i]; }
-    return make_uint2(nvfp4_codes8(lo, b, hi_first), nvfp4_codes8(hi, b, hi_first));
+    return nvfp4_codes16(v, b, hi_first);
 }
 
 // ---- 256-bit global accesses (sm_100) -------------------------------------------------------

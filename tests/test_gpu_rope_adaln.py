@@ -114,6 +114,7 @@ def test_adaln_golden(ck, golden):
 
 @pytest.mark.parametrize("xshape,mshape", [((2, 256, 768), (2, 1, 768)), ((1, 4608, 3072), (1, 1, 3072)),
                                            ((3, 5, 100), (3, 5, 100)), ((2, 7, 5000), (2, 1, 5000)),
+                                           ((1, 300, 12288), (1, 1, 12288)), ((2, 130, 6144), (2, 1, 6144)),
                                            ((2, 16, 64), (2, 1, 64))])
 @pytest.mark.parametrize("dt", [torch.bfloat16, torch.float16, torch.float32])
 def test_adaln_vs_oracle(ck, orc, xshape, mshape, dt):
@@ -139,7 +140,10 @@ def test_rmsnorm_vs_torch(ck):
     torch.testing.assert_close(y.float(), ref.float(), rtol=1e-2, atol=1e-2)
 
 
-@pytest.mark.parametrize("N,D,B", [(4608, 3072, 1), (9216, 3072, 2), (200, 1024, 2), (130, 64, 1), (77, 4096, 1)])
+# 3072 and 4096: fully unrolled builds; 6144: one row buffer per warp; 12288: no modulation cache (it would
+# leave room for four warps only); 8192: between the two
+@pytest.mark.parametrize("N,D,B", [(4608, 3072, 1), (9216, 3072, 2), (200, 1024, 2), (130, 64, 1), (77, 4096, 1),
+                                   (520, 6144, 2), (300, 8192, 1), (300, 12288, 1)])
 @pytest.mark.parametrize("dt", [torch.bfloat16, torch.float16])
 def test_fused_adaln_quantize_is_adaln_then_quantize(ck, orc, N, D, B, dt):
     g = torch.Generator().manual_seed(8)
