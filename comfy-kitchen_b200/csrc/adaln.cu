@@ -261,7 +261,7 @@ norm_stream_kernel(const NormArgs a, const int ring, const int64_t rows_per_cta,
                     for (int j = 0; j < 16; j += 2) Elem<T>::round2(y[j], y[j + 1]);
                     if (kMode == kOutNvfp4) {
                         uint32_t s8;
-                        const uint2 packed = nvfp4_encode_block(y, ctx, a.hi_first != 0, s8);
+                        const uint2 packed = nvfp4_encode_block_lean(y, ctx, a.hi_first != 0, s8);
                         *reinterpret_cast<uint2*>(static_cast<uint8_t*>(a.out) + row * (D >> 1) + (int64_t)c * 8) = packed;
                         a.sf[sf_offset(row, c, a.sf_cpad)] = (uint8_t)s8;
                     } else {

@@ -432,6 +432,21 @@ __device__ __forceinline__ uint2 nvfp4_encode_block(const float (&v)[16], const 
     for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(v[i]));
     const Nvfp4Block b = nvfp4_block_scale<kExactDiv>(amax, c);
     s8 = b.s8;
+    float lo[8], hi[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) { lo[i] = v[i]; hi[i] = v[8 + i]; }
+    return make_uint2(nvfp4_codes8(lo, b, hi_first), nvfp4_codes8(hi, b, hi_first));
+}
+
+// The same result through nvfp4_codes16: fewer instructions and no divergence region on the common path, which
+// pays in the instruction-bound fused norm -> quantize kernels (the HBM-bound stand-alone quantizer measured
+// 8 % faster with the form above).
+__device__ __forceinline__ uint2 nvfp4_encode_block_lean(const float (&v)[16], const Nvfp4Ctx& c, bool hi_first, uint32_t& s8) {
+    float amax = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(v[i]));
+    const Nvfp4Block b = nvfp4_block_scale<false>(amax, c);
+    s8 = b.s8;
     return nvfp4_codes16(v, b, hi_first);
 }
 
