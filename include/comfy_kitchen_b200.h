@@ -47,7 +47,10 @@ int ck_abi_version(void);
 int ck_check_device(void); /* 0 when the current device is sm_100 */
 /* Library options (process-wide).  "nvfp4_exact_div" = 1: the NVFP4 quantizer uses plain IEEE
  * divisions instead of the shared-reciprocal sequence; the bytes are the same either way (the
- * tests check that on the device), only the speed differs. */
+ * tests check that on the device), only the speed differs.  "norm_warps" = n > 0 forces the warps
+ * per CTA of the norm kernels (0: the launcher chooses) and "norm_cache" = 0 keeps them from caching
+ * the modulation rows in shared memory (-1: the launcher chooses); both are for tuning runs and
+ * change no result. */
 int ck_set_option(const char* name, int value);
 
 /* ---- per-tensor FP8 ----
