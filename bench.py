@@ -448,10 +448,10 @@ def run_case(args) -> None:
 
 def dit_forward_ms(device, steps: int = 3) -> dict:
     """ms per forward of the full synthetic stack on one GPU (one CUDA graph per forward), for the default line."""
-    from comfy_kitchen.dit_stack import DiTConfig, DiTStack, gemm_flops_per_forward
+    from comfy_kitchen.dit_stack import DiTConfig, DiTStack, TensorParallel, gemm_flops_per_forward
 
     cfg = DiTConfig()
-    stack = DiTStack(cfg, device)
+    stack = DiTStack(cfg, device, tp=TensorParallel(single=True))   # rank 0 measures this alone
     g = torch.Generator().manual_seed(11)
     img = torch.randn(cfg.img_tokens, cfg.hidden, generator=g).bfloat16().to(device)
     txt = torch.randn(cfg.txt_tokens, cfg.hidden, generator=g).bfloat16().to(device)
@@ -655,6 +655,11 @@ def main() -> None:
                      "kernel": "gemm_blockscaled_kernel<fp4>", "peak_source": f"4 x bf16_tflops_sustained ({peaks['_source']})"},
     }
 
+    # The legs below are single-GPU measurements that rank 0 makes alone: the process group goes first, so that
+    # nothing in them can wait for a rank that has already left.
+    if dist is not None:
+        dist.destroy_process_group()
+        dist = None
     if rank == 0 and not args.no_extras:
         # ---- e2e through the public API with host buffers
         h2d, d2h = wl.make_host()
@@ -686,8 +691,6 @@ def main() -> None:
         line["e2e"] = None
     if rank == 0:
         print(json.dumps(line))
-    if dist is not None:
-        dist.destroy_process_group()
 
 
 if __name__ == "__main__":

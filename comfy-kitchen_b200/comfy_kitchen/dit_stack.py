@@ -77,11 +77,13 @@ class DiTConfig:
 class TensorParallel:
     """Rank bookkeeping and the one collective the stack needs."""
 
-    def __init__(self, group=None):
+    def __init__(self, group=None, single: bool = False):
+        """``single=True`` gives a one-rank instance even inside an initialised process group (a measurement
+        that one rank makes on its own must not enter collectives the other ranks never join)."""
         import torch.distributed as dist
 
         self._dist = dist
-        if dist.is_available() and dist.is_initialized():
+        if not single and dist.is_available() and dist.is_initialized():
             self.group = group
             self.rank = dist.get_rank(group)
             self.world = dist.get_world_size(group)

@@ -119,3 +119,47 @@ def test_two_rank_tensor_parallel_matches_single_rank():
     assert sc0 == sc1                                  # calibrated scales agree across ranks (max all-reduce)
     # same weights, different summation order and per-shard activation scales: close, not equal
     assert ((y0 - want).norm() / want.norm()).item() < 0.02
+
+
+def _solo_worker(rank: int, world: int, port: int, out):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    from tests import dit_oracle_ops as ops
+
+    torch.set_num_threads(2)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        if rank == 0:
+            # what bench.py's default line does on rank 0 of a multi-rank launch: a forward of its own, while the
+            # other rank never enters a collective
+            cfg = DiTConfig(**TINY)
+            stack = DiTStack(cfg, "cpu", tp=TensorParallel(single=True), ops=ops)
+            img, txt, vec = _inputs(cfg)
+            stack.calibrate(img, txt, vec)
+            y = stack.forward(img, txt, vec)
+            out.put((stack.tp.world, stack.heads_local, y.float()))
+        dist.barrier()
+    finally:
+        dist.destroy_process_group()
+
+
+def test_single_rank_stack_inside_a_process_group_does_not_wait_for_peers():
+    from tests import dit_oracle_ops as ops
+
+    cfg = DiTConfig(**TINY)
+    single = DiTStack(cfg, "cpu", ops=ops)
+    img, txt, vec = _inputs(cfg)
+    single.calibrate(img, txt, vec)
+    want = single.forward(img, txt, vec).float()
+
+    ctx = mp.get_context("spawn")
+    out = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_solo_worker, args=(r, 2, port, out)) for r in range(2)]
+    for p in procs:
+        p.start()
+    world, heads_local, y = out.get(timeout=300)
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    assert world == 1 and heads_local == cfg.heads
+    assert torch.equal(y, want)
