@@ -21,6 +21,7 @@
 namespace ck {
 extern int g_norm_warps;   // 0 = the launcher chooses; > 0 forces the warps per CTA (tuning runs)
 extern int g_norm_cache;   // -1 = the launcher chooses; 0 = no modulation cache (tuning runs)
+extern int g_norm_group;   // 0 = the launcher chooses; 1, 2, 4 = warps that share a row (tuning runs)
 namespace {
 
 enum OutMode { kOutPlain = 0, kOutNvfp4 = 1, kOutMxfp8 = 2 };
@@ -87,20 +88,28 @@ constexpr uint32_t kRowWaitLimit = 1u << 22;
 // pass for the output; a lane owns whole 16-element chunks.
 // kIters > 0: the row is exactly kIters x 512 elements (known at compile time, so both passes unroll fully and
 // no lane is ever past the row's end); 0: any row length.
-template <typename T, int kMode, int kMaxThreads, int kIters>
+// kGroup > 1: wide rows.  kGroup consecutive warps share a row, each staging and processing D / kGroup
+// elements of it; they exchange their partial sums through shared memory at a named barrier of their own
+// (which also carries "a copy never arrived", so that the group leaves together).
+template <typename T, int kMode, int kMaxThreads, int kIters, int kGroup = 1>
 __global__ void __launch_bounds__(kMaxThreads)
 norm_stream_kernel(const NormArgs a, const int ring, const int64_t rows_per_cta, const int cache_mod) {
     extern __shared__ __align__(128) uint8_t smem[];
     const int warps = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int grp = warp / kGroup, member = warp % kGroup, n_groups = warps / kGroup;
     const int64_t D = a.D;
-    const uint32_t row_bytes = (uint32_t)(D * sizeof(T));
+    const int64_t seg_elems = D / kGroup;                      // this warp's share of a row
+    const uint32_t row_bytes = (uint32_t)(seg_elems * sizeof(T));
     float* s_mul = reinterpret_cast<float*>(smem);            // [D]  (only when cache_mod)
     const int64_t mod_elems = round_up(D, 512);                // whole groups of 32 chunks
     float* s_add = s_mul + mod_elems;
     uint8_t* rows_base = smem + (cache_mod ? (size_t)mod_elems * 8 : 0);
     uint8_t* my_rows = rows_base + (size_t)warp * ring * row_bytes;
     uint64_t* my_bars = reinterpret_cast<uint64_t*>(rows_base + (size_t)warps * ring * row_bytes) + warp * ring;
-    const int nchunk = kIters > 0 ? kIters * 32 : (int)(D >> 4);  // 16-element chunks per row
+    // partial sums of the group's members, two sets (rows alternate between them)
+    float2* s_part = reinterpret_cast<float2*>(reinterpret_cast<uint64_t*>(rows_base + (size_t)warps * ring * row_bytes) + warps * ring);
+    const int nchunk = kIters > 0 ? kIters * 32 : (int)(seg_elems >> 4);  // 16-element chunks in this warp's share
+    const int cbase = member * nchunk;                         // its first chunk's index in the row
 
     if (lane == 0) {
         for (int s = 0; s < ring; ++s)
@@ -120,20 +129,20 @@ norm_stream_kernel(const NormArgs a, const int ring, const int64_t rows_per_cta,
             const uint32_t bar = smem_u32(&my_bars[slot]);
             asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(row_bytes) : "memory");
             asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                         ::"r"(smem_u32(my_rows + (size_t)slot * row_bytes)), "l"(xg + r * D), "r"(row_bytes), "r"(bar) : "memory");
+                         ::"r"(smem_u32(my_rows + (size_t)slot * row_bytes)), "l"(xg + r * D + member * seg_elems), "r"(row_bytes), "r"(bar) : "memory");
         }
     };
 
-    int64_t r_issue = r0 + warp;
+    int64_t r_issue = r0 + grp;
     int64_t issued = 0;
-    for (; issued < ring - 1; ++issued, r_issue += warps) issue(r_issue, (int)(issued % ring));
+    for (; issued < ring - 1; ++issued, r_issue += n_groups) issue(r_issue, (int)(issued % ring));
 
     const Nvfp4Ctx ctx = nvfp4_ctx(kMode == kOutNvfp4 ? __ldg(a.global_scale) : 1.0f);
     const float inv_d = 1.0f / (float)D;
     const T* __restrict__ scale_g = static_cast<const T*>(a.scale);
     const T* __restrict__ shift_g = static_cast<const T*>(a.shift);
 
-    int64_t row = r0 + warp;
+    int64_t row = r0 + grp;
     int64_t i = 0;
     bool alive = true;
     for (int64_t seg = r0; seg < r1;) {
@@ -157,15 +166,15 @@ norm_stream_kernel(const NormArgs a, const int ring, const int64_t rows_per_cta,
                 __syncthreads();
             }
         }
-        for (; row < seg_end && alive; row += warps, ++i) {
+        for (; row < seg_end && alive; row += n_groups, ++i) {
             // refill the slot consumed in the previous iteration
             issue(r_issue, (int)(issued % ring));
             ++issued;
-            r_issue += warps;
+            r_issue += n_groups;
 
             if (row >= a.N) {
                 // rows that exist only as padding of the tiled scale buffer: zero their scale bytes
-                if (kMode != kOutPlain)
+                if (kMode != kOutPlain && member == 0)
                     for (int64_t c4 = lane; c4 < (a.sf_cpad >> 2); c4 += 32)
                         *reinterpret_cast<uint32_t*>(a.sf + sf_offset(row, c4 * 4, a.sf_cpad)) = 0u;
                 continue;
@@ -181,13 +190,14 @@ norm_stream_kernel(const NormArgs a, const int ring, const int64_t rows_per_cta,
                 if (!__all_sync(0xffffffffu, done != 0)) {
                     if (lane == 0) atomicCAS(&g_norm_status, 0, 1);
                     alive = false;  // stop touching rows; still take part in the CTA barriers below
-                    break;
+                    if (kGroup == 1) break;   // (a group leaves together at its barrier below)
                 }
             }
             const T* xs = reinterpret_cast<const T*>(my_rows + (size_t)slot * row_bytes);
 
-            // statistics in one pass, shifted by the row's first element
-            const float shift0 = a.rms ? 0.0f : Elem<T>::to_f32(xs[0]);
+            // statistics in one pass, shifted by the row's first element (a group's other members fetch it from
+            // global memory: it sits in the first member's buffer)
+            const float shift0 = a.rms ? 0.0f : Elem<T>::to_f32((kGroup == 1 || member == 0) ? xs[0] : xg[row * D]);
             // two accumulator pairs, updated with sm_100's packed fp32 instructions (two IEEE operations each)
             float2 s1 = make_float2(0.0f, 0.0f), s2 = s1;
             const float2 nshift = make_float2(-shift0, -shift0);
@@ -202,8 +212,22 @@ norm_stream_kernel(const NormArgs a, const int ring, const int64_t rows_per_cta,
                     s2 = __ffma2_rn(d, d, s2);
                 }
             }
-            const float m1 = warp_sum(s1.x + s1.y) * inv_d;   // mean - shift0
-            const float m2 = warp_sum(s2.x + s2.y) * inv_d;   // E[(x - shift0)^2]
+            float sum1 = warp_sum(s1.x + s1.y), sum2 = warp_sum(s2.x + s2.y);
+            if (kGroup > 1) {
+                float2* part = s_part + (grp * 2 + (int)(i & 1)) * kGroup;
+                if (lane == 0) part[member] = make_float2(sum1, sum2);
+                __syncwarp();
+                // the group's barrier: publishes the partial sums and ORs "my copy never arrived"
+                uint32_t any_failed;
+                asm volatile("{ .reg .pred p, q; setp.ne.b32 p, %1, 0; barrier.red.or.pred q, %2, %3, p; selp.u32 %0, 1, 0, q; }"
+                             : "=r"(any_failed) : "r"(alive ? 0u : 1u), "r"(1 + grp), "r"(kGroup * 32) : "memory");
+                if (any_failed) { alive = false; break; }
+                sum1 = 0.0f; sum2 = 0.0f;
+#pragma unroll
+                for (int k = 0; k < kGroup; ++k) { const float2 v = part[k]; sum1 += v.x; sum2 += v.y; }
+            }
+            const float m1 = sum1 * inv_d;   // mean - shift0
+            const float m2 = sum2 * inv_d;   // E[(x - shift0)^2]
             const float mean = a.rms ? 0.0f : shift0 + m1;
             const float var = a.rms ? m2 : fmaxf(m2 - m1 * m1, 0.0f);
             const float rstd = rsqrtf(var + a.eps);
@@ -216,8 +240,10 @@ norm_stream_kernel(const NormArgs a, const int ring, const int64_t rows_per_cta,
             // whole-warp steps: the MXFP8 block encoder shuffles between lane pairs
 #pragma unroll(kIters > 0 ? kIters : 2)
             for (int c0 = 0; c0 < nchunk; c0 += 32) {
-                const int c = c0 + lane;
+                const int c = c0 + lane;          // chunk within this warp's share
+                const int cg = cbase + c;         // chunk within the row
                 const bool ok = kIters > 0 || c < nchunk;
+                const bool row_tail = kGroup == 1 || member == kGroup - 1;   // lanes past the share's end are past the row's end
                 float y[16];
                 if (kMode == kOutMxfp8) {
                     // its block encoder shuffles between lane pairs: lanes past the row's end take part with zeros
@@ -225,7 +251,7 @@ norm_stream_kernel(const NormArgs a, const int ring, const int64_t rows_per_cta,
                     for (int j = 0; j < 16; ++j) y[j] = 0.0f;
                 } else if (!ok) {
                     // scale columns that pad the row to a multiple of 4
-                    if (kMode == kOutNvfp4 && c < a.sf_cpad) a.sf[sf_offset(row, c, a.sf_cpad)] = 0;
+                    if (kMode == kOutNvfp4 && row_tail && cg < a.sf_cpad) a.sf[sf_offset(row, cg, a.sf_cpad)] = 0;
                     continue;
                 }
                 if (ok) {
@@ -234,8 +260,8 @@ norm_stream_kernel(const NormArgs a, const int ring, const int64_t rows_per_cta,
                     if (cache_mod) {
 #pragma unroll
                         for (int j4 = 0; j4 < 4; ++j4) {
-                            const float4 mu = *reinterpret_cast<const float4*>(s_mul + mod_pos(c, j4 * 4));
-                            const float4 ad = *reinterpret_cast<const float4*>(s_add + mod_pos(c, j4 * 4));
+                            const float4 mu = *reinterpret_cast<const float4*>(s_mul + mod_pos(cg, j4 * 4));
+                            const float4 ad = *reinterpret_cast<const float4*>(s_add + mod_pos(cg, j4 * 4));
                             const float2 ya = __ffma2_rn(__ffma2_rn(make_float2(f[4 * j4 + 0], f[4 * j4 + 1]), rstd2, nmr2),
                                                          make_float2(mu.x, mu.y), make_float2(ad.x, ad.y));
                             const float2 yb = __ffma2_rn(__ffma2_rn(make_float2(f[4 * j4 + 2], f[4 * j4 + 3]), rstd2, nmr2),
@@ -246,15 +272,15 @@ norm_stream_kernel(const NormArgs a, const int ring, const int64_t rows_per_cta,
                         float m[16], b[16];
 #pragma unroll
                         for (int j = 0; j < 16; ++j) { m[j] = a.rms ? 1.0f : 0.0f; b[j] = 0.0f; }
-                        if (scale_g) load16<T>(sc + (int64_t)c * 16, m);
-                        if (shift_g) load16<T>(sh + (int64_t)c * 16, b);
+                        if (scale_g) load16<T>(sc + (int64_t)cg * 16, m);
+                        if (shift_g) load16<T>(sh + (int64_t)cg * 16, b);
 #pragma unroll
                         for (int j = 0; j < 16; ++j)
                             y[j] = fmaf(fmaf(f[j], rstd, nmr), a.rms ? m[j] : 1.0f + m[j], b[j]);
                     }
                 }
                 if (kMode == kOutPlain) {
-                    if (ok) store16<T>(static_cast<T*>(a.out) + row * D + (int64_t)c * 16, y);
+                    if (ok) store16<T>(static_cast<T*>(a.out) + row * D + (int64_t)cg * 16, y);
                 } else {
                     // the quantizers see the activation as it would have been stored
 #pragma unroll
@@ -262,8 +288,8 @@ norm_stream_kernel(const NormArgs a, const int ring, const int64_t rows_per_cta,
                     if (kMode == kOutNvfp4) {
                         uint32_t s8;
                         const uint2 packed = nvfp4_encode_block_lean(y, ctx, a.hi_first != 0, s8);
-                        *reinterpret_cast<uint2*>(static_cast<uint8_t*>(a.out) + row * (D >> 1) + (int64_t)c * 8) = packed;
-                        a.sf[sf_offset(row, c, a.sf_cpad)] = (uint8_t)s8;
+                        *reinterpret_cast<uint2*>(static_cast<uint8_t*>(a.out) + row * (D >> 1) + (int64_t)cg * 8) = packed;
+                        a.sf[sf_offset(row, cg, a.sf_cpad)] = (uint8_t)s8;
                     } else {
                         // 32-element block = this lane's chunk and its neighbour's (lane ^ 1)
                         uint32_t e;
@@ -276,11 +302,11 @@ norm_stream_kernel(const NormArgs a, const int ring, const int64_t rows_per_cta,
                         amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
                         const uint2 p0 = mxfp8_encode8(lo, amax, e), p1 = mxfp8_encode8(hi, amax, e);
                         if (ok) {
-                            *reinterpret_cast<uint4*>(static_cast<uint8_t*>(a.out) + row * D + (int64_t)c * 16) =
+                            *reinterpret_cast<uint4*>(static_cast<uint8_t*>(a.out) + row * D + (int64_t)cg * 16) =
                                 make_uint4(p0.x, p0.y, p1.x, p1.y);
-                            if ((lane & 1) == 0) a.sf[sf_offset(row, c >> 1, a.sf_cpad)] = (uint8_t)e;
-                        } else if ((lane & 1) == 0 && (c >> 1) < a.sf_cpad) {
-                            a.sf[sf_offset(row, c >> 1, a.sf_cpad)] = 0;
+                            if ((lane & 1) == 0) a.sf[sf_offset(row, cg >> 1, a.sf_cpad)] = (uint8_t)e;
+                        } else if ((lane & 1) == 0 && row_tail && (cg >> 1) < a.sf_cpad) {
+                            a.sf[sf_offset(row, cg >> 1, a.sf_cpad)] = 0;
                         }
                     }
                 }
@@ -351,6 +377,20 @@ int launch_warp(const NormArgs& a, cudaStream_t stream) {
     // and the modulation cache is worth about a quarter: so take the most warps whose rows fit once, give
     // them a second (third) buffer if there is room, and give up the cache where that doubles the warps
     // (rows of 16 KB and more).  g_norm_warps > 0 forces the warp count (up to 24, for tuning runs).
+    // Rows too wide for 16 warps to stage one each (beside the modulation cache) are shared by 2 or 4
+    // consecutive warps, each staging and processing an equal share of whole 32-element blocks: 16 warps per
+    // SM stay in flight for rows up to 48 KB.  (Measured, 18432 rows: 12288 elements 386 -> 222 us with four
+    // warps per row, 8192 elements 204 -> 147 us with two; 5120 elements fit 16 single warps and are faster so.)
+    int group = 1;
+    if (g_norm_group > 0) {
+        group = g_norm_group;
+    } else {
+        const size_t need_cache = cache_mod ? (size_t)round_up(a.D, 512) * 8 : 0;
+        while (group < 4 && 16 * (row_bytes / group) + need_cache > 225 * 1024) group *= 2;
+    }
+    if (group != 1 && group != 2 && group != 4) CK_FAIL(CK_ERR_SHAPE, "adaln: warps per row must be 1, 2 or 4");
+    if (a.D % (32 * group) != 0) group = 1;
+    const size_t warp_bytes = row_bytes / group;   // what one warp stages of a row
     int warps = 0, ring = 1;
     size_t mod_bytes = 0;
     {
@@ -364,13 +404,15 @@ int launch_warp(const NormArgs& a, cudaStream_t stream) {
             int w = 0;
             if (g_norm_warps > 0) {
                 w = g_norm_warps > 24 ? 24 : g_norm_warps;
-                if ((size_t)w * row_bytes > budget) w = 0;
+                if (group > 1 && w > 16) w = 16;
+                w -= w % group;
+                if ((size_t)w * warp_bytes > budget) w = 0;
             } else {
                 for (int cand : {16, 12, 8, 6, 4, 2, 1})
-                    if ((size_t)cand * row_bytes <= budget) { w = cand; break; }
+                    if (cand % group == 0 && (size_t)cand * warp_bytes <= budget) { w = cand; break; }
             }
             if (w == 0) continue;
-            const int r = (size_t)w * 3 * row_bytes <= budget ? 3 : ((size_t)w * 2 * row_bytes <= budget ? 2 : 1);
+            const int r = (size_t)w * 3 * warp_bytes <= budget ? 3 : ((size_t)w * 2 * warp_bytes <= budget ? 2 : 1);
             const double score = w * (cache ? 1.0 : 0.75) * (r >= 2 ? 1.0 : 0.93);
             if (score > best) { best = score; warps = w; ring = r; best_cache = cache; mod_bytes = mb; }
         }
@@ -378,15 +420,17 @@ int launch_warp(const NormArgs& a, cudaStream_t stream) {
             CK_FAIL(CK_ERR_SHAPE, "adaln: a row of %lld bytes does not fit the staging ring", (long long)row_bytes);
         cache_mod = best_cache;
     }
-    const size_t smem = mod_bytes + (size_t)warps * ring * row_bytes + (size_t)warps * ring * 8;
+    const size_t smem = mod_bytes + (size_t)warps * ring * warp_bytes + (size_t)warps * ring * 8 + (size_t)warps * 16;
     // two builds of the kernel: up to 16 warps with 128 registers per thread, up to 24 with 80
     // rows of 3072 and 4096 elements (the common hidden sizes) get fully unrolled builds
     const int iters = (a.D == 3072) ? 6 : (a.D == 4096 ? 8 : 0);
-    auto kern = warps > 16 ? norm_stream_kernel<T, kMode, 768, 0>
+    auto kern = group == 4 ? norm_stream_kernel<T, kMode, 512, 0, 4>
+              : group == 2 ? norm_stream_kernel<T, kMode, 512, 0, 2>
+              : warps > 16 ? norm_stream_kernel<T, kMode, 768, 0>
                            : (iters == 6 ? norm_stream_kernel<T, kMode, 512, 6>
                                          : (iters == 8 ? norm_stream_kernel<T, kMode, 512, 8> : norm_stream_kernel<T, kMode, 512, 0>));
-    const int attr_idx = warps > 16 ? 3 : (iters == 6 ? 1 : (iters == 8 ? 2 : 0));
-    static bool attr_set[4][64] = {};
+    const int attr_idx = group == 4 ? 5 : (group == 2 ? 4 : (warps > 16 ? 3 : (iters == 6 ? 1 : (iters == 8 ? 2 : 0))));
+    static bool attr_set[6][64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev < 0 || dev >= 64 || !attr_set[attr_idx][dev]) {
@@ -397,8 +441,8 @@ int launch_warp(const NormArgs& a, cudaStream_t stream) {
     const int64_t rows = kMode == kOutPlain ? a.N : round_up(a.N, 128);
     int sms = 148;
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    // one CTA per SM, each with a contiguous range of rows (at least one row per warp)
-    int64_t grid = ceil_div(rows, warps);
+    // one CTA per SM, each with a contiguous range of rows (at least one row per warp or group of warps)
+    int64_t grid = ceil_div(rows, warps / group);
     if (grid > sms) grid = sms;
     const int64_t rows_per_cta = ceil_div(rows, grid);
     grid = ceil_div(rows, rows_per_cta);

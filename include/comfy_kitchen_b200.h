@@ -48,9 +48,11 @@ int ck_check_device(void); /* 0 when the current device is sm_100 */
 /* Library options (process-wide).  "nvfp4_exact_div" = 1: the NVFP4 quantizer uses plain IEEE
  * divisions instead of the shared-reciprocal sequence; the bytes are the same either way (the
  * tests check that on the device), only the speed differs.  "norm_warps" = n > 0 forces the warps
- * per CTA of the norm kernels (0: the launcher chooses) and "norm_cache" = 0 keeps them from caching
- * the modulation rows in shared memory (-1: the launcher chooses); both are for tuning runs and
- * change no result. */
+ * per CTA of the norm kernels (0: the launcher chooses), "norm_cache" = 0 keeps them from caching
+ * the modulation rows in shared memory (-1: the launcher chooses) and "norm_group" = 1, 2 or 4 sets
+ * how many warps share a row (0: the launcher chooses; more than one changes the summation order of
+ * the row statistics, so a result may move by one rounding step of the output type, while the fused
+ * outputs stay equal to norm kernel -> quantizer).  All three are for tuning runs. */
 int ck_set_option(const char* name, int value);
 
 /* ---- per-tensor FP8 ----

@@ -184,6 +184,49 @@ def test_fused_vs_all_eager_composition_mismatch_rate(ck, orc, golden):
     assert (lo.float().mean() + hi.float().mean()).item() / 2 < 0.02
 
 
+@pytest.mark.parametrize("group", [2, 4])
+@pytest.mark.parametrize("N,D", [(300, 2048), (257, 4352), (130, 12288)])
+def test_warp_groups_per_row(ck, orc, group, N, D):
+    """Rows shared by 2 or 4 warps (forced here on narrow rows too; the launcher uses them for rows that do not
+    fit 16 single warps): the fused outputs still equal adaln -> quantize byte for byte, AdaLN itself stays
+    within one bf16 step of the exactly rounded value, RMSNorm takes the same path, padding rows and columns of the scale buffer
+    are written, and no bounded wait runs out."""
+    g = torch.Generator().manual_seed(12)
+    x = torch.randn(1, N, D, generator=g).bfloat16().cuda()
+    sc = (0.1 * torch.randn(1, 1, D, generator=g)).bfloat16().cuda()
+    sh = (0.1 * torch.randn(1, 1, D, generator=g)).bfloat16().cuda()
+    w = (1 + 0.1 * torch.randn(D, generator=g)).bfloat16().cuda()
+    ck.set_option("norm_group", group)
+    try:
+        y = ck.adaln(x, sc, sh, 1e-6).reshape(N, D)
+        gs = (y.float().abs().max() / (6 * 448)).float()
+        q, sf = ck.adaln_quantize_nvfp4(x, sc, sh, gs, 1e-6)
+        q2, sf2 = ck.quantize_nvfp4(y, gs)
+        assert torch.equal(q, q2) and torch.equal(sf.view(torch.uint8), sf2.view(torch.uint8))
+        q8, sf8 = ck.adaln_quantize_mxfp8(x, sc, sh, 1e-6)
+        q8b, sf8b = ck.quantize_mxfp8(y)
+        assert torch.equal(q8.view(torch.uint8), q8b.view(torch.uint8))
+        assert torch.equal(sf8.view(torch.uint8), sf8b.view(torch.uint8))
+        yr = ck.rmsnorm(x.reshape(N, D), w, 1e-6)
+        qr, sr = ck.rmsnorm_quantize_nvfp4(x.reshape(N, D), w, gs, 1e-6)
+        qr2, sr2 = ck.quantize_nvfp4(yr, gs)
+        assert torch.equal(qr, qr2) and torch.equal(sr.view(torch.uint8), sr2.view(torch.uint8))
+    finally:
+        ck.set_option("norm_group", 0)
+    # against the fp64 value rounded once to bf16: at most one bf16 step away, and rarely (the kernel's fp32
+    # statistics move a few values across a rounding boundary, with one warp per row just as with four)
+    xd = x.cpu().double()
+    mean, var = xd.mean(-1, keepdim=True), xd.var(-1, unbiased=False, keepdim=True)
+    exact = ((xd - mean) / torch.sqrt(var + 1e-6) * (1 + sc.cpu().double()) + sh.cpu().double()).reshape(N, D)
+    want = exact.float().bfloat16()
+    got = y.cpu()
+    assert (got != want).float().mean().item() < 1e-3
+    # (the absolute floor covers values that are themselves the small difference of terms of size one, where fp32
+    # evaluation is only accurate to about 1e-7 absolute)
+    assert ((got.float() - want.float()).abs() <= 2.0 ** -7 * want.float().abs() + 1e-6).all()
+    assert ck.norm_device_status() == 0
+
+
 def test_rmsnorm_quantize(ck):
     g = torch.Generator().manual_seed(10)
     x = torch.randn(300, 1024, generator=g).bfloat16().cuda()
