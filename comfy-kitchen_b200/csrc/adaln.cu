@@ -7,11 +7,12 @@
 // comfy_kitchen/backends/eager/adaln.py:11-14.  Modulation rows are grouped as in
 // comfy_kitchen/backends/_modulation.py:12-57: row r reads row r / group.
 //
-// Fast path (D a multiple of 8, row <= 16 KB): persistent warps, one row per warp at a time.  Each warp
-// owns a small ring of row buffers in shared memory that it fills with cp.async.bulk (completion on
-// its own mbarriers), so the loads of the next rows are in flight while the current row is reduced
-// and written; the row is read from shared memory three times (sum, centred sum of squares, output)
-// and from HBM once.  The result is either stored in x's dtype, or — fused variants — rounded to
+// Fast path (D a multiple of 16, row <= 48 KB): persistent warps, one row per warp at a time (per group of
+// 2 or 4 warps for rows too wide for 16 warps to stage one each).  Each warp owns a small ring of row
+// buffers in shared memory that it fills with cp.async.bulk (completion on its own mbarriers), so the
+// loads of the next rows are in flight while the current row is reduced and written; the row is read
+// from shared memory twice (shifted sums, output) and from HBM once.  The result is either stored in
+// x's dtype, or — fused variants — rounded to
 // x's dtype in registers and pushed through the same block encoders as quantize_nvfp4 /
 // quantize_mxfp8, so the packed output is byte-identical to "adaln kernel, then quantize kernel"
 // while the intermediate activation never reaches HBM (2.5625 instead of 6.5625 bytes per element
