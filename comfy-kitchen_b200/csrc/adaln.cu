@@ -390,7 +390,7 @@ int launch_warp(const NormArgs& a, cudaStream_t stream) {
         while (group < 4 && 16 * (row_bytes / group) + need_cache > 225 * 1024) group *= 2;
     }
     if (group != 1 && group != 2 && group != 4) CK_FAIL(CK_ERR_SHAPE, "adaln: warps per row must be 1, 2 or 4");
-    if (a.D % (32 * group) != 0) group = 1;
+    while (group > 1 && a.D % (32 * group) != 0) group /= 2;   // every share must be whole 32-element blocks
     const size_t warp_bytes = row_bytes / group;   // what one warp stages of a row
     int warps = 0, ring = 1;
     size_t mod_bytes = 0;
