@@ -52,7 +52,9 @@ int ck_check_device(void); /* 0 when the current device is sm_100 */
  * the modulation rows in shared memory (-1: the launcher chooses) and "norm_group" = 1, 2 or 4 sets
  * how many warps share a row (0: the launcher chooses; more than one changes the summation order of
  * the row statistics, so a result may move by one rounding step of the output type, while the fused
- * outputs stay equal to norm kernel -> quantizer).  All three are for tuning runs. */
+ * outputs stay equal to norm kernel -> quantizer).  "rope_threads_per_sm" = n > 0 sets how many threads
+ * per SM the RoPE launcher aims for when it splits the walk over the broadcast dimension (0: default).
+ * All four are for tuning runs. */
 int ck_set_option(const char* name, int value);
 
 /* ---- per-tensor FP8 ----
