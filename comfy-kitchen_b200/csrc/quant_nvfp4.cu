@@ -23,6 +23,7 @@ namespace ck {
 // 0 = reciprocal-sequence divisions (default), 1 = plain IEEE divisions everywhere.
 // Both produce the same bytes; the switch exists so tests can check that on the device.
 extern int g_nvfp4_exact_div;
+extern int g_gelu_table_min;   // activated elements from which the gather quantizer tabulates GELU per CTA (< 0: never)
 
 namespace {
 
@@ -187,6 +188,118 @@ quantize_nvfp4_gather_kernel(const QuantSegment s0, const QuantSegment s1, const
             uint8_t* dst = sf + ((int64_t)blockIdx.y * (sf_cpad >> 2) + tile_col) * 512 + (tid & 31) * 16;
             *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(s_sf + t * 512 + (tid & 31) * 16);
         }
+    }
+}
+
+// The same operator for large activated inputs.  GELU(tanh) with the accurate tanhf costs ~30 instructions per
+// element and made the kernel above instruction-bound (2 TB/s); a 16-bit input has only 65536 possible values,
+// so every CTA first tabulates round(gelu(x)) for all of them in shared memory (128 KB, filled with the very
+// function the kernel above applies, hence the same bits) and then looks elements up: two 16-bit loads per
+// pair instead of the arithmetic.  One persistent CTA of 1024 threads per SM; each quarter of it walks tiles
+// of the kernel above with its own staging area and named barrier.  The fill costs 64 evaluations per thread,
+// so the launcher takes this path only when the activated part is large (>= 16 M elements).
+constexpr int kLutThreads = 1024;
+constexpr int kLutGroups = kLutThreads / kThreads;
+constexpr int kLutSmem = 65536 * 2 + kLutGroups * kSfTiles * 512;
+
+template <typename T>
+__device__ __forceinline__ uint32_t gelu_bits(uint32_t bits);
+// Most of the table needs no evaluation.  |x| >= 8: the tanh argument exceeds 24, tanhf is exactly +-1, so the
+// result is x for positive and 0.5 * x * 0 = -0.0 for negative inputs.  bf16 with |x| < 2^-26: the tanh is below
+// 2^-26 and 1 + tanh rounds to 1, so the result is 0.5 * x, an exponent decrement.  Infinities and NaNs take the
+// arithmetic.  (The parity test compares the table path with the arithmetic kernel on all 65536 inputs.)
+template <>
+__device__ __forceinline__ uint32_t gelu_bits<__nv_bfloat16>(uint32_t bits) {
+    const uint32_t e = (bits >> 7) & 0xffu;
+    if (e >= 130u && e != 255u) return (bits & 0x8000u) ? 0x8000u : bits;
+    if (e >= 2u && e <= 100u) return bits - 0x80u;
+    const float y = Elem<__nv_bfloat16>::round(gelu_tanh(__uint_as_float(bits << 16)));
+    return __float_as_uint(y) >> 16;
+}
+template <>
+__device__ __forceinline__ uint32_t gelu_bits<__half>(uint32_t bits) {
+    const uint32_t e = (bits >> 10) & 0x1fu;
+    if (e >= 18u && e != 31u) return (bits & 0x8000u) ? 0x8000u : bits;
+    const __half_raw in{(unsigned short)bits};
+    const __half out = __float2half_rn(gelu_tanh(__half2float(__half(in))));
+    return (uint32_t)__half_raw(out).x;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kLutThreads, 1)
+quantize_nvfp4_gather_lut_kernel(const QuantSegment s0, const QuantSegment s1, const float* __restrict__ global_scale,
+                                 uint8_t* __restrict__ q, uint8_t* __restrict__ sf, int64_t rows, int64_t cols,
+                                 int64_t sf_cpad, bool hi_first, int tiles_x, int64_t num_tiles) {
+    extern __shared__ __align__(16) uint8_t lut_smem[];
+    uint16_t* lut = reinterpret_cast<uint16_t*>(lut_smem);
+    const int grp = threadIdx.x / kThreads, tid = threadIdx.x % kThreads;
+    uint8_t* s_sf = lut_smem + 65536 * 2 + grp * (kSfTiles * 512);
+    for (uint32_t i = threadIdx.x; i < 65536u; i += kLutThreads) lut[i] = (uint16_t)gelu_bits<T>(i);
+    __syncthreads();
+
+    const int blk = tid & 15, sub = tid >> 4;
+    const Nvfp4Ctx ctx = nvfp4_ctx(__ldg(global_scale));
+    const uint32_t bar_id = 1 + grp;
+    for (int64_t tile = (int64_t)blockIdx.x * kLutGroups + grp; tile < num_tiles; tile += (int64_t)gridDim.x * kLutGroups) {
+        const int64_t tile_x = tile % tiles_x, tile_y = tile / tiles_x;
+        const int64_t row0 = tile_y * kTileRows;
+        const int64_t col = tile_x * kTileCols + blk * 16;
+        reinterpret_cast<uint2*>(s_sf)[tid] = make_uint2(0u, 0u);
+        asm volatile("bar.sync %0, %1;" ::"r"(bar_id), "r"(kThreads) : "memory");
+
+        const bool col_ok = col < cols;
+        const bool second = col >= s0.cols;
+        const QuantSegment& sg = second ? s1 : s0;
+        const int64_t c = second ? col - s0.cols : col;
+        const T* src = nullptr;
+        int64_t row_stride = 0;
+        int act = 0;
+        if (col_ok) {
+            src = static_cast<const T*>(sg.base) + (c / sg.group) * sg.group_stride + c % sg.group;
+            row_stride = sg.row_stride;
+            act = sg.act;
+        }
+        constexpr int kUnroll = 4;
+#pragma unroll 1
+        for (int it = 0; it < kTileRows / kRowsPerStep; it += kUnroll) {
+            Raw16<T> raw[kUnroll];
+#pragma unroll
+            for (int u = 0; u < kUnroll; ++u) {
+                const int64_t row = row0 + (it + u) * kRowsPerStep + sub;
+                if (col_ok && row < rows) load_raw16<T>(src + row * row_stride, raw[u]);
+                else zero_raw16<T>(raw[u]);
+            }
+#pragma unroll
+            for (int u = 0; u < kUnroll; ++u) {
+                const int r_in_tile = (it + u) * kRowsPerStep + sub;
+                const int64_t row = row0 + r_in_tile;
+                if (act == 1) {
+#pragma unroll
+                    for (int k = 0; k < 8; ++k) {
+                        const uint32_t w = raw[u].w[k];
+                        raw[u].w[k] = (uint32_t)lut[w & 0xffffu] | ((uint32_t)lut[w >> 16] << 16);
+                    }
+                }
+                float v[16];
+                unpack16(raw[u], v);
+                uint32_t s8;
+                const uint2 packed = nvfp4_encode_block<false>(v, ctx, hi_first, s8);
+                if (col_ok && row < rows) {
+                    *reinterpret_cast<uint2*>(q + row * (cols >> 1) + (col >> 1)) = packed;
+                    s_sf[(blk >> 2) * 512 + sf_tile_offset(r_in_tile, blk & 3)] = (uint8_t)s8;
+                }
+            }
+        }
+        asm volatile("bar.sync %0, %1;" ::"r"(bar_id), "r"(kThreads) : "memory");
+        if (tid < kSfTiles * 32) {
+            const int t = tid >> 5;
+            const int64_t tile_col = (tile_x * kTileCols >> 6) + t;
+            if (tile_col < (sf_cpad >> 2)) {
+                uint8_t* dst = sf + (tile_y * (sf_cpad >> 2) + tile_col) * 512 + (tid & 31) * 16;
+                *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(s_sf + t * 512 + (tid & 31) * 16);
+            }
+        }
+        asm volatile("bar.sync %0, %1;" ::"r"(bar_id), "r"(kThreads) : "memory");   // staging is read before the next tile clears it
     }
 }
 
@@ -362,6 +475,29 @@ extern "C" int launch_quantize_nvfp4_gather_kernel(const void* base0, int64_t co
     auto* g = static_cast<const float*>(global_scale);
     auto* q = static_cast<uint8_t*>(output);
     auto* sf = static_cast<uint8_t*>(block_scales);
+    const int64_t act_elems = num_rows * ((act0 == 1 ? cols0 : 0) + ((cols1 > 0 && act1 == 1) ? cols1 : 0));
+    if (act_elems >= g_gelu_table_min && g_gelu_table_min >= 0) {
+        // large activated input: tabulate the activation per CTA and look it up
+        int dev = 0, sms = 148;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        const int64_t num_tiles = (int64_t)grid.x * grid.y;
+        int64_t ctas = ceil_div(num_tiles, (int64_t)kLutGroups);
+        if (ctas > sms) ctas = sms;
+        static bool attr_set[2][64] = {};
+        const int ti = input_dtype_code == CK_BF16 ? 0 : 1;
+        if (dev < 0 || dev >= 64 || !attr_set[ti][dev]) {
+            cudaError_t e = ti == 0 ? cudaFuncSetAttribute(quantize_nvfp4_gather_lut_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, kLutSmem)
+                                    : cudaFuncSetAttribute(quantize_nvfp4_gather_lut_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, kLutSmem);
+            if (e != cudaSuccess) CK_FAIL((int)e, "quantize_nvfp4_gather: cannot reserve shared memory: %s", cudaGetErrorString(e));
+            if (dev >= 0 && dev < 64) attr_set[ti][dev] = true;
+        }
+        if (ti == 0)
+            quantize_nvfp4_gather_lut_kernel<__nv_bfloat16><<<(unsigned)ctas, kLutThreads, kLutSmem, stream>>>(s0, s1, g, q, sf, num_rows, cols, sf_cpad, hi_first, (int)grid.x, num_tiles);
+        else
+            quantize_nvfp4_gather_lut_kernel<__half><<<(unsigned)ctas, kLutThreads, kLutSmem, stream>>>(s0, s1, g, q, sf, num_rows, cols, sf_cpad, hi_first, (int)grid.x, num_tiles);
+        return launch_status("quantize_nvfp4_gather");
+    }
     if (input_dtype_code == CK_BF16)
         quantize_nvfp4_gather_kernel<__nv_bfloat16><<<grid, kThreads, 0, stream>>>(s0, s1, g, q, sf, num_rows, cols, sf_cpad, hi_first);
     else

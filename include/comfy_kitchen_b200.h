@@ -54,7 +54,8 @@ int ck_check_device(void); /* 0 when the current device is sm_100 */
  * the row statistics, so a result may move by one rounding step of the output type, while the fused
  * outputs stay equal to norm kernel -> quantizer).  "rope_threads_per_sm" = n > 0 sets how many threads
  * per SM the RoPE launcher aims for when it splits the walk over the broadcast dimension (0: default).
- * All four are for tuning runs. */
+ * "gelu_table_min" = n: the gather quantizer tabulates GELU per CTA from n activated elements on
+ * (default 16 Mi; negative: never; the bytes are the same either way).  All five are for tuning runs. */
 int ck_set_option(const char* name, int value);
 
 /* ---- per-tensor FP8 ----

@@ -294,6 +294,34 @@ def test_quantize_nvfp4_gather_matches_concatenation():
     assert bad_codes < 2e-3 and bad_scales < 2e-3, (bad_codes, bad_scales)
 
 
+@pytest.mark.parametrize("dt", [torch.bfloat16, torch.float16])
+def test_quantize_nvfp4_gather_table_path_equals_arithmetic_path(dt):
+    """Large activated inputs go through a per-CTA table of round(gelu(x)) over all 65536 input values; forced
+    here on a small input (option gelu_table_min = 0) and compared with the arithmetic kernel (option -1): the
+    bytes are the same, for every input value (the second segment holds all 65536 bit patterns, NaNs included)
+    and for random data, with and without a plain first segment, at a ragged row count."""
+    from comfy_kitchen.backends import cuda as ck
+
+    g = torch.Generator().manual_seed(6)
+    rows = 300
+    every = torch.arange(65536, dtype=torch.int32).to(torch.int16).view(dt).reshape(64, 1024)   # each value once
+    rnd = (2.0 * torch.randn(rows - 64, 1024, generator=g)).to(dt)
+    act = torch.cat([every, rnd]).cuda()
+    plain = torch.randn(rows, 384, generator=g).to(dt).cuda()
+    gs = torch.tensor(4.0 / (6 * 448)).cuda()
+    outs = {}
+    try:
+        for mode in (-1, 0):
+            ck.set_option("gelu_table_min", mode)
+            outs[mode] = (ck.quantize_nvfp4_gather([(plain, None), (act, "gelu_tanh")], gs),
+                          ck.quantize_nvfp4_gather([(act, "gelu_tanh")], gs))
+    finally:
+        ck.set_option("gelu_table_min", 16 << 20)
+    for (qa, sa), (qb, sb) in zip(outs[-1], outs[0]):
+        assert torch.equal(qa, qb)
+        assert torch.equal(sa.view(torch.uint8), sb.view(torch.uint8))
+
+
 @pytest.mark.parametrize("ot", [torch.float8_e4m3fn, torch.float8_e5m2])
 def test_stochastic_rounding_exhaustive(ck, orc, ot):
     """All 65536 fp16 inputs x all 256 random bytes against the oracle (which the reference fixtures pin), and
