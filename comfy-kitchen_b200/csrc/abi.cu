@@ -22,17 +22,23 @@ extern "C" const char* ck_last_error(void) { return ck::g_error; }
 
 extern "C" int ck_abi_version(void) { return 1; }
 
-namespace ck { int g_nvfp4_exact_div = 0; int g_norm_warps = 0; int g_norm_cache = -1; int g_norm_group = 0; int g_rope_threads_per_sm = 0; int g_gelu_table_min = 16 << 20; }
+namespace ck {
+int g_nvfp4_exact_div = 0, g_norm_warps = 0, g_norm_cache = -1, g_norm_group = 0, g_norm_poll_limit = 0;
+int g_rope_threads_per_sm = 0, g_gelu_table_min = 16 << 20, g_gemm_tile = 0, g_gemm_map_cache = 1;
+}
 
-// Library options.  "nvfp4_exact_div": 1 makes the NVFP4 quantizer use plain IEEE divisions
-// instead of the shared-reciprocal sequence (same bytes, slower); used by the tests.
+// Library options: the public one is described in the C header, the tuning knobs in ck_options.h.
 extern "C" int ck_set_option(const char* name, int value) {
+    static const struct { const char* name; int* slot; } table[] = {
+        {"norm_warps", &ck::g_norm_warps},   {"norm_cache", &ck::g_norm_cache},
+        {"norm_group", &ck::g_norm_group},   {"norm_poll_limit", &ck::g_norm_poll_limit},
+        {"rope_threads_per_sm", &ck::g_rope_threads_per_sm}, {"gelu_table_min", &ck::g_gelu_table_min},
+        {"gemm_tile", &ck::g_gemm_tile},     {"gemm_map_cache", &ck::g_gemm_map_cache},
+    };
     if (name && !strcmp(name, "nvfp4_exact_div")) { ck::g_nvfp4_exact_div = value ? 1 : 0; return CK_OK; }
-    if (name && !strcmp(name, "norm_warps")) { ck::g_norm_warps = value; return CK_OK; }   // 0 = choose; for tuning runs
-    if (name && !strcmp(name, "rope_threads_per_sm")) { ck::g_rope_threads_per_sm = value; return CK_OK; }   // 0 = default
-    if (name && !strcmp(name, "gelu_table_min")) { ck::g_gelu_table_min = value; return CK_OK; }   // elements; < 0 = never tabulate
-    if (name && !strcmp(name, "norm_group")) { ck::g_norm_group = value; return CK_OK; }   // 0 = choose; 1, 2, 4 warps per row
-    if (name && !strcmp(name, "norm_cache")) { ck::g_norm_cache = value; return CK_OK; }   // -1 = choose; 0 / 1 = modulation cache off / on where possible
+    if (name)
+        for (const auto& t : table)
+            if (!strcmp(name, t.name)) { *t.slot = value; return CK_OK; }
     CK_FAIL(CK_ERR_UNSUPPORTED, "ck_set_option: unknown option '%s'", name ? name : "(null)");
 }
 

@@ -20,9 +20,6 @@
 #include "ck_common.cuh"
 
 namespace ck {
-extern int g_norm_warps;   // 0 = the launcher chooses; > 0 forces the warps per CTA (tuning runs)
-extern int g_norm_cache;   // -1 = the launcher chooses; 0 = no modulation cache (tuning runs)
-extern int g_norm_group;   // 0 = the launcher chooses; 1, 2, 4 = warps that share a row (tuning runs)
 namespace {
 
 enum OutMode { kOutPlain = 0, kOutNvfp4 = 1, kOutMxfp8 = 2 };
@@ -94,7 +91,8 @@ constexpr uint32_t kRowWaitLimit = 1u << 22;
 // (which also carries "a copy never arrived", so that the group leaves together).
 template <typename T, int kMode, int kMaxThreads, int kIters, int kGroup = 1>
 __global__ void __launch_bounds__(kMaxThreads)
-norm_stream_kernel(const NormArgs a, const int ring, const int64_t rows_per_cta, const int cache_mod) {
+norm_stream_kernel(const NormArgs a, const int ring, const int64_t rows_per_cta, const int cache_mod,
+                   const uint32_t poll_limit) {
     extern __shared__ __align__(128) uint8_t smem[];
     const int warps = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int grp = warp / kGroup, member = warp % kGroup, n_groups = warps / kGroup;
@@ -185,7 +183,7 @@ norm_stream_kernel(const NormArgs a, const int ring, const int64_t rows_per_cta,
             {
                 const uint32_t bar = smem_u32(&my_bars[slot]), parity = (uint32_t)((i / ring) & 1);
                 uint32_t done = 0;
-                for (uint32_t spin = 0; spin < kRowWaitLimit && !done; ++spin)
+                for (uint32_t spin = 0; spin < poll_limit && !done; ++spin)
                     asm volatile("{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
                                  : "=r"(done) : "r"(bar), "r"(parity) : "memory");
                 if (!__all_sync(0xffffffffu, done != 0)) {
@@ -315,6 +313,19 @@ norm_stream_kernel(const NormArgs a, const int ring, const int64_t rows_per_cta,
             __syncwarp();  // every lane is done with this slot before it is refilled
         }
         seg = seg_end;
+    }
+    if (!alive) {
+        // A wait ran out (or a group member's did).  The copies this warp issued for rows i .. issued-1 may still
+        // be in flight: shared memory must not be released under them, so wait for each with the full limit.
+        const int64_t lim = min(r1, a.N);
+        for (int64_t j = i; j < issued; ++j) {
+            if (r0 + grp + j * n_groups >= lim) break;
+            const uint32_t bar = smem_u32(&my_bars[j % ring]), parity = (uint32_t)((j / ring) & 1);
+            uint32_t done = 0;
+            for (uint32_t spin = 0; spin < kRowWaitLimit && !done; ++spin)
+                asm volatile("{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
+                             : "=r"(done) : "r"(bar), "r"(parity) : "memory");
+        }
     }
 }
 
@@ -447,7 +458,8 @@ int launch_warp(const NormArgs& a, cudaStream_t stream) {
     if (grid > sms) grid = sms;
     const int64_t rows_per_cta = ceil_div(rows, grid);
     grid = ceil_div(rows, rows_per_cta);
-    kern<<<(unsigned)grid, warps * 32, smem, stream>>>(a, ring, rows_per_cta, cache_mod);
+    const uint32_t poll_limit = g_norm_poll_limit == 0 ? kRowWaitLimit : (g_norm_poll_limit < 0 ? 0u : (uint32_t)g_norm_poll_limit);
+    kern<<<(unsigned)grid, warps * 32, smem, stream>>>(a, ring, rows_per_cta, cache_mod, poll_limit);
     return launch_status("adaln");
 }
 
@@ -556,6 +568,6 @@ extern "C" int ck_norm_device_status(void) {
     e = cudaMemcpyFromSymbol(&v, ck::g_norm_status, sizeof(int));
     if (e != cudaSuccess) CK_FAIL((int)e, "norm status: %s", cudaGetErrorString(e));
     cudaMemcpyToSymbol(ck::g_norm_status, &zero, sizeof(int));
-    if (v != 0) ck::set_error("norm kernel: a bounded wait on a row copy ran out");
-    return v;
+    if (v != 0) CK_FAIL(CK_ERR_DEVICE_TIMEOUT, "norm kernel: a bounded wait on a row copy ran out");
+    return CK_OK;
 }

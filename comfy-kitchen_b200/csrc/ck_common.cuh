@@ -14,14 +14,10 @@
 #define CK_E4M3 5
 #define CK_E5M2 6
 
-// status codes returned by every launch_* entry point
-#define CK_OK 0
-#define CK_ERR_DTYPE (-1)
-#define CK_ERR_SHAPE (-2)
-#define CK_ERR_ALIGN (-3)
-#define CK_ERR_NULL (-4)
-#define CK_ERR_UNSUPPORTED (-5)
-#define CK_ERR_DEVICE_TIMEOUT (-6)
+// Status codes and the declaration of every extern "C" entry point: including the public header here
+// makes the compiler check each definition in csrc/*.cu against what callers bind to.
+#include "comfy_kitchen_b200.h"
+#include "ck_options.h"
 
 namespace ck {
 

@@ -10,7 +10,7 @@
 // (MXFP8); the reference's CUDA backend forwards NVFP4 to a library GEMM
 // (backends/cuda/ops/cublas_gemm_nvfp4.cu:64-340) and has no MXFP8 kernel.
 //
-// Kernel structure: persistent clusters of two CTAs (one per SM of a pair), 704
+// Kernel structure: persistent clusters of two CTAs (one per SM of a pair), 736
 // threads each.  A pair works on a 256 x 256 output tile with tcgen05.mma
 // .cta_group::2: CTA r of the pair holds rows 128r..128r+127 of the A tile, rows
 // 128r..128r+127 of the W tile (i.e. half of N) and, in TMEM, the 128 x 256 fp32
@@ -82,19 +82,10 @@ constexpr uint32_t kTmemAcc = 0;
 __device__ __forceinline__ uint32_t tmem_sfa_col(uint32_t b) { return 256u + 48u * b; }
 __device__ __forceinline__ uint32_t tmem_sfb_col(uint32_t b) { return 272u + 48u * b; }
 
-#ifndef CK_GEMM_PROBE
-#define CK_GEMM_PROBE 0   // timing experiments only: 1 = no scale moves, 8 = timestamps, 16 = no epilogue work
-#endif
 
 constexpr uint32_t kSpinLimit = 1u << 22;   // polls of mbarrier.try_wait before giving up (a fraction of a second)
 
 __device__ int g_gemm_status = 0;           // 0 ok; otherwise (code << 16 | CTA) of the first failure
-#if CK_GEMM_PROBE & 8
-__device__ long long g_probe_ts[7 * 4 * 256];   // pair 0, per role and k-tile: timestamps (role 0 MMA, 1/2 movers, 3/4 producers of CTA 0/1)
-#define CK_TS(role, it, k) do { if (pair == 0 && lane == 0 && (it) < 256) g_probe_ts[(role) * 1024 + 4 * (it) + (k)] = clock64(); } while (0)
-#else
-#define CK_TS(role, it, k) do { } while (0)
-#endif
 
 enum : int { kTimeoutFull = 1, kTimeoutEmpty = 2, kTimeoutTmemFull = 3, kTimeoutTmemEmpty = 4, kTimeoutSfFull = 5 };
 
@@ -185,15 +176,8 @@ __device__ __forceinline__ void bulk_load(void* dst, const void* src, uint32_t b
 }
 // Shared -> global tile store (clipped at the tensor's edges), tracked by the issuing thread's bulk groups.
 __device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, const void* src, int c0, int c1) {
-#if CK_GEMM_PROBE & 16384   // timing experiment: output lines marked evict-first in L2
-    uint64_t policy;
-    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(policy));
-    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group.L2::cache_hint [%0, {%2, %3}], [%1], %4;"
-                 ::"l"(map), "r"(smem_u32(src)), "r"(c0), "r"(c1), "l"(policy) : "memory");
-#else
     asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
                  ::"l"(map), "r"(smem_u32(src)), "r"(c0), "r"(c1) : "memory");
-#endif
     asm volatile("cp.async.bulk.commit_group;" ::: "memory");
 }
 __device__ __forceinline__ void bulk_wait_read_all() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
@@ -328,8 +312,7 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
     uint64_t* tmem_full = sf_full + kSfBufs;  //            accumulator complete -> epilogue
     uint64_t* tmem_empty = tmem_full + 1;     //            (leader's) both CTAs' accumulators copied out -> MMA issuer
     uint64_t* tile_open = tmem_empty + 1;     //            first MMA of a tile issued -> the second MMA issuer
-    uint64_t* probe_bar = tile_open + 1;      //            timing experiments only
-    uint32_t* s_tmem_base = reinterpret_cast<uint32_t*>(probe_bar + 1);
+    uint32_t* s_tmem_base = reinterpret_cast<uint32_t*>(tile_open + 1);
     volatile int* s_abort = reinterpret_cast<volatile int*>(s_tmem_base + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -347,7 +330,6 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
         mbar_init(tmem_full, 2);   // one commit per tile from each MMA issuer
         mbar_init(tile_open, 1);
         mbar_init(tmem_empty, 2 * kEpiWarps);
-        mbar_init(probe_bar, 1u << 20);
         *s_abort = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -378,22 +360,18 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
             for (int kt = 0; kt < k_tiles && ok; ++kt, ++it) {
                 const int s = it % kStages;
                 const uint32_t round = it / kStages;
-                CK_TS(3 + rank, it, 0);
                 if (round > 0) ok = mbar_wait(&empty[s], (round - 1) & 1, s_abort, kTimeoutEmpty);
                 if (!ok) break;
-                CK_TS(3 + rank, it, 1);
                 // operands are computed by the whole warp; one elected lane issues the copies
                 uint8_t* st = stage_base + s * kStageBytes;
                 int n_sf = p.sf_tiles_k - kt * kSfTilesPerStage;  // scale tiles valid in this k-tile (the last may be short)
                 if (n_sf > kSfTilesPerStage) n_sf = kSfTilesPerStage;
                 const uint32_t sf_bytes = (uint32_t)n_sf * 512u;
                 const size_t sf_off = (size_t)kt * (kSfTilesPerStage * 512);
-                // 2048: timing experiment — A is loaded for every other k-tile only (what sharing A between pairs would save)
-                const bool skip_a = (CK_GEMM_PROBE & 2048) && (kt & 1);
-                const uint32_t tx_bytes = (skip_a ? 0 : kSmemA) + kSmemB + sf_bytes * ((have_a ? 1 : 0) + b_tiles);
+                const uint32_t tx_bytes = kSmemA + kSmemB + sf_bytes * ((have_a ? 1 : 0) + b_tiles);
                 if (elect_one()) {
                     mbar_expect_tx(&full[s], tx_bytes);
-                    if (!skip_a) tma_load_2d(st, &map_a, kt * 128, tm * 256 + (int)rank * BM, &full[s]);
+                    tma_load_2d(st, &map_a, kt * 128, tm * 256 + (int)rank * BM, &full[s]);
                     tma_load_2d(st + kSmemA, &map_b, kt * 128, tn * BN + (int)rank * (BN / 2), &full[s]);
                     if (have_a) bulk_load(st + kSmemA + kSmemB, sfa_src + sf_off, sf_bytes, &full[s]);
                     bulk_load(st + kSmemA + kSmemB + kSmemSfA, sfb_src + sf_off, sf_bytes, &full[s]);
@@ -402,7 +380,6 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
                                   sf_bytes, &full[s]);
                 }
                 __syncwarp();
-                CK_TS(3 + rank, it, 2);   // copies of this k-tile issued
             }
         }
         // drain: every copy this warp issued must have landed before the CTA may exit
@@ -425,16 +402,13 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
             for (int kt = 0; kt < k_tiles && ok; ++kt, ++it) {
                 const int s = it % kStages;
                 const uint32_t b = it % kSfBufs;
-                if (warp == kFirstMoverWarp) CK_TS(1 + rank, it, 0);
                 ok = mbar_wait(&full[s], (it / kStages) & 1, s_abort, kTimeoutFull);
                 if (!ok) break;
-                if (warp == kFirstMoverWarp) CK_TS(1 + rank, it, 1);
                 const uint8_t* sfa_s = stage_base + s * kStageBytes + kSmemA + kSmemB + lane * 16;
                 const uint8_t* sfb_s = sfa_s + kSmemSfA;
                 constexpr int kNa = kFp4 ? 16 : 4, kNb = kFp4 ? 32 : 8;   // words per lane: A scales, W scales
                 uint32_t ra[kNa], rb[kNb];
-                if constexpr ((CK_GEMM_PROBE & 1) != 0) {
-                } else {
+                {
 #pragma unroll
                     for (int t = 0; t < kSfTilesPerStage; ++t) {  // k-block t: A columns 4t.., W columns 8t.. (first, then second row tile)
                         const uint4 v = *reinterpret_cast<const uint4*>(sfa_s + t * 512);
@@ -455,11 +429,9 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
                     if (!ok) break;
                 }
                 tc_fence_after();
-                if (warp == kFirstMoverWarp) CK_TS(1 + rank, it, 2);
                 const uint32_t t_sfa = tmem_base + lane_base + tmem_sfa_col(b);
                 const uint32_t t_sfb = tmem_base + lane_base + tmem_sfb_col(b);
-                if constexpr ((CK_GEMM_PROBE & 1) != 0) {
-                } else if constexpr (kFp4) {
+                if constexpr (kFp4) {
                     tc_st16(t_sfa, ra);
                     tc_st16(t_sfb, rb);
                     tc_st16(t_sfb + 16, rb + 16);
@@ -471,7 +443,6 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive_cluster(&sf_full[b], 0);   // the leader's barrier
-                if (warp == kFirstMoverWarp) CK_TS(1 + rank, it, 3);
             }
         }
     } else if (warp == 1 || warp == kSecondMmaWarp) {
@@ -492,15 +463,9 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
         bool ok = true, ready = false;
         for (int tile = pair; tile < num_tiles && ok; tile += num_pairs, ++local_tile) {
             ready = false;
-#if CK_GEMM_PROBE & 8
-            if (which == 0) CK_TS(0, 240 + local_tile, 0);
-#endif
             if (local_tile > 0) ok = mbar_wait(tmem_empty, (local_tile - 1) & 1, s_abort, kTimeoutTmemEmpty);
             if (!ok) break;
             tc_fence_after();
-#if CK_GEMM_PROBE & 8
-            if (which == 0) CK_TS(0, 240 + local_tile, 1);
-#endif
             const uint32_t d_tmem = tmem_base + kTmemAcc;
             if (which == 1 && k_tiles > 1) {   // the overwriting MMA must be in the pipe before any of mine
                 ok = mbar_wait(tile_open, local_tile & 1, s_abort, kTimeoutTmemEmpty);
@@ -510,17 +475,11 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
                 if ((uint32_t)(kt & 1) != which) continue;
                 const int s = it % kStages;
                 const uint32_t sb = it % kSfBufs;
-#if CK_GEMM_PROBE & 8
-                if (which == 0) CK_TS(0, it, 0);
-#endif
                 // The movers of both CTAs publish sf_full only after they saw their full[s], so this one wait
                 // covers the operands too.  `ready` is an early look taken while the previous k-tile was issued.
                 if (!__all_sync(0xffffffffu, ready)) ok = mbar_wait(&sf_full[sb], (it / kSfBufs) & 1, s_abort, kTimeoutSfFull);
                 if (!ok) break;
                 tc_fence_after();
-#if CK_GEMM_PROBE & 8
-                if (which == 0) CK_TS(0, it, 1);
-#endif
                 // every descriptor of this stage is "stage start >> 4" plus a constant (the same in both CTAs)
                 const uint32_t st16 = smem16 + (uint32_t)s * (kStageBytes >> 4);
                 const uint32_t a_lo = st16 | kDescLoLbo1, b_lo = (st16 + (kSmemA >> 4)) | kDescLoLbo1;
@@ -535,23 +494,13 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
                         if (kFp4) { sfa += 4 * kb; sfb += 8 * kb; }
                         else { idesc |= ((uint32_t)kb << 29) | ((uint32_t)kb << 4); }
                         tc_mma<kFp4>(d_tmem, a_lo + 2 * kb, b_lo + 2 * kb, idesc, (kt > 0 || kb > 0) ? 1u : 0u, sfa, sfb);
-#if (CK_GEMM_PROBE & 4104) == 4104   // fine-grained issue trace: role 5 = after each MMA issue
-                        if (which == 0) CK_TS(5, it, kb);
-#endif
                         if (kt == 0 && kb == 0 && lane == 0) mbar_arrive(tile_open);   // which == 0 here
                     }
                     // the pipe is busy with these for a while: look at my next k-tile's barrier now
                     if (kb == 1) ready = kt + 2 < k_tiles &&
                                          mbar_test_wait(&sf_full[(it + 2) % kSfBufs], ((it + 2) / kSfBufs) & 1);
                 }
-                if (CK_GEMM_PROBE & 256) tc_commit_pair(probe_bar);   // timing experiment: what one more commit costs
                 tc_commit_pair(&empty[s]);                      // stage and scale buffer reusable once these MMAs are done
-#if (CK_GEMM_PROBE & 4104) == 4104
-                if (which == 0) CK_TS(6, it, 0);   // after the stage commit
-#endif
-#if CK_GEMM_PROBE & 8
-                if (which == 0) CK_TS(0, it, 2);
-#endif
             }
             // the accumulator is complete when both issuers' MMAs are (an issuer that had no k-tile in this tile
             // commits nothing and arrives at once)
@@ -594,20 +543,15 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
             ok = mbar_wait(tmem_full, local_tile & 1, s_abort, kTimeoutTmemFull);
             if (!ok) break;
             tc_fence_after();
-            if (warp == kFirstEpiWarp) CK_TS(1 + rank, 240 + local_tile, 0);
             const uint32_t acc = tmem_base + kTmemAcc + ((uint32_t)(q * 32) << 16) + (uint32_t)(part * 64);
             const int row0 = tm * 256 + (int)rank * BM + q * 32;   // first of this warp's 32 rows
             uint32_t r[2][32];
-            if (!(CK_GEMM_PROBE & 16)) {
-                tc_ld32(acc, r[0]);
-                tc_ld32(acc + 32, r[1]);
-                tc_wait_ld();
-            }
+            tc_ld32(acc, r[0]);
+            tc_ld32(acc + 32, r[1]);
+            tc_wait_ld();
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(tmem_empty, 0);
-            if (warp == kFirstEpiWarp) CK_TS(1 + rank, 240 + local_tile, 2);
-            if (CK_GEMM_PROBE & 16) continue;
             const bool store_ok = row0 < p.M;
             // a staging chunk is 32 rows x 64 bytes: 32 columns of a 16-bit output, 16 of an fp32 one
             const int n_chunks = p.out_code == CK_F32 ? 4 : 2;
@@ -637,17 +581,14 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
                                 w[i] = __float_as_uint(fmaf(__uint_as_float(r[c >> 5][c & 31]), alpha, bias_at(c)));
                             }
                         }
-                        if (!(CK_GEMM_PROBE & 1024) || w[0] == 0x12345678u)   // 1024: timing experiment without the staging writes
                         *reinterpret_cast<uint4*>(my_row + ((j ^ sw) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
                     }
-                    if (!(CK_GEMM_PROBE & 512)) fence_async_smem();   // 512: timing experiment without the proxy fence
+                    fence_async_smem();
                     __syncwarp();
                     const int col = n0 + ch * chunk_cols;
-                    if (lane == 0 && store_ok && col < p.N && !(CK_GEMM_PROBE & 32))
-                        tma_store_2d(&map_out, stg, (CK_GEMM_PROBE & 8192) ? (e & 3) * 32 : col, (CK_GEMM_PROBE & 8192) ? (e >> 2) * 32 : row0);   // 8192: timing experiment, every store lands on the same 16 KB
+                    if (lane == 0 && store_ok && col < p.N) tma_store_2d(&map_out, stg, col, row0);
                 }
             }
-            if (warp == kFirstEpiWarp) CK_TS(1 + rank, 240 + local_tile, 3);
         }
         if (lane == 0) bulk_wait_all();   // the staging buffer must outlive the stores that read it
         __syncwarp();
@@ -829,15 +770,9 @@ extern "C" int launch_cublas_gemm_blockwise_fp4_kernel(const void* B_ptr, const 
                                  M, N, K, alpha_device_ptr, out_dtype_code, stream);
 }
 
-#if CK_GEMM_PROBE & 8
-extern "C" int ck_probe_read(long long* out) {
-    cudaDeviceSynchronize();
-    return (int)cudaMemcpyFromSymbol(out, ck::g_probe_ts, sizeof(long long) * 7 * 4 * 256);
-}
-#endif
 
 // Reads and clears the device-side status word of the GEMM kernels (synchronises the device).
-// 0 = no bounded wait ran out since the last call.
+// 0 = no bounded wait ran out since the last call, CK_ERR_DEVICE_TIMEOUT otherwise.
 extern "C" int ck_gemm_device_status(void) {
     int v = 0, zero = 0;
     cudaError_t e = cudaDeviceSynchronize();
@@ -845,6 +780,6 @@ extern "C" int ck_gemm_device_status(void) {
     e = cudaMemcpyFromSymbol(&v, ck::g_gemm_status, sizeof(int));
     if (e != cudaSuccess) CK_FAIL((int)e, "gemm status: %s", cudaGetErrorString(e));
     cudaMemcpyToSymbol(ck::g_gemm_status, &zero, sizeof(int));
-    if (v != 0) ck::set_error("gemm kernel: bounded wait %d ran out in CTA %d", v >> 16, v & 0xffff);
-    return v;
+    if (v != 0) CK_FAIL(CK_ERR_DEVICE_TIMEOUT, "gemm kernel: bounded wait %d ran out in CTA %d", v >> 16, v & 0xffff);
+    return CK_OK;
 }

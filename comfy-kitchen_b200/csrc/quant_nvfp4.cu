@@ -22,8 +22,6 @@ namespace ck {
 
 // 0 = reciprocal-sequence divisions (default), 1 = plain IEEE divisions everywhere.
 // Both produce the same bytes; the switch exists so tests can check that on the device.
-extern int g_nvfp4_exact_div;
-extern int g_gelu_table_min;   // activated elements from which the gather quantizer tabulates GELU per CTA (< 0: never)
 
 namespace {
 

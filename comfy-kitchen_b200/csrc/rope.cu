@@ -16,7 +16,6 @@
 #include "ck_common.cuh"
 
 namespace ck {
-extern int g_rope_threads_per_sm;   // 0 = default; threads per SM the launcher aims for when it splits the broadcast walk (tuning runs)
 namespace {
 
 struct RopeParams {

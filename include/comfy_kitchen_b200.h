@@ -6,7 +6,7 @@
  * Conventions
  *   - every pointer is a DEVICE pointer on the current device unless stated;
  *     the library never allocates, frees or synchronises (the two
- *     ck_*_device_status calls excepted) and launches on the stream it is given;
+ *     ck_*_device_status calls excepted, which synchronise) and launches on the stream it is given;
  *   - dtype codes: 0 float32, 1 float16, 2 bfloat16, 5 float8_e4m3fn, 6 float8_e5m2
  *     (comfy_kitchen/backends/eager/quantization.py:33-41);
  *   - block scales use the 128x4 tiled layout of
@@ -45,17 +45,12 @@ typedef struct CUstream_st* ck_stream_t; /* cudaStream_t */
 const char* ck_last_error(void);
 int ck_abi_version(void);
 int ck_check_device(void); /* 0 when the current device is sm_100 */
-/* Library options (process-wide).  "nvfp4_exact_div" = 1: the NVFP4 quantizer uses plain IEEE
- * divisions instead of the shared-reciprocal sequence; the bytes are the same either way (the
- * tests check that on the device), only the speed differs.  "norm_warps" = n > 0 forces the warps
- * per CTA of the norm kernels (0: the launcher chooses), "norm_cache" = 0 keeps them from caching
- * the modulation rows in shared memory (-1: the launcher chooses) and "norm_group" = 1, 2 or 4 sets
- * how many warps share a row (0: the launcher chooses; more than one changes the summation order of
- * the row statistics, so a result may move by one rounding step of the output type, while the fused
- * outputs stay equal to norm kernel -> quantizer).  "rope_threads_per_sm" = n > 0 sets how many threads
- * per SM the RoPE launcher aims for when it splits the walk over the broadcast dimension (0: default).
- * "gelu_table_min" = n: the gather quantizer tabulates GELU per CTA from n activated elements on
- * (default 16 Mi; negative: never; the bytes are the same either way).  All five are for tuning runs. */
+/* Library options (process-wide).  The one option that belongs to the interface:
+ * "nvfp4_exact_div" = 1 makes the NVFP4 quantizer use plain IEEE divisions instead of the
+ * shared-reciprocal sequence; the bytes are the same either way (the tests check that on the
+ * device), only the speed differs.  The launchers' tuning knobs are listed in the library's
+ * internal header csrc/ck_options.h; none of them changes a result's bytes beyond what that
+ * header states.  Unknown names return CK_ERR_UNSUPPORTED. */
 int ck_set_option(const char* name, int value);
 
 /* ---- per-tensor FP8 ----
@@ -77,7 +72,16 @@ int launch_dequantize_fp8_kernel(const void* input, void* output, const void* sc
 /* ---- NVFP4 ----
  * Replaces launch_quantize_nvfp4_kernel / launch_dequantize_nvfp4_kernel
  * (dlpack_bindings.cpp:102-124, ops/quantize_nvfp4.cu:323-435).
- * input [orig_rows, orig_cols];
+ * input [orig_rows, orig_cols]; output bytes [num_rows, num_cols/2]; block_scales
+ * tiled [roundup(num_rows,128), roundup(num_cols/16,4)]; num_* >= orig_* (the
+ * excess reads as zero; pad_16x of the Python API).  epsilon is accepted and
+ * ignored, as in the reference.  Arithmetic: backends/eager/quantization.py:117-221. */
+int launch_quantize_nvfp4_kernel(const void* input, const void* global_scale, void* output, void* block_scales,
+                                 int64_t num_rows, int64_t num_cols, int64_t orig_rows, int64_t orig_cols,
+                                 float epsilon, int input_dtype_code, bool hi_first, ck_stream_t stream);
+int launch_dequantize_nvfp4_kernel(const void* input, const void* global_scale, const void* block_scales,
+                                   void* output, int64_t num_rows, int64_t num_cols, int output_dtype_code,
+                                   bool hi_first, ck_stream_t stream);
 
 /* NVFP4 quantize of the column concatenation [seg0 | seg1] (seg1 optional: cols1 = 0).  Element (row, c) of a
  * segment is read at  base + (c / group) * group_stride + row * row_stride + c % group  (elements of the input
@@ -91,16 +95,7 @@ int launch_quantize_nvfp4_gather_kernel(const void* base0, int64_t cols0, int64_
                                         int64_t row_stride0, int act0, const void* base1, int64_t cols1,
                                         int64_t group1, int64_t group_stride1, int64_t row_stride1, int act1,
                                         const void* global_scale, void* output, void* block_scales,
-                                        int64_t num_rows, int input_dtype_code, bool hi_first, ck_stream_t stream); output bytes [num_rows, num_cols/2]; block_scales
- * tiled [roundup(num_rows,128), roundup(num_cols/16,4)]; num_* >= orig_* (the
- * excess reads as zero; pad_16x of the Python API).  epsilon is accepted and
- * ignored, as in the reference.  Arithmetic: backends/eager/quantization.py:117-221. */
-int launch_quantize_nvfp4_kernel(const void* input, const void* global_scale, void* output, void* block_scales,
-                                 int64_t num_rows, int64_t num_cols, int64_t orig_rows, int64_t orig_cols,
-                                 float epsilon, int input_dtype_code, bool hi_first, ck_stream_t stream);
-int launch_dequantize_nvfp4_kernel(const void* input, const void* global_scale, const void* block_scales,
-                                   void* output, int64_t num_rows, int64_t num_cols, int output_dtype_code,
-                                   bool hi_first, ck_stream_t stream);
+                                        int64_t num_rows, int input_dtype_code, bool hi_first, ck_stream_t stream);
 
 /* ---- MXFP8 ----
  * launch_quantize_mxfp8_kernel replaces the reference's entry point of that name
@@ -134,25 +129,15 @@ int launch_scaled_mm_nvfp4_kernel(const void* A, const void* A_scale, const void
 int launch_scaled_mm_mxfp8_kernel(const void* A, const void* A_scale, const void* B, const void* B_scale, void* D,
                                   const void* bias, int bias_dtype_code, int64_t M, int64_t N, int64_t K,
                                   int out_dtype_code, ck_stream_t stream);
-/* Synchronises the device, returns and clears the GEMM kernels' status word
- * (non-zero when a bounded device-side wait ran out). */
+/* Synchronises the device, reads and clears the GEMM kernels' status word.  Returns 0, or
+ * CK_ERR_DEVICE_TIMEOUT when a bounded device-side wait ran out since the last call
+ * (ck_last_error() names the wait and the CTA), or a positive cudaError_t. */
 int ck_gemm_device_status(void);
 
 /* ---- RoPE ----
  * Replaces launch_apply_rope_kernel (dlpack_bindings.cpp:75-101,
  * ops/apply_rope.cu:358-404).  x is [batch, dim1, dim2, head_dim] with the given
- * element strides (used for input and output alike);
-
-/* Per-head RMSNorm of q and k + RoPE of both + relayout of q, k, v for attention, one pass.
- * No single counterpart in the reference: it composes apply_rope (backends/eager/rope.py:9-32)
- * with torch's rms_norm and the caller's permutes.  qkv: [tokens, >= 3*heads*128] with row_stride
- * elements between tokens, columns [q heads | k heads | v heads]; q_weight, k_weight: [128] in
- * qkv's dtype (bf16 or fp16); freqs: fp32 [total_tokens, 64, 2, 2]; q_out, k_out, v_out:
- * [heads, total_tokens, 128]; rows token_offset .. token_offset+tokens-1 of every head are written. */
-int launch_qk_norm_rope_kernel(const void* qkv, int64_t row_stride, const void* q_weight, const void* k_weight,
-                               const float* freqs, void* q_out, void* k_out, void* v_out, int64_t tokens,
-                               int64_t heads, int64_t token_offset, int64_t total_tokens, float eps,
-                               int dtype_code, ck_stream_t stream); freqs is
+ * element strides (used for input and output alike); freqs is
  * [freqs_batch, freqs_dim1, freqs_dim2, head_dim/2, 2, 2], each leading dim 1
  * (broadcast) or >= x's.  xk / xk_out may both be NULL.
  * Arithmetic: backends/eager/rope.py:9-32. */
@@ -163,6 +148,17 @@ int launch_apply_rope_kernel(const void* xq, const void* xk, const void* freqs, 
                              int64_t stride_freqs_dim1, int64_t stride_freqs_dim2, int64_t stride_freqs_dim,
                              int64_t stride_freqs_rot, int64_t stride_freqs_pair, int input_dtype_code,
                              int freqs_dtype_code, bool split_half, ck_stream_t stream);
+
+/* Per-head RMSNorm of q and k + RoPE of both + relayout of q, k, v for attention, one pass.
+ * No single counterpart in the reference: it composes apply_rope (backends/eager/rope.py:9-32)
+ * with torch's rms_norm and the caller's permutes.  qkv: [tokens, >= 3*heads*128] with row_stride
+ * elements between tokens, columns [q heads | k heads | v heads]; q_weight, k_weight: [128] in
+ * qkv's dtype (bf16 or fp16); freqs: fp32 [total_tokens, 64, 2, 2]; q_out, k_out, v_out:
+ * [heads, total_tokens, 128]; rows token_offset .. token_offset+tokens-1 of every head are written. */
+int launch_qk_norm_rope_kernel(const void* qkv, int64_t row_stride, const void* q_weight, const void* k_weight,
+                               const float* freqs, void* q_out, void* k_out, void* v_out, int64_t tokens,
+                               int64_t heads, int64_t token_offset, int64_t total_tokens, float eps,
+                               int dtype_code, ck_stream_t stream);
 
 /* ---- AdaLN / RMSNorm ----
  * launch_adaln_kernel replaces the reference's entry point of that name
@@ -186,8 +182,9 @@ int launch_adaln_quantize_mxfp8_kernel(const void* x, const void* scale, const v
                                        void* block_scales, int64_t N, int64_t D, int64_t scale_group,
                                        int64_t shift_group, float eps, int dtype_code, int norm_kind,
                                        ck_stream_t stream);
-/* Synchronises the device, returns and clears the norm kernels' status word
- * (non-zero when a bounded device-side wait on a row copy ran out). */
+/* Synchronises the device, reads and clears the norm kernels' status word.  Returns 0, or
+ * CK_ERR_DEVICE_TIMEOUT when a bounded device-side wait on a row copy ran out since the last
+ * call (the rows concerned were not written), or a positive cudaError_t. */
 int ck_norm_device_status(void);
 
 #ifdef __cplusplus

@@ -33,6 +33,28 @@ def test_library_exports_every_declared_symbol():
     assert set(declared) <= bound, sorted(set(declared) - bound)
 
 
+def test_header_is_valid_c_and_cxx():
+    """The boundary header must compile by itself in both languages (every csrc/*.cu also includes it through
+    ck_common.cuh, so a definition that drifts from its declaration fails the build)."""
+    import os
+    import shutil
+    import subprocess
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    header = os.path.join(root, "include", "comfy_kitchen_b200.h")
+    for cmd in (["gcc", "-std=c11", "-Wall", "-Werror", "-fsyntax-only", "-x", "c", header],
+                ["g++", "-std=c++17", "-Wall", "-Werror", "-fsyntax-only", "-x", "c++", header]):
+        if shutil.which(cmd[0]) is None:
+            pytest.skip(f"{cmd[0]} not installed")
+        r = subprocess.run(cmd, capture_output=True, text=True)
+        assert r.returncode == 0, r.stderr
+    common = open(os.path.join(root, "comfy-kitchen_b200", "csrc", "ck_common.cuh")).read()
+    assert '#include "comfy_kitchen_b200.h"' in common
+    for name in os.listdir(os.path.join(root, "comfy-kitchen_b200", "csrc")):
+        if name.endswith(".cu"):
+            assert '#include "ck_common.cuh"' in open(os.path.join(root, "comfy-kitchen_b200", "csrc", name)).read(), name
+
+
 def test_argument_errors_come_back_as_status_and_message():
     lib = _native.load()
     assert lib.ck_abi_version() == 1

@@ -202,10 +202,60 @@ def test_full_size_properties(ck, orc):
     bound = torch.maximum(x.float().abs() * 2.0 ** -4, step * 2.0 ** -10)
     assert bool((err <= bound).all())
     del step, err, bound, d8
-    # FP8: dequantize(quantize(x)) requantizes to the same codes
+    # FP8: dequantize(quantize(x)) requantizes to the same codes.  The fp32 dequantized value is code * scale
+    # rounded once, and multiplying it by fp32(1 / scale) lands within 2^-22 of the code, far inside the
+    # E4M3 rounding interval, so the bytes must come back unchanged.
     s = (x.float().abs().max() / 448.0).float()
     q1 = ck.quantize_per_tensor_fp8(x, s)
-    assert q1.shape == x.shape
+    d1 = ck.dequantize_per_tensor_fp8(q1, s, torch.float32)
+    q1b = ck.quantize_per_tensor_fp8(d1, s)
+    assert torch.equal(q1b.view(torch.uint8), q1.view(torch.uint8))
+
+
+SWEEP_SHAPES = [(m, k) for m in (1024, 4608, 18432, 65536) for k in (3072, 12288)]
+
+
+@pytest.mark.parametrize("M,K", SWEEP_SHAPES)
+def test_sweep_shapes_vs_oracle_row_samples(ck, orc, M, K):
+    """Every shape of the quantizer sweep, all three formats: the device result on the whole tensor must equal the
+    CPU oracle's on a row sample (rows 0..255, the last 128 and 640 random ones).  Rows are independent for all
+    three quantizers -- only the per-tensor scale is global and it is passed in -- and block scales of sampled
+    rows are compared after un-tiling."""
+    g = torch.Generator(device="cuda").manual_seed(1)
+    x = torch.randn(M, K, device="cuda", generator=g, dtype=torch.float32)
+    x = torch.where(torch.rand(M, K, device="cuda", generator=g) < 0.001, 50.0 * torch.randn(M, K, device="cuda", generator=g), x)
+    x = x.bfloat16()
+    rows = torch.cat([torch.arange(0, 256), torch.arange(M - 128, M),
+                      torch.randint(0, M, (640,), generator=torch.Generator().manual_seed(M + K))]).unique()
+    rc = rows.cuda()
+    xs = x[rc].cpu()
+    amax = x.float().abs().max()
+    # NVFP4
+    gs = (amax / (6.0 * 448.0)).float()
+    q, sf = ck.quantize_nvfp4(x, gs)
+    q_ref, sf_ref = orc.quantize_nvfp4(xs, gs.cpu())
+    assert torch.equal(q[rc].cpu(), q_ref)
+    sf_plain = orc.from_blocked(sf.view(torch.uint8).cpu(), M, K // 16)
+    assert torch.equal(sf_plain[rows], orc.from_blocked(sf_ref.view(torch.uint8), len(rows), K // 16))
+    d = ck.dequantize_nvfp4(q, gs, sf, torch.bfloat16)
+    assert _same_bits(d[rc], orc.dequantize_nvfp4(q_ref, gs.cpu(), sf_ref, torch.bfloat16))
+    del q, sf, d
+    # MXFP8
+    q8, sf8 = ck.quantize_mxfp8(x)
+    q8_ref, sf8_ref = orc.quantize_mxfp8(xs)
+    assert torch.equal(q8[rc].view(torch.uint8).cpu(), q8_ref.view(torch.uint8))
+    sf8_plain = orc.from_blocked(sf8.view(torch.uint8).cpu(), M, K // 32)
+    assert torch.equal(sf8_plain[rows], orc.from_blocked(sf8_ref.view(torch.uint8), len(rows), K // 32))
+    d8 = ck.dequantize_mxfp8(q8, sf8, torch.bfloat16)
+    assert _same_bits(d8[rc], orc.dequantize_mxfp8(q8_ref, sf8_ref, torch.bfloat16))
+    del q8, sf8, d8
+    # FP8 per tensor
+    s = (amax / 448.0).float()
+    qf = ck.quantize_per_tensor_fp8(x, s)
+    qf_ref = orc.quantize_per_tensor_fp8(xs, s.cpu())
+    assert torch.equal(qf[rc].view(torch.uint8).cpu(), qf_ref.view(torch.uint8))
+    df = ck.dequantize_per_tensor_fp8(qf, s, torch.bfloat16)
+    assert _same_bits(df[rc], orc.dequantize_per_tensor_fp8(qf_ref, s.cpu(), torch.bfloat16))
 
 
 def test_nvfp4_reciprocal_division_is_exact(ck):

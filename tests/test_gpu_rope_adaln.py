@@ -246,6 +246,35 @@ def test_norm_status_word_is_clear(ck):
     assert ck.norm_device_status() == 0
 
 
+@pytest.mark.parametrize("group", [0, 2])
+def test_norm_bounded_wait_runs_out_and_recovers(ck, group):
+    """The time-out path of the norm kernel's row waits, exercised without any fault: with the library's
+    poll limit set to "no poll" every consumer gives its first row up at once, records the status word and
+    leaves (after waiting, with the normal limit, for the copies it had in flight).  The call returns, the
+    status call reports CK_ERR_DEVICE_TIMEOUT once and clears, and the next normal call is correct."""
+    g = torch.Generator().manual_seed(21)
+    x = torch.randn(1, 200, 3072, generator=g).bfloat16().cuda()
+    sc = (0.1 * torch.randn(1, 1, 3072, generator=g)).bfloat16().cuda()
+    sh = (0.1 * torch.randn(1, 1, 3072, generator=g)).bfloat16().cuda()
+    want = ck.adaln(x, sc, sh, 1e-6)
+    assert ck.norm_device_status() == 0
+    ck.set_option("norm_poll_limit", -1)
+    ck.set_option("norm_group", group)
+    try:
+        ck.adaln(x, sc, sh, 1e-6)
+        status = ck.norm_device_status()      # synchronises: the kernel has returned
+    finally:
+        ck.set_option("norm_poll_limit", 0)
+        ck.set_option("norm_group", 0)
+    assert status == -6                        # CK_ERR_DEVICE_TIMEOUT
+    from comfy_kitchen import _native
+    assert b"bounded wait" in _native.load().ck_last_error()
+    assert ck.norm_device_status() == 0       # cleared by the read
+    again = ck.adaln(x, sc, sh, 1e-6)
+    assert torch.equal(again, want)
+    assert ck.norm_device_status() == 0
+
+
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 def test_qk_norm_rope_matches_composition(ck, dtype):
     """Fused per-head RMSNorm + RoPE + relayout against rms_norm (fp32) -> oracle rope -> permute; two calls fill a
