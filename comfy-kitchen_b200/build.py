@@ -21,7 +21,7 @@ OBJ = os.path.join(HERE, "build")
 LIB_DIR = os.path.join(HERE, "lib")
 LIB = os.path.join(LIB_DIR, "libcomfy_kitchen_b200.so")
 
-SOURCES = ["abi.cu", "quant_fp8.cu", "quant_nvfp4.cu", "quant_mxfp8.cu", "rope.cu", "qk_norm_rope.cu", "adaln.cu", "gemm_blockscaled.cu"]
+SOURCES = ["abi.cu", "quant_fp8.cu", "quant_nvfp4.cu", "quant_mxfp8.cu", "rope.cu", "qk_norm_rope.cu", "adaln.cu", "gemm_blockscaled.cu", "tp_exchange.cu"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",

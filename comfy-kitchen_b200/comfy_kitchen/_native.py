@@ -24,6 +24,8 @@ SIGNATURES: dict[str, list] = {
     "ck_gemm_device_status": [],
     "ck_norm_device_status": [],
     "ck_set_option": [c_char_p, I],
+    "ck_tp_device_status": [],
+    "launch_tp_exchange_kernel": [P, P, P, I, I, P, P, I64, I64, I64, I, I, P],
     "launch_quantize_fp8_kernel": [P, P, P, I64, I, I, P],
     "launch_dequantize_fp8_kernel": [P, P, P, I64, I, I, P],
     "launch_quantize_nvfp4_kernel": [P, P, P, P, I64, I64, I64, I64, F, I, B, P],
@@ -42,7 +44,7 @@ SIGNATURES: dict[str, list] = {
     "launch_adaln_quantize_nvfp4_kernel": [P, P, P, P, P, P, I64, I64, I64, I64, F, I, B, I, P],
     "launch_adaln_quantize_mxfp8_kernel": [P, P, P, P, P, I64, I64, I64, I64, F, I, I, P],
 }
-_RESTYPES = {"ck_last_error": c_char_p}
+_RESTYPES = {"ck_last_error": c_char_p, "ck_tp_pad_bytes": c_int64}
 
 _lib = None
 
@@ -66,6 +68,8 @@ def load() -> ctypes.CDLL:
         fn = getattr(lib, name)  # AttributeError here means header and library disagree
         fn.argtypes = argtypes
         fn.restype = c_int
+    lib.ck_tp_pad_bytes.argtypes = []
+    lib.ck_tp_pad_bytes.restype = c_int64
     lib.ck_last_error.argtypes = []
     lib.ck_last_error.restype = c_char_p
     _lib = lib

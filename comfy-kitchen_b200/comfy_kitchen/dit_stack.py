@@ -169,6 +169,8 @@ class DiTStack:
         self.tp = tp or TensorParallel()
         cfg.validate(self.tp.world)
         self.sites = _Sites()
+        self.exchange = None   # PeerExchange once enable_peer_exchange() has run (CUDA only)
+        self._xbuf = None      # the residual stream [tokens, hidden], text tokens first; updated in place
         self._mods = None   # all blocks' modulation vectors during a forward
         self.heads_local = cfg.heads // self.tp.world
         self.freqs = rope_freqs(cfg, self.device)
@@ -354,68 +356,111 @@ class DiTStack:
             off += qkv.shape[0]
         return F.scaled_dot_product_attention(q, k, v)[0]   # [heads_local, tokens, head_dim]; the quantizer reads it in place
 
-    def _row_parallel(self, linears, inputs, sites) -> torch.Tensor:
-        """Row-parallel GEMMs of consecutive token ranges written into one buffer, then one all-reduce.
+    def enable_peer_exchange(self, mode: str | None = None) -> None:
+        """Replace "NCCL all-reduce, then residual update" by the fused exchange kernel over peer memory
+        (comfy_kitchen/tp_exchange.py).  Every rank must call this at the same point.  The residual stream then
+        lives in the exchange's shared buffer."""
+        from comfy_kitchen.tp_exchange import PeerExchange
+
+        assert self.device.type == "cuda"
+        self.exchange = PeerExchange(self.tp.group, self.device, self.cfg.tokens, self.cfg.hidden, torch.bfloat16, mode)
+        self._xbuf = self.exchange.residual
+
+    def try_enable_peer_exchange(self, mode: str | None = None) -> str | None:
+        """enable_peer_exchange() with agreement between the ranks: the exchange is kept only if every rank
+        could set it up; otherwise every rank stays on the NCCL path.  Returns None on success, else why not."""
+        err = None
+        try:
+            self.enable_peer_exchange(mode)
+        except Exception as e:  # noqa: BLE001 - any failure means "use the NCCL path"
+            err = f"{type(e).__name__}: {e}"
+        if self.tp.world > 1:
+            ok = torch.tensor([0.0 if err else 1.0], device=self.device)
+            self.tp._dist.all_reduce(ok, op=self.tp._dist.ReduceOp.MIN, group=self.tp.group)
+            if float(ok.item()) < 1.0 and err is None:
+                err = "another rank could not set the exchange up"
+        if err:
+            self.exchange, self._xbuf = None, None
+        return err
+
+    def _residual(self, rows: int) -> torch.Tensor:
+        if self._xbuf is None or self._xbuf.shape[0] != rows:
+            assert self.exchange is None, "the exchange buffers are sized for the configured token count"
+            self._xbuf = torch.empty((rows, self.cfg.hidden), device=self.device, dtype=torch.bfloat16)
+        return self._xbuf
+
+    def _row_parallel_update(self, linears, inputs, sites, gates) -> None:
+        """Row-parallel GEMMs of consecutive token ranges of the residual stream, the sum of their partial
+        results over the ranks, and  x += gate * y  on the residual stream (one gate per range).
         inputs: per range the list of (tensor, activation) segments that make up the GEMM's input columns."""
         rows = [segs[0][0].shape[-2] for segs in inputs]
-        y = torch.empty((sum(rows), self.cfg.hidden), device=inputs[0][0][0].device, dtype=torch.bfloat16)
+        x = self._xbuf
+        assert sum(rows) == x.shape[0]
+        fused = self.exchange is not None
+        y = self.exchange.partial if fused else torch.empty_like(x)
         off = 0
         for lin, segs, site, r in zip(linears, inputs, sites, rows):
             qx, sx, g = self._quant(site, segs)
             lin(qx, sx, g, out=y[off:off + r])
             off += r
-        return self.tp.all_reduce_sum(y)
+        if fused:
+            self.tp.all_reduce_calls += 1
+            self.exchange.exchange(gates[0], gates[1] if len(gates) > 1 else None, rows[0] if len(gates) > 1 else 0)
+            return
+        y = self.tp.all_reduce_sum(y)
+        off = 0
+        for gate, r in zip(gates, rows):
+            x[off:off + r].addcmul_(gate, y[off:off + r])
+            off += r
 
-    def _double_block(self, i: int, img: torch.Tensor, txt: torch.Tensor, vec: torch.Tensor):
-        blk, tt = self.double[i], self.cfg.txt_tokens
-        order = ("txt", "img")   # token order of the joint sequence
+    def _double_block(self, i: int, vec: torch.Tensor) -> None:
+        blk, tt = self.double[i], self._tt
+        order = ("txt", "img")   # token order of the residual stream
         mods = {s: self._modulation(blk[s], vec, 6) for s in order}
-        xs = {"img": img, "txt": txt}
+        xs = {"txt": self._xbuf[:tt], "img": self._xbuf[tt:]}
         parts = []
         for s in order:
             shift1, scale1 = mods[s][0], mods[s][1]
             qx, sx, g = self._norm_quant(f"d{i}.{s}.attn_in", xs[s], scale1, shift1)
             parts.append((blk[s]["qkv"](qx, sx, g), blk[s]["q_norm"], blk[s]["k_norm"]))
         o = self._attend(parts)
-        y = self._row_parallel([blk[s]["proj"] for s in order], [[(o[:, :tt], None)], [(o[:, tt:], None)]],
-                               [f"d{i}.{s}.attn_out" for s in order])
-        for s, ysl in (("txt", y[:tt]), ("img", y[tt:])):
-            xs[s] = torch.addcmul(xs[s], mods[s][2], ysl)
+        self._row_parallel_update([blk[s]["proj"] for s in order], [[(o[:, :tt], None)], [(o[:, tt:], None)]],
+                                  [f"d{i}.{s}.attn_out" for s in order], [mods[s][2] for s in order])
         mids = []
         for s in order:
             shift2, scale2 = mods[s][3], mods[s][4]
             qx, sx, g = self._norm_quant(f"d{i}.{s}.mlp_in", xs[s], scale2, shift2)
             mids.append([(blk[s]["up"](qx, sx, g), "gelu_tanh")])   # GELU happens inside the quantizer
-        y = self._row_parallel([blk[s]["down"] for s in order], mids, [f"d{i}.{s}.mlp_mid" for s in order])
-        for s, ysl in (("txt", y[:tt]), ("img", y[tt:])):
-            xs[s] = torch.addcmul(xs[s], mods[s][5], ysl)
-        return xs["img"], xs["txt"]
+        self._row_parallel_update([blk[s]["down"] for s in order], mids, [f"d{i}.{s}.mlp_mid" for s in order],
+                                  [mods[s][5] for s in order])
 
-    def _single_block(self, i: int, x: torch.Tensor, vec: torch.Tensor) -> torch.Tensor:
+    def _single_block(self, i: int, vec: torch.Tensor) -> None:
         p, c, hl = self.single[i], self.cfg, self.heads_local
         shift, scale, gate = self._modulation(p, vec, 3)
-        qx, sx, g = self._norm_quant(f"s{i}.in", x, scale, shift)
+        qx, sx, g = self._norm_quant(f"s{i}.in", self._xbuf, scale, shift)
         h1 = p["linear1"](qx, sx, g)   # [tokens, q | k | v | mlp]: the fused kernel reads the first part in place
         n_qkv = 3 * hl * c.head_dim
         o = self._attend([(h1, p["q_norm"], p["k_norm"])])
         # linear2's input columns: [attention output | GELU(mlp part of h1)], both read where they are
-        y = self._row_parallel([p["linear2"]], [[(o, None), (h1[:, n_qkv:], "gelu_tanh")]], [f"s{i}.mid"])
-        return torch.addcmul(x, gate, y)
+        self._row_parallel_update([p["linear2"]], [[(o, None), (h1[:, n_qkv:], "gelu_tanh")]], [f"s{i}.mid"], [gate])
 
     @torch.no_grad()
     def forward(self, img: torch.Tensor, txt: torch.Tensor, vec: torch.Tensor) -> torch.Tensor:
         """img [img_tokens, hidden], txt [txt_tokens, hidden], vec [1, hidden] (bf16) -> [tokens, hidden],
         text tokens first.  Every rank receives the same inputs and returns the same (replicated) output."""
         self._mods = F.linear(F.silu(vec), self.mod_w, self.mod_b) if self.mod_w is not None else None
+        tt = self._tt = txt.shape[0]
+        x = self._residual(tt + img.shape[0])
+        x[:tt].copy_(txt)
+        x[tt:].copy_(img)
         try:
             for i in range(self.cfg.n_double):
-                img, txt = self._double_block(i, img, txt, vec)
-            x = torch.cat([txt, img])
+                self._double_block(i, vec)
             for i in range(self.cfg.n_single):
-                x = self._single_block(i, x, vec)
+                self._single_block(i, vec)
         finally:
             self._mods = None
-        return x
+        return x.clone()   # the residual buffer is reused by the next forward
 
     __call__ = forward
 
@@ -425,11 +470,13 @@ class DiTStack:
         The forward is ~40 small launches per block; replaying a graph removes their host cost.  Needs static
         activation scales (call calibrate() first) so that no value-dependent host work is left in the forward.
         Inputs are copied into the graph's own buffers; the returned tensor is the graph's output buffer
-        (overwritten by the next replay).  Single rank only: capturing the NCCL all-reduces of a tensor-parallel
-        forward did not complete on the test machines (NCCL 2.28, two ranks, with the default and with the
-        thread-local capture error mode alike), so tensor-parallel runs launch eagerly.
+        (overwritten by the next replay).  On several ranks this needs the peer exchange
+        (enable_peer_exchange()): its kernels are ordinary launches and are recorded like any other, whereas a
+        forward that ends its row-parallel GEMMs with NCCL calls is recorded in segments (capture_segments()).
+        Every rank must capture, and later replay, in step.
         """
-        assert self.tp.world == 1, "graph capture is for a single rank; tensor-parallel forwards launch eagerly"
+        assert self.tp.world == 1 or self.exchange is not None, \
+            "several ranks: enable_peer_exchange() first, or use capture_segments()"
         assert self.device.type == "cuda", "graph capture needs a CUDA device"
         assert self.sites.static, "calibrate() first: capture needs static activation scales"
         bufs = [img.clone(), txt.clone(), vec.clone()]
@@ -441,8 +488,14 @@ class DiTStack:
         torch.cuda.current_stream(self.device).wait_stream(side)
         torch.cuda.synchronize(self.device)
         graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph, stream=side):
+        with torch.cuda.graph(graph, stream=side, capture_error_mode="thread_local"):
             out = self.forward(*bufs)
+
+        torch.cuda.current_stream(self.device).wait_stream(side)
+        if self.tp.world > 1:
+            # no rank replays (and waits in an exchange kernel) while another is still recording
+            torch.cuda.synchronize(self.device)
+            self.tp._dist.barrier(group=self.tp.group)
 
         def replay(img_, txt_, vec_):
             bufs[0].copy_(img_, non_blocking=True)
@@ -453,6 +506,60 @@ class DiTStack:
 
         replay.graph = graph
         return replay
+
+    def capture_best(self, img: torch.Tensor, txt: torch.Tensor, vec: torch.Tensor):
+        """(replay, description): one graph per forward where that is possible (one rank, or the peer exchange
+        is on), else the chain of graphs between NCCL all-reduces."""
+        if self.tp.world == 1:
+            return self.capture(img, txt, vec), "one CUDA graph per forward"
+        if self.exchange is not None:
+            return self.capture(img, txt, vec), "one CUDA graph per forward, fused all-reduce + residual kernels (peer memory) inside"
+        return self.capture_segments(img, txt, vec), "CUDA graphs between NCCL all-reduces"
+
+    @torch.no_grad()
+    def exchange_report(self, img: torch.Tensor, txt: torch.Tensor, vec: torch.Tensor, iters: int = 20) -> dict:
+        """Stand-alone timings (device events, every rank in step) of the two parts of a forward that do not
+        shrink with the rank count: the exchange after every row-parallel GEMM, and the norm -> quantize front
+        end that every rank runs on the whole sequence.  Multiplied out to one forward."""
+        n = self.expected_all_reduces()
+        x = self._residual(self.cfg.tokens)
+        gate = torch.zeros(self.cfg.hidden, device=self.device, dtype=torch.bfloat16)
+
+        def timed(fn):
+            for _ in range(3):
+                fn()
+            torch.cuda.synchronize(self.device)
+            if self.tp.world > 1:
+                self.tp._dist.barrier(group=self.tp.group)
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            for _ in range(iters):
+                fn()
+            b.record()
+            torch.cuda.synchronize(self.device)
+            t = torch.tensor([a.elapsed_time(b) / iters], device=self.device, dtype=torch.float64)
+            if self.tp.world > 1:
+                self.tp._dist.all_reduce(t, op=self.tp._dist.ReduceOp.MAX, group=self.tp.group)
+            return float(t.item())
+
+        if self.exchange is not None:
+            per = timed(lambda: self.exchange.exchange(gate))
+            what = "fused all-reduce + residual kernel over peer memory (" + self.exchange.mode + ")"
+        else:
+            y = torch.zeros_like(x)
+
+            def nccl():
+                self.tp.all_reduce_sum(y)
+                x.addcmul_(gate, y)
+            per = timed(nccl)
+            what = "NCCL all-reduce + addcmul"
+        scale = torch.zeros(1, 1, self.cfg.hidden, device=self.device, dtype=torch.bfloat16)
+        g = torch.ones((), device=self.device)
+        per_norm = timed(lambda: self.ops.adaln_quantize_nvfp4(x[None], scale, scale, g, self.cfg.eps))
+        return {"all_reduce_ms": round(per * n, 3), "all_reduce_us_each": round(per * 1e3, 1), "all_reduce_how": what,
+                "all_reduce_bytes_each": int(x.numel() * 2),
+                "elementwise_ms": round(per_norm * n, 3),
+                "elementwise_what": f"norm -> NVFP4 of the whole sequence, {n} per forward, done in full on every rank"}
 
     def capture_segments(self, img: torch.Tensor, txt: torch.Tensor, vec: torch.Tensor):
         """Tensor-parallel variant of capture(): the forward is recorded as a chain of CUDA graphs that ends at

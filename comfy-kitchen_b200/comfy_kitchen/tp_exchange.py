@@ -1,0 +1,132 @@
+"""Host side of the tensor-parallel exchange kernel (csrc/tp_exchange.cu).
+
+The reference has no multi-GPU code; a tensor-parallel port of it would end every row-parallel GEMM with
+an NCCL all-reduce and an elementwise residual update.  ``PeerExchange`` replaces that pair by one kernel
+that reads the ranks' partial results straight from their memory over NVLink and pushes the updated
+residual into every rank's buffer:
+
+    ex = PeerExchange(group, device, rows, cols, torch.bfloat16)
+    gemm(..., out=ex.partial[a:b])          # this rank's partial sums
+    ex.exchange(gate0, gate1, split_row)     # ex.residual += gate * sum_over_ranks(partial), on every rank
+
+Buffers: each rank allocates one block holding [partial | residual | flag pad] and maps the other ranks'
+blocks into its address space, through torch's symmetric memory when that is available and otherwise
+through CUDA IPC handles of an ordinary allocation (exchanged over the process group).  Nothing here is
+NCCL; the process group is used for the one-time handle exchange and for host-side barriers only.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+
+import torch
+
+from comfy_kitchen import _native
+
+
+def _align(n: int, a: int = 256) -> int:
+    return (n + a - 1) // a * a
+
+
+class PeerExchange:
+    """One rank's view of the shared buffers of a tensor-parallel group, and the launch of the fused
+    all-reduce + residual kernel.  World size 1 works too (the kernel then only applies the residual update),
+    which is what the single-GPU tests exercise."""
+
+    def __init__(self, group, device, rows: int, cols: int, dtype: torch.dtype = torch.bfloat16, mode: str | None = None):
+        import torch.distributed as dist
+
+        assert dtype in (torch.bfloat16, torch.float16) and cols % 8 == 0
+        self.device = torch.device(device)
+        self.rows, self.cols, self.dtype = rows, cols, dtype
+        self._dist, self.group = dist, group
+        live = dist.is_available() and dist.is_initialized()
+        self.world = dist.get_world_size(group) if live else 1
+        self.rank = dist.get_rank(group) if live else 0
+        lib = _native.load()
+        mat = _align(rows * cols * 2)
+        self._pad_bytes = _align(int(lib.ck_tp_pad_bytes()))
+        self._offsets = (0, mat, 2 * mat)
+        total = 2 * mat + self._pad_bytes
+        mode = mode or os.environ.get("CK_TP_PEER_MEMORY", "auto")
+        self._keep = []          # objects that own the mappings
+        bases = None
+        errors = []
+        if self.world == 1:
+            self._block = torch.zeros(total, dtype=torch.uint8, device=self.device)
+            bases, self.mode = [self._block.data_ptr()], "local"
+        else:
+            for m in (("symm", "ipc") if mode == "auto" else (mode,)):
+                try:
+                    bases = self._map_symmetric(total) if m == "symm" else self._map_ipc(total)
+                    self.mode = m
+                    break
+                except Exception as e:  # fall through to the next way of sharing memory
+                    errors.append(f"{m}: {type(e).__name__}: {e}")
+            if bases is None:
+                raise RuntimeError("no way to share device memory between the ranks: " + "; ".join(errors))
+        self._block.zero_()
+        torch.cuda.synchronize(self.device)
+        if self.world > 1:
+            dist.barrier(group=group)   # every pad is zero before anyone's first launch
+        n = rows * cols
+        self.partial = self._block[:n * 2].view(dtype).view(rows, cols)
+        self.residual = self._block[mat:mat + n * 2].view(dtype).view(rows, cols)
+        arr = ctypes.c_void_p * self.world
+        self._partials = arr(*[b + self._offsets[0] for b in bases])
+        self._residuals = arr(*[b + self._offsets[1] for b in bases])
+        self._pads = arr(*[b + self._offsets[2] for b in bases])
+        self.calls = 0
+
+    # ---- ways of making one allocation per rank visible to all ranks
+
+    def _map_symmetric(self, total: int):
+        import torch.distributed._symmetric_memory as symm_mem
+
+        self._block = symm_mem.empty(total, dtype=torch.uint8, device=self.device)
+        group = self.group if self.group is not None else self._dist.group.WORLD
+        handle = symm_mem.rendezvous(self._block, group)
+        self._keep.append(handle)
+        ptrs = [int(p) for p in handle.buffer_ptrs]
+        assert len(ptrs) == self.world and ptrs[self.rank] == self._block.data_ptr()
+        return ptrs
+
+    def _map_ipc(self, total: int):
+        # an allocation of its own (large enough that the caching allocator gives it a private segment)
+        self._block = torch.empty(max(total, 32 << 20), dtype=torch.uint8, device=self.device)
+        storage = self._block.untyped_storage()
+        meta = storage._share_cuda_()
+        gathered = [None] * self.world
+        self._dist.all_gather_object(gathered, (self.rank, meta), group=self.group)
+        ptrs = []
+        for r, m in sorted(gathered, key=lambda t: t[0]):
+            if r == self.rank:
+                ptrs.append(self._block.data_ptr())
+                continue
+            peer = torch.UntypedStorage._new_shared_cuda(*m)
+            self._keep.append(peer)
+            ptrs.append(peer.data_ptr())
+        return ptrs
+
+    # ---- the exchange
+
+    def exchange(self, gate0: torch.Tensor, gate1: torch.Tensor | None = None, split_row: int = 0, blocks: int = 0) -> torch.Tensor:
+        """residual <- residual + gate * sum_over_ranks(partial), on every rank (rows below split_row use gate0,
+        the rest gate1).  Every rank of the group must make the same sequence of calls."""
+        g0 = gate0.reshape(-1)
+        assert g0.numel() == self.cols and g0.dtype == self.dtype and g0.is_contiguous()
+        g1 = None
+        if gate1 is not None:
+            g1 = gate1.reshape(-1)
+            assert g1.numel() == self.cols and g1.dtype == self.dtype and g1.is_contiguous()
+        code = 2 if self.dtype == torch.bfloat16 else 1
+        _native.call("launch_tp_exchange_kernel", self._partials, self._residuals, self._pads, self.world, self.rank,
+                     ctypes.c_void_p(g0.data_ptr()), ctypes.c_void_p(0 if g1 is None else g1.data_ptr()),
+                     int(split_row), self.rows, self.cols, code, int(blocks),
+                     ctypes.c_void_p(torch.cuda.current_stream(self.device).cuda_stream))
+        self.calls += 1
+        return self.residual
+
+    def status(self) -> int:
+        """Synchronise and read (then clear) the kernel's status word: 0, or -6 after a wait for a peer ran out."""
+        return int(_native.load().ck_tp_device_status())

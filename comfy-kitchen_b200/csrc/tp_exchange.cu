@@ -1,0 +1,249 @@
+// Exchange step of the tensor-parallel stack: sum of the row-parallel GEMMs' partial results over the
+// ranks, fused with the residual update that follows it, over NVLink peer memory.
+//
+//   x[r, c] <- bf16( x[r, c] + gate[c] * bf16( sum_i partial_i[r, c] ) )        on every rank
+//
+// i.e. all_reduce(sum) of the [rows, cols] partial outputs followed by addcmul(x, gate, y), in one
+// kernel and without a collective library.  The reference has no multi-GPU code; this stands where a
+// tensor-parallel port of it would call ncclAllReduce and an elementwise kernel.
+//
+// Every rank runs the same launch (same grid).  Rank r owns the r-th contiguous slice of the matrix:
+//   1. start barrier  - block b tells block b of every peer "my partial is complete" (it is: the GEMM
+//                       that wrote it precedes this kernel on the stream) and waits for theirs;
+//   2. reduce         - 16-byte loads of the slice from all ranks' partial buffers (plain peer loads,
+//                       no multicast), fp32 sum in rank order, one rounding to the 16-bit type, the
+//                       residual update in fp32, one more rounding;
+//   3. push           - the updated slice is stored into the residual buffer of every rank;
+//   4. end barrier    - block b waits until block b of every peer has finished pushing, so that when
+//                       the kernel completes on a rank its whole residual buffer is up to date.
+// Since one rank computes each element, all ranks end with bit-identical residuals.
+//
+// Barrier flags live in a per-rank pad that the peers can write: start[block][source rank] and
+// end[block][source rank] hold the epoch of the last call that signalled; the epoch itself is kept in the
+// rank's own memory and advanced by the kernel, so a CUDA graph can replay the launch.  Every wait is
+// bounded by wall-clock time (%globaltimer); on expiry the block records a status word and carries on
+// without waiting (the result is then wrong, and ck_tp_device_status() says so).
+#include "ck_common.cuh"
+
+namespace ck {
+namespace {
+
+constexpr int kMaxRanks = 8;
+constexpr int kMaxBlocks = 512;
+constexpr int kThreads = 512;
+constexpr unsigned long long kWaitNs = 4000000000ull;   // 4 s: far beyond any skew between ranks in a running job
+
+__device__ int g_tp_status = 0;   // 0 ok; otherwise (phase << 16 | block) of the first wait that ran out
+
+struct ExchangeParams {
+    const uint4* partial[kMaxRanks];
+    uint4* residual[kMaxRanks];
+    uint32_t* pad[kMaxRanks];     // each rank's flag pad: start[kMaxBlocks][kMaxRanks], end[...], then epoch[kMaxBlocks]
+    const void* gate0;
+    const void* gate1;
+    int64_t split_vec;            // vectors (of 8 elements) before this index use gate0, the rest gate1
+    int64_t total_vec;            // rows * cols / 8
+    int vec_per_row;              // cols / 8
+    int rank, world;
+};
+
+__device__ __forceinline__ uint32_t* pad_start(uint32_t* pad, int block, int src) { return pad + (block * kMaxRanks + src); }
+__device__ __forceinline__ uint32_t* pad_end(uint32_t* pad, int block, int src) { return pad + kMaxBlocks * kMaxRanks + (block * kMaxRanks + src); }
+__device__ __forceinline__ uint32_t* pad_epoch(uint32_t* pad, int block) { return pad + 2 * kMaxBlocks * kMaxRanks + block; }
+
+__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
+    uint32_t v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ unsigned long long now_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+// 16-byte load that is served from L2 / the owning GPU, never from this SM's L1 (the data may have been
+// rewritten by another GPU since the last call).
+__device__ __forceinline__ uint4 ld_cg(const uint4* p) {
+    uint4 v;
+    asm volatile("ld.global.cg.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
+
+// Threads 0 .. world-1 of the block: signal peer `threadIdx.x`, then wait for its signal.
+__device__ __forceinline__ void block_barrier(const ExchangeParams& p, bool end_phase, uint32_t epoch) {
+    __syncthreads();
+    if ((int)threadIdx.x < p.world) {
+        const int peer = threadIdx.x;
+        uint32_t* theirs = end_phase ? pad_end(p.pad[peer], blockIdx.x, p.rank) : pad_start(p.pad[peer], blockIdx.x, p.rank);
+        st_release_sys(theirs, epoch);
+        const uint32_t* mine = end_phase ? pad_end(p.pad[p.rank], blockIdx.x, peer) : pad_start(p.pad[p.rank], blockIdx.x, peer);
+        const unsigned long long t0 = now_ns();
+        uint32_t spins = 0;
+        while ((int32_t)(ld_acquire_sys(mine) - epoch) < 0) {
+            if ((++spins & 255u) == 0 && now_ns() - t0 > kWaitNs) {
+                atomicCAS(&g_tp_status, 0, ((end_phase ? 2 : 1) << 16) | (int)blockIdx.x);
+                break;
+            }
+        }
+    }
+    __syncthreads();
+}
+
+template <typename T>
+__device__ __forceinline__ void unpack8(const uint4& v, float (&f)[8]);
+template <>
+__device__ __forceinline__ void unpack8<__nv_bfloat16>(const uint4& v, float (&f)[8]) {
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { f[2 * i] = __uint_as_float(w[i] << 16); f[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u); }
+}
+template <>
+__device__ __forceinline__ void unpack8<__half>(const uint4& v, float (&f)[8]) {
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float2 t = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
+        f[2 * i] = t.x; f[2 * i + 1] = t.y;
+    }
+}
+template <typename T>
+__device__ __forceinline__ uint32_t pack2(float a, float b);
+template <>
+__device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float a, float b) {
+    const __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+    return *reinterpret_cast<const uint32_t*>(&v);
+}
+template <>
+__device__ __forceinline__ uint32_t pack2<__half>(float a, float b) {
+    const __half2 v = __floats2half2_rn(a, b);
+    return *reinterpret_cast<const uint32_t*>(&v);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kThreads)
+tp_exchange_kernel(const ExchangeParams p) {
+    __shared__ uint32_t s_epoch;
+    uint32_t* my_pad = p.pad[p.rank];
+    if (threadIdx.x == 0) s_epoch = *pad_epoch(my_pad, blockIdx.x) + 1u;
+    __syncthreads();
+    const uint32_t epoch = s_epoch;
+
+    block_barrier(p, false, epoch);   // every rank's partial result is complete
+
+    // this rank's slice, and this block's part of it
+    const int64_t lo = p.total_vec * p.rank / p.world, hi = p.total_vec * (p.rank + 1) / p.world;
+    const int64_t per_block = (hi - lo + gridDim.x - 1) / gridDim.x;
+    const int64_t b0 = lo + per_block * blockIdx.x;
+    const int64_t b1 = b0 + per_block < hi ? b0 + per_block : hi;
+    constexpr int kUnroll = 2;
+    for (int64_t base = b0 + threadIdx.x; base < b1; base += (int64_t)kThreads * kUnroll) {
+        uint4 part[kUnroll][kMaxRanks];
+        uint4 xv[kUnroll];
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u) {
+            const int64_t idx = base + (int64_t)u * kThreads;
+            if (idx < b1) {
+#pragma unroll
+                for (int i = 0; i < kMaxRanks; ++i)
+                    if (i < p.world) part[u][i] = ld_cg(p.partial[i] + idx);
+                xv[u] = ld_cg(p.residual[p.rank] + idx);
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u) {
+            const int64_t idx = base + (int64_t)u * kThreads;
+            if (idx >= b1) continue;
+            float sum[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) sum[j] = 0.0f;
+#pragma unroll
+            for (int i = 0; i < kMaxRanks; ++i) {
+                if (i < p.world) {
+                    float f[8];
+                    unpack8<T>(part[u][i], f);
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) sum[j] += f[j];
+                }
+            }
+            const int col_vec = (int)(idx % p.vec_per_row);
+            const uint4* gate = reinterpret_cast<const uint4*>(idx < p.split_vec ? p.gate0 : p.gate1) + col_vec;
+            float g[8], x[8];
+            unpack8<T>(__ldg(gate), g);
+            unpack8<T>(xv[u], x);
+            uint32_t w[4];
+#pragma unroll
+            for (int j = 0; j < 8; j += 2) {
+                // y = the all-reduced GEMM output as it would have been stored; then x + gate * y, product and
+                // sum rounded separately in fp32 (what an elementwise addcmul on 16-bit tensors computes)
+                const float y0 = Elem<T>::round(sum[j]), y1 = Elem<T>::round(sum[j + 1]);
+                w[j >> 1] = pack2<T>(__fadd_rn(x[j], __fmul_rn(g[j], y0)), __fadd_rn(x[j + 1], __fmul_rn(g[j + 1], y1)));
+            }
+            const uint4 out = make_uint4(w[0], w[1], w[2], w[3]);
+#pragma unroll
+            for (int i = 0; i < kMaxRanks; ++i)
+                if (i < p.world) p.residual[i][idx] = out;
+        }
+    }
+    __threadfence_system();           // this thread's pushes are visible system-wide before the block signals
+    block_barrier(p, true, epoch);    // every peer has finished pushing its slice into my residual buffer
+    if (threadIdx.x == 0) *pad_epoch(my_pad, blockIdx.x) = epoch;
+}
+
+}  // namespace
+}  // namespace ck
+
+extern "C" int64_t ck_tp_pad_bytes(void) {
+    return (int64_t)sizeof(uint32_t) * (2 * ck::kMaxBlocks * ck::kMaxRanks + ck::kMaxBlocks);
+}
+
+extern "C" int launch_tp_exchange_kernel(const void* const* partials, void* const* residuals, void* const* pads, int world,
+                                         int rank, const void* gate0, const void* gate1, int64_t split_row, int64_t rows,
+                                         int64_t cols, int dtype_code, int blocks, cudaStream_t stream) {
+    using namespace ck;
+    if (!partials || !residuals || !pads || !gate0) CK_FAIL(CK_ERR_NULL, "tp_exchange: null pointer");
+    if (world < 1 || world > kMaxRanks || rank < 0 || rank >= world)
+        CK_FAIL(CK_ERR_SHAPE, "tp_exchange: rank %d of %d (at most %d ranks)", rank, world, kMaxRanks);
+    if (rows <= 0 || cols <= 0 || cols % 8 != 0 || split_row < 0)
+        CK_FAIL(CK_ERR_SHAPE, "tp_exchange: bad shape rows=%lld cols=%lld (cols must be a multiple of 8)", (long long)rows, (long long)cols);
+    if (dtype_code != CK_BF16 && dtype_code != CK_F16) CK_FAIL(CK_ERR_DTYPE, "tp_exchange: dtype code %d (bf16 or fp16)", dtype_code);
+    ExchangeParams p{};
+    for (int i = 0; i < world; ++i) {
+        if (!partials[i] || !residuals[i] || !pads[i]) CK_FAIL(CK_ERR_NULL, "tp_exchange: null buffer of rank %d", i);
+        if (!aligned16(partials[i]) || !aligned16(residuals[i]) || !aligned16(pads[i]))
+            CK_FAIL(CK_ERR_ALIGN, "tp_exchange: buffers must be 16-byte aligned");
+        p.partial[i] = static_cast<const uint4*>(partials[i]);
+        p.residual[i] = static_cast<uint4*>(residuals[i]);
+        p.pad[i] = static_cast<uint32_t*>(pads[i]);
+    }
+    if (!aligned16(gate0) || (gate1 && !aligned16(gate1))) CK_FAIL(CK_ERR_ALIGN, "tp_exchange: gates must be 16-byte aligned");
+    p.gate0 = gate0;
+    p.gate1 = gate1 ? gate1 : gate0;
+    p.vec_per_row = (int)(cols / 8);
+    p.total_vec = rows * (cols / 8);
+    p.split_vec = (split_row < rows ? split_row : rows) * (cols / 8);
+    if (!gate1) p.split_vec = p.total_vec;
+    p.rank = rank;
+    p.world = world;
+    if (blocks <= 0) blocks = 148;   // one per SM: 114 registers x 512 threads leave room for one block per SM
+    if (blocks > kMaxBlocks) blocks = kMaxBlocks;
+    if (dtype_code == CK_BF16) tp_exchange_kernel<__nv_bfloat16><<<blocks, kThreads, 0, stream>>>(p);
+    else tp_exchange_kernel<__half><<<blocks, kThreads, 0, stream>>>(p);
+    return launch_status("tp_exchange");
+}
+
+// Reads and clears the exchange kernel's status word (synchronises the device): 0, or
+// CK_ERR_DEVICE_TIMEOUT when a wait for a peer ran out since the last call.
+extern "C" int ck_tp_device_status(void) {
+    int v = 0, zero = 0;
+    cudaError_t e = cudaDeviceSynchronize();
+    if (e != cudaSuccess) CK_FAIL((int)e, "tp status: %s", cudaGetErrorString(e));
+    e = cudaMemcpyFromSymbol(&v, ck::g_tp_status, sizeof(int));
+    if (e != cudaSuccess) CK_FAIL((int)e, "tp status: %s", cudaGetErrorString(e));
+    cudaMemcpyToSymbol(ck::g_tp_status, &zero, sizeof(int));
+    if (v != 0) CK_FAIL(CK_ERR_DEVICE_TIMEOUT, "tp exchange kernel: the %s barrier of block %d timed out waiting for a peer",
+                        (v >> 16) == 1 ? "start" : "end", v & 0xffff);
+    return CK_OK;
+}

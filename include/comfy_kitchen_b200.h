@@ -187,6 +187,24 @@ int launch_adaln_quantize_mxfp8_kernel(const void* x, const void* scale, const v
  * call (the rows concerned were not written), or a positive cudaError_t. */
 int ck_norm_device_status(void);
 
+/* ---- tensor-parallel exchange (no counterpart in the reference, which has no multi-GPU code) ----
+ * Stands where a tensor-parallel port would call ncclAllReduce on the row-parallel GEMM's output and
+ * then an elementwise kernel:  x <- x + gate * (sum over ranks of partial), on every rank, in one
+ * kernel over NVLink peer memory.  Every rank launches it with the same arguments but its own `rank`.
+ * partials / residuals / pads: HOST arrays of `world` device pointers, entry i being rank i's buffer
+ * as mapped into this process (peer-accessible memory: CUDA IPC or symmetric memory); partial and
+ * residual are [rows, cols] of the 16-bit dtype; a pad is ck_tp_pad_bytes() bytes, zeroed once before
+ * first use, written by the kernel only.  Rows below split_row use gate0, the others gate1 (each [cols];
+ * gate1 NULL = gate0 for all).  blocks: grid size, the same on every rank (0 = default).  All ranks'
+ * residual buffers end bit-identical.  Waits for peers are bounded (seconds); see ck_tp_device_status. */
+int64_t ck_tp_pad_bytes(void);
+int launch_tp_exchange_kernel(const void* const* partials, void* const* residuals, void* const* pads, int world,
+                              int rank, const void* gate0, const void* gate1, int64_t split_row, int64_t rows,
+                              int64_t cols, int dtype_code, int blocks, ck_stream_t stream);
+/* Synchronises the device, reads and clears the exchange kernel's status word: 0, or
+ * CK_ERR_DEVICE_TIMEOUT when a wait for a peer ran out since the last call. */
+int ck_tp_device_status(void);
+
 #ifdef __cplusplus
 }
 #endif

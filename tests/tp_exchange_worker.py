@@ -1,0 +1,97 @@
+"""One rank of the multi-GPU exchange test (see tests/test_gpu_tp_exchange.py); run under torch.distributed.run."""
+import datetime
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+for p in (os.path.join(ROOT, "comfy-kitchen_b200"), ROOT):
+    if p not in sys.path:
+        sys.path.insert(0, p)
+
+
+def main() -> None:
+    rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=120))
+    from comfy_kitchen.dit_stack import DiTConfig, DiTStack, TensorParallel
+    from comfy_kitchen.tp_exchange import PeerExchange
+
+    # ---- the kernel against NCCL all-reduce + addcmul, both ways of sharing memory
+    rows, cols, split = 1000, 3072, 256
+    for mode in ("symm", "ipc"):
+        try:
+            ex = PeerExchange(None, dev, rows, cols, torch.bfloat16, mode=mode)
+            ok = torch.ones(1, device=dev)
+        except Exception as e:  # noqa: BLE001
+            print(f"[rank {rank}] peer memory mode {mode} unavailable: {type(e).__name__}: {e}", flush=True)
+            ex, ok = None, torch.zeros(1, device=dev)
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+        if ok.item() < 1:
+            continue
+        g = torch.Generator(device=dev).manual_seed(100 + rank)
+        gs = torch.Generator(device=dev).manual_seed(7)      # the same on every rank
+        x0 = torch.randn(rows, cols, device=dev, generator=gs).bfloat16()
+        g0 = torch.randn(cols, device=dev, generator=gs).bfloat16()
+        g1 = torch.randn(cols, device=dev, generator=gs).bfloat16()
+        ex.residual.copy_(x0)
+        want = x0.clone()
+        for it in range(3):
+            part = torch.randn(rows, cols, device=dev, generator=g).bfloat16()
+            ex.partial.copy_(part)
+            ex.exchange(g0, g1, split)
+            # reference: fp32 sum over the ranks in rank order, rounded once, then addcmul
+            allp = [torch.empty_like(part) for _ in range(world)]
+            dist.all_gather(allp, part)
+            s = torch.zeros(rows, cols, device=dev)
+            for t in allp:
+                s += t.float()
+            y = s.bfloat16()
+            want[:split] = torch.addcmul(want[:split], g0, y[:split])
+            want[split:] = torch.addcmul(want[split:], g1, y[split:])
+            assert torch.equal(ex.residual, want), f"rank {rank} mode {mode} call {it}: residual differs"
+        # all ranks hold the same bits
+        mine = ex.residual.clone()
+        ref = mine.clone()
+        dist.broadcast(ref, 0)
+        assert torch.equal(mine, ref)
+        assert ex.status() == 0
+        print(f"[rank {rank}] exchange kernel ok with peer memory mode {mode}", flush=True)
+        del ex
+
+    # ---- the stack: peer-exchange forward (eager and one graph) against the NCCL forward
+    cfg = DiTConfig(n_double=2, n_single=2, txt_tokens=128, img_grid=(16, 24))
+    g = torch.Generator().manual_seed(3)
+    img = torch.randn(cfg.img_tokens, cfg.hidden, generator=g).bfloat16().to(dev)
+    txt = torch.randn(cfg.txt_tokens, cfg.hidden, generator=g).bfloat16().to(dev)
+    vec = torch.randn(1, cfg.hidden, generator=g).bfloat16().to(dev)
+    base = DiTStack(cfg, dev, tp=TensorParallel())
+    base.calibrate(img, txt, vec)
+    y_nccl = base.forward(img, txt, vec)
+    fused = DiTStack(cfg, dev, tp=TensorParallel())
+    why = fused.try_enable_peer_exchange()
+    assert why is None, why
+    fused.sites.static = dict(base.sites.static)
+    y_eager = fused.forward(img, txt, vec)
+    rel = ((y_eager.float() - y_nccl.float()).norm() / y_nccl.float().norm()).item()
+    assert rel < 2e-2, rel      # NCCL sums in another order and precision: tolerance, not equality
+    run, how = fused.capture_best(img, txt, vec)
+    assert "one CUDA graph" in how
+    for _ in range(2):
+        y_graph = run(img, txt, vec)
+    torch.cuda.synchronize()
+    assert torch.equal(y_graph, y_eager), "graph replay differs from the eager forward"
+    assert fused.exchange.status() == 0
+    assert fused.ops.gemm_device_status() == 0
+    dist.barrier()
+    if rank == 0:
+        print(f"stack: fused vs NCCL relative difference {rel:.2e}; {how}")
+        print("TP_EXCHANGE_WORKER_OK", flush=True)
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
