@@ -242,20 +242,42 @@ SWEEP_M = (1024, 4608, 18432, 65536)
 SWEEP_K = (3072, 12288)
 
 
+class _GraphLoop:
+    """A list of launches recorded once into a CUDA graph, so that replaying them costs no host time per launch
+    (a Python call into the library takes longer than the small kernels run)."""
+
+    def __init__(self, fns, device):
+        self.n = len(fns)
+        side = torch.cuda.Stream(device)
+        side.wait_stream(torch.cuda.current_stream(device))
+        with torch.cuda.stream(side):
+            for f in fns:   # warm up on the capture stream: lazy initialisation must not be recorded
+                f()
+        torch.cuda.current_stream(device).wait_stream(side)
+        torch.cuda.synchronize(device)
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph, stream=side):
+            for f in fns:
+                f()
+        torch.cuda.current_stream(device).wait_stream(side)
+        self.graph.replay()
+        torch.cuda.synchronize(device)
+
+    def seconds_per_launch(self, reps: int) -> float:
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(reps):
+            self.graph.replay()
+        b.record()
+        b.synchronize()
+        return a.elapsed_time(b) / (reps * self.n) * 1e-3
+
+
 def _rotating_time(make_fn, n_sets: int, iters: int) -> float:
-    """Seconds per launch, back to back inside one event pair, cycling through `n_sets` independent sets of
-    tensors whose combined size exceeds L2 (so no launch finds its input there)."""
-    fns = [make_fn(i) for i in range(n_sets)]
-    for f in fns:
-        f()
-    torch.cuda.synchronize()
-    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    a.record()
-    for i in range(iters):
-        fns[i % n_sets]()
-    b.record()
-    torch.cuda.synchronize()
-    return a.elapsed_time(b) / iters * 1e-3
+    """Seconds per launch: one launch per tensor set, recorded into a CUDA graph and replayed back to back; the
+    sets together exceed L2, so no launch finds its input there."""
+    loop = _GraphLoop([make_fn(i) for i in range(n_sets)], torch.cuda.current_device())
+    return loop.seconds_per_launch(max(2, iters // n_sets))
 
 
 def quantizer_sweep(device, hbm_gbs: float) -> dict:
@@ -348,76 +370,74 @@ def _library_scaled_mm(kind: str, qa, qb, sa, sb, ga, gb, bias):
                         swizzle_a=SwizzleType.SWIZZLE_32_4_4, swizzle_b=SwizzleType.SWIZZLE_32_4_4)
 
 
-def gemm_vs_library(device, kinds=("nvfp4", "mxfp8"), rounds: int = 6) -> dict:
+def gemm_vs_library(device, kinds=("nvfp4", "mxfp8"), rounds: int = 5) -> dict:
     """Our block-scaled GEMMs beside the library's (cuBLASLt through torch's scaled_mm, the reference's eager
-    call) on the twelve sweep shapes, same process, same operands: single launches timed with CUDA events,
-    L2 flushed (256 MB memset) before each one, ours / library / ours / library ... so that clock drift under
-    the power cap hits both alike.  Reports TFLOP/s per shape and the ratio ours / library."""
+    call) on the twelve sweep shapes, same process, same operands.  Per shape and implementation the launches over
+    rotating operand sets (together larger than L2, at least two) are recorded into a CUDA graph; the two graphs
+    are replayed in turn, ours / library / ours / ..., so that clock drift under the power cap hits both alike,
+    and the median round counts.  Reports TFLOP/s per shape and the ratio ours / library."""
     from comfy_kitchen.backends import cuda as ck
 
-    flush = torch.empty(256 << 20, dtype=torch.uint8, device=device)
     g = torch.Generator(device=device).manual_seed(7)
-
-    def once(fn):
-        flush.zero_()
-        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        a.record()
-        fn()
-        b.record()
-        b.synchronize()
-        return a.elapsed_time(b)
-
     out = {}
     for kind in kinds:
         rows, lib_note = [], None
         for bsz in BATCHES:
             for name, n, k in LAYERS:
                 m = TOKENS * bsz
-                x = torch.randn(m, k, device=device, generator=g).bfloat16()
-                w = (0.02 * torch.randn(n, k, device=device, generator=g)).bfloat16()
-                bias16 = (0.02 * torch.randn(n, device=device, generator=g)).bfloat16()
-                if kind == "nvfp4":
-                    gx = (x.float().abs().max() / (6 * 448)).float().reshape(1)
-                    gw = (w.float().abs().max() / (6 * 448)).float().reshape(1)
-                    qx, sx = ck.quantize_nvfp4(x, gx)
-                    qw, sw = ck.quantize_nvfp4(w, gw)
-                    alpha = gx * gw
-                    ours = lambda: ck.scaled_mm_nvfp4(qx, qw, gx, gw, sx, sw, bias=bias16, out_dtype=torch.bfloat16, alpha=alpha)  # noqa: E731
-                else:
-                    gx = gw = None
-                    qx, sx = ck.quantize_mxfp8(x)
-                    qw, sw = ck.quantize_mxfp8(w)
-                    ours = lambda: ck.scaled_mm_mxfp8(qx, qw, sx, sw, bias=bias16, out_dtype=torch.bfloat16)  # noqa: E731
-                del x, w
-                lib = lambda: _library_scaled_mm(kind, qx, qw, sx, sw, gx, gw, bias16)  # noqa: E731
-                y = ours()
+                set_bytes = m * k // (2 if kind == "nvfp4" else 1) + n * k // (2 if kind == "nvfp4" else 1) + 2 * m * n
+                n_sets = max(2, min(8, -(-(300 << 20) // set_bytes)))
+                ours, lib = [], []
+                diff = None
+                for i in range(n_sets):
+                    x = torch.randn(m, k, device=device, generator=g).bfloat16()
+                    w = (0.02 * torch.randn(n, k, device=device, generator=g)).bfloat16()
+                    bias16 = (0.02 * torch.randn(n, device=device, generator=g)).bfloat16()
+                    if kind == "nvfp4":
+                        gx = (x.float().abs().max() / (6 * 448)).float().reshape(1)
+                        gw = (w.float().abs().max() / (6 * 448)).float().reshape(1)
+                        qx, sx = ck.quantize_nvfp4(x, gx)
+                        qw, sw = ck.quantize_nvfp4(w, gw)
+                        alpha = gx * gw
+                        ours.append(lambda qx=qx, qw=qw, gx=gx, gw=gw, sx=sx, sw=sw, b=bias16, al=alpha:
+                                    ck.scaled_mm_nvfp4(qx, qw, gx, gw, sx, sw, bias=b, out_dtype=torch.bfloat16, alpha=al))
+                    else:
+                        gx = gw = None
+                        qx, sx = ck.quantize_mxfp8(x)
+                        qw, sw = ck.quantize_mxfp8(w)
+                        ours.append(lambda qx=qx, qw=qw, sx=sx, sw=sw, b=bias16:
+                                    ck.scaled_mm_mxfp8(qx, qw, sx, sw, bias=b, out_dtype=torch.bfloat16))
+                    lib.append(lambda qx=qx, qw=qw, sx=sx, sw=sw, gx=gx, gw=gw, b=bias16:
+                               _library_scaled_mm(kind, qx, qw, sx, sw, gx, gw, b))
+                    del x, w
                 try:
-                    y_lib = lib()
+                    y, y_lib = ours[0](), lib[0]()
                     torch.cuda.synchronize()
                     diff = (y.float() - y_lib.float()).abs().max().item() / max(y_lib.float().abs().max().item(), 1e-30)
+                    loop_lib = _GraphLoop(lib, device)
                 except Exception as e:  # the library leg is a comparison, not the product: report and go on
-                    lib, lib_note, diff = None, f"{type(e).__name__}: {str(e)[:160]}", None
-                for _ in range(2):
-                    once(ours)
-                    if lib:
-                        once(lib)
+                    loop_lib, lib_note = None, f"{type(e).__name__}: {str(e)[:160]}"
+                loop_ours = _GraphLoop(ours, device)
+                reps = max(2, 16 // n_sets)
                 t_o, t_l = [], []
                 for _ in range(rounds):
-                    t_o.append(once(ours))
-                    if lib:
-                        t_l.append(once(lib))
+                    t_o.append(loop_ours.seconds_per_launch(reps))
+                    if loop_lib:
+                        t_l.append(loop_lib.seconds_per_launch(reps))
                 t_o.sort()
                 t_l.sort()
-                fl = 2.0 * m * n * k / 1e9
-                row = {"shape": [m, n, k], "ours_tflops": round(fl / t_o[len(t_o) // 2], 0)}
-                if lib:
+                fl = 2.0 * m * n * k / 1e12
+                row = {"shape": [m, n, k], "sets": n_sets, "ours_tflops": round(fl / t_o[len(t_o) // 2], 0)}
+                if loop_lib:
                     row["library_tflops"] = round(fl / t_l[len(t_l) // 2], 0)
                     row["ratio"] = round(t_l[len(t_l) // 2] / t_o[len(t_o) // 2], 3)
                     row["max_abs_diff_over_max"] = round(diff, 5)
                 rows.append(row)
+                del ours, lib, loop_ours, loop_lib
         ratios = [r["ratio"] for r in rows if "ratio" in r]
         out[kind] = {"shapes": rows, "library": "cuBLASLt via torch scaled_mm (the reference's eager call), bf16 bias",
-                     "timing": f"median of {rounds} single launches each, interleaved, L2 flushed before every launch"}
+                     "timing": f"median of {rounds} rounds, each a CUDA graph of launches over rotating operand sets larger "
+                               "than L2, ours and the library's graph replayed in turn"}
         if ratios:
             prod = 1.0
             for r in ratios:

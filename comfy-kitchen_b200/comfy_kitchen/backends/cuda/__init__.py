@@ -237,9 +237,13 @@ def scaled_mm_nvfp4(
     out_dtype: torch.dtype | None = None,
     alpha: torch.Tensor | None = None,
     out: torch.Tensor | None = None,
+    residual: torch.Tensor | None = None,
+    gate: torch.Tensor | None = None,
 ) -> torch.Tensor:
     """``out`` (not in the reference's signature): a contiguous [M, N] tensor of ``out_dtype`` to write into,
-    e.g. a row range of a larger buffer."""
+    e.g. a row range of a larger buffer.  ``residual`` [M, N] and ``gate`` [N] (both of ``out_dtype``, bf16 or
+    fp16; also additions): the kernel's epilogue returns ``residual + gate * y`` instead of ``y`` (bytes equal to
+    the GEMM followed by ``torch.addcmul``); ``out`` may be ``residual`` itself."""
     a, b = _plain(a), _plain(b)
     block_scale_a, block_scale_b = _plain(block_scale_a), _plain(block_scale_b)
     if alpha is None:
@@ -272,12 +276,27 @@ def scaled_mm_nvfp4(
         out = torch.empty(m, n, dtype=out_dtype, device=a.device)
     else:
         assert out.shape == (m, n) and out.dtype == out_dtype and out.is_contiguous() and out.device == a.device
+    if residual is not None:
+        assert gate is not None, "residual needs a gate"
+        gate = gate.reshape(-1)
+        assert out_dtype in (torch.bfloat16, torch.float16), "the fused residual update needs a 16-bit output"
+        assert residual.shape == (m, n) and residual.dtype == out_dtype and residual.is_contiguous()
+        assert gate.numel() == n and gate.dtype == out_dtype and gate.is_contiguous()
+        _native.call(
+            "launch_scaled_mm_nvfp4_residual_kernel", _ptr(a.contiguous()), _ptr(block_scale_a.contiguous().view(torch.uint8)),
+            _ptr(b.contiguous()), _ptr(block_scale_b.contiguous().view(torch.uint8)), _ptr(out), _ptr(bias), bias_code,
+            _ptr(residual), _ptr(gate), m, n, k, _ptr(alpha), _code(out_dtype, "scaled_mm_nvfp4"), _stream(a.device),
+        )
+        return out
     _native.call(
         "launch_scaled_mm_nvfp4_kernel", _ptr(a.contiguous()), _ptr(block_scale_a.contiguous().view(torch.uint8)),
         _ptr(b.contiguous()), _ptr(block_scale_b.contiguous().view(torch.uint8)), _ptr(out), _ptr(bias), bias_code,
         m, n, k, _ptr(alpha), _code(out_dtype, "scaled_mm_nvfp4"), _stream(a.device),
     )
     return out
+
+
+launch_residual_supported = True   # scaled_mm_nvfp4 accepts residual= / gate= (see its docstring)
 
 
 # ------------------------------------------------------------------ MXFP8

@@ -138,10 +138,11 @@ class QuantLinear:
         self.qdata, self.block_scales = ops.quantize_nvfp4(w.contiguous(), self.tensor_scale)
         self.bias = bias
 
-    def __call__(self, qx: torch.Tensor, sx: torch.Tensor, act_scale: torch.Tensor, out=None) -> torch.Tensor:
+    def __call__(self, qx: torch.Tensor, sx: torch.Tensor, act_scale: torch.Tensor, out=None, residual=None, gate=None) -> torch.Tensor:
         alpha = (act_scale * self.tensor_scale).reshape(1)
+        extra = {} if residual is None else {"residual": residual, "gate": gate}
         return self.ops.scaled_mm_nvfp4(qx, self.qdata, act_scale, self.tensor_scale, sx, self.block_scales,
-                                        bias=self.bias, out_dtype=torch.bfloat16, alpha=alpha, out=out)
+                                        bias=self.bias, out_dtype=torch.bfloat16, alpha=alpha, out=out, **extra)
 
 
 def _weight_scale(w: torch.Tensor) -> torch.Tensor:
@@ -170,6 +171,9 @@ class DiTStack:
         cfg.validate(self.tp.world)
         self.sites = _Sites()
         self.exchange = None   # PeerExchange once enable_peer_exchange() has run (CUDA only)
+        # the GEMM kernel can apply x += gate * y in its epilogue (CUDA backend; the CPU operator sets used by
+        # the tests have no such argument)
+        self.fuse_residual_in_gemm = self.device.type == "cuda" and hasattr(ops, "launch_residual_supported")
         self._xbuf = None      # the residual stream [tokens, hidden], text tokens first; updated in place
         self._mods = None   # all blocks' modulation vectors during a forward
         self.heads_local = cfg.heads // self.tp.world
@@ -397,6 +401,15 @@ class DiTStack:
         x = self._xbuf
         assert sum(rows) == x.shape[0]
         fused = self.exchange is not None
+        if self.tp.world == 1 and self.fuse_residual_in_gemm and self.tp.on_all_reduce is None:
+            # one rank: nothing to sum, so the GEMM's epilogue applies the residual update itself, in place
+            self.tp.all_reduce_calls += 1
+            off = 0
+            for lin, segs, site, r, gate in zip(linears, inputs, sites, rows, gates):
+                qx, sx, g = self._quant(site, segs)
+                lin(qx, sx, g, out=x[off:off + r], residual=x[off:off + r], gate=gate)
+                off += r
+            return
         y = self.exchange.partial if fused else torch.empty_like(x)
         off = 0
         for lin, segs, site, r in zip(linears, inputs, sites, rows):

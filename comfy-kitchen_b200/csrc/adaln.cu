@@ -415,13 +415,13 @@ int launch_warp(const NormArgs& a, cudaStream_t stream) {
             const size_t budget = 225 * 1024 - mb;
             int w = 0;
             if (g_norm_warps > 0) {
-                w = g_norm_warps > 24 ? 24 : g_norm_warps;
+                w = g_norm_warps > 32 ? 32 : g_norm_warps;
                 if (group > 1 && w > 16) w = 16;
                 w -= w % group;
                 if ((size_t)w * warp_bytes > budget) w = 0;
             } else {
-                for (int cand : {16, 12, 8, 6, 4, 2, 1})
-                    if (cand % group == 0 && (size_t)cand * warp_bytes <= budget) { w = cand; break; }
+                for (int cand : {32, 24, 16, 12, 8, 6, 4, 2, 1})
+                    if (cand % group == 0 && (group == 1 || cand <= 16) && (size_t)cand * warp_bytes <= budget) { w = cand; break; }
             }
             if (w == 0) continue;
             const int r = (size_t)w * 3 * warp_bytes <= budget ? 3 : ((size_t)w * 2 * warp_bytes <= budget ? 2 : 1);
@@ -433,16 +433,17 @@ int launch_warp(const NormArgs& a, cudaStream_t stream) {
         cache_mod = best_cache;
     }
     const size_t smem = mod_bytes + (size_t)warps * ring * warp_bytes + (size_t)warps * ring * 8 + (size_t)warps * 16;
-    // two builds of the kernel: up to 16 warps with 128 registers per thread, up to 24 with 80
+    // three builds of the kernel: up to 16 warps with 128 registers per thread, up to 24 with 80, up to 32 with 64
     // rows of 3072 and 4096 elements (the common hidden sizes) get fully unrolled builds
     const int iters = (a.D == 3072) ? 6 : (a.D == 4096 ? 8 : 0);
     auto kern = group == 4 ? norm_stream_kernel<T, kMode, 512, 0, 4>
               : group == 2 ? norm_stream_kernel<T, kMode, 512, 0, 2>
-              : warps > 16 ? norm_stream_kernel<T, kMode, 768, 0>
+              : warps > 24 ? (iters == 6 ? norm_stream_kernel<T, kMode, 1024, 6> : norm_stream_kernel<T, kMode, 1024, 0>)
+              : warps > 16 ? (iters == 8 ? norm_stream_kernel<T, kMode, 768, 8> : norm_stream_kernel<T, kMode, 768, 0>)
                            : (iters == 6 ? norm_stream_kernel<T, kMode, 512, 6>
                                          : (iters == 8 ? norm_stream_kernel<T, kMode, 512, 8> : norm_stream_kernel<T, kMode, 512, 0>));
-    const int attr_idx = group == 4 ? 5 : (group == 2 ? 4 : (warps > 16 ? 3 : (iters == 6 ? 1 : (iters == 8 ? 2 : 0))));
-    static bool attr_set[6][64] = {};
+    const int attr_idx = group == 4 ? 5 : (group == 2 ? 4 : (warps > 24 ? (iters == 6 ? 6 : 7) : (warps > 16 ? (iters == 8 ? 8 : 3) : (iters == 6 ? 1 : (iters == 8 ? 2 : 0)))));
+    static bool attr_set[9][64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev < 0 || dev >= 64 || !attr_set[attr_idx][dev]) {

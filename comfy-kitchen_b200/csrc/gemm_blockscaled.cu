@@ -47,6 +47,7 @@
 #include <cudaTypedefs.h>
 
 #include <mutex>
+#include <unordered_map>
 
 #include "ck_common.cuh"
 
@@ -262,6 +263,9 @@ struct GemmParams {
     int sf_row_tiles_b;   // 128-row scale tiles of W
     int out_code, bias_code;
     int tiles_m, tiles_n; // pair tiles (256 x 256)
+    // fused residual update (16-bit outputs only): D = residual + gate[n] * round(alpha * acc + bias); both null = off
+    const void* residual; // [M, N] in the output dtype, row pitch N (may be D itself)
+    const void* gate;     // [N] in the output dtype
 };
 
 // Tile order: bands of kGroupM tile rows, walked column by column inside a band, so that the ~74 tiles in
@@ -295,7 +299,7 @@ __device__ __forceinline__ uint32_t pack_pair<__half>(float a, float b) {
     return *reinterpret_cast<const uint32_t*>(&v);
 }
 
-template <bool kFp4>
+template <bool kFp4, bool kRes>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
 gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                         const __grid_constant__ CUtensorMap map_out, const GemmParams p) {
@@ -312,7 +316,8 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
     uint64_t* tmem_full = sf_full + kSfBufs;  //            accumulator complete -> epilogue
     uint64_t* tmem_empty = tmem_full + 1;     //            (leader's) both CTAs' accumulators copied out -> MMA issuer
     uint64_t* tile_open = tmem_empty + 1;     //            first MMA of a tile issued -> the second MMA issuer
-    uint32_t* s_tmem_base = reinterpret_cast<uint32_t*>(tile_open + 1);
+    uint64_t* drain = tile_open + 1;          // [2]        an MMA issuer that gave up: its MMAs in flight are done
+    uint32_t* s_tmem_base = reinterpret_cast<uint32_t*>(drain + 2);
     volatile int* s_abort = reinterpret_cast<volatile int*>(s_tmem_base + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -329,6 +334,8 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
         for (int b = 0; b < kSfBufs; ++b) mbar_init(&sf_full[b], 8);
         mbar_init(tmem_full, 2);   // one commit per tile from each MMA issuer
         mbar_init(tile_open, 1);
+        mbar_init(&drain[0], 1);
+        mbar_init(&drain[1], 1);
         mbar_init(tmem_empty, 2 * kEpiWarps);
         *s_abort = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -506,6 +513,12 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
             // commits nothing and arrives at once)
             if (ok) tc_commit_pair(tmem_full);
         }
+        if (!ok) {
+            // Gave up on a wait: the MMAs already issued still read both CTAs' stages and write both accumulators.
+            // Wait (bounded) until they are done before this CTA goes on to the final cluster barrier.
+            tc_commit_pair(&drain[which]);
+            (void)mbar_wait(&drain[which], 0, s_abort, kTimeoutTmemFull);
+        }
         }
     } else {
         // ------------------------------------------------------------ epilogue (warps 2..17)
@@ -540,6 +553,19 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
                 bias_reg[k] = b;
             }
             auto bias_at = [&](int col) { return __shfl_sync(0xffffffffu, bias_reg[col >> 5], col & 31); };
+            // fused residual update: gate for these 64 columns, kept like the bias
+            constexpr bool fuse_res = kRes;
+            float gate_reg[2] = {0.0f, 0.0f};
+            if (fuse_res) {
+#pragma unroll
+                for (int k = 0; k < 2; ++k) {
+                    const int n = n0 + k * 32 + lane;
+                    if (n < p.N)
+                        gate_reg[k] = p.out_code == CK_F16 ? __half2float(static_cast<const __half*>(p.gate)[n])
+                                                           : __bfloat162float(static_cast<const __nv_bfloat16*>(p.gate)[n]);
+                }
+            }
+            auto gate_at = [&](int col) { return __shfl_sync(0xffffffffu, gate_reg[col >> 5], col & 31); };
             ok = mbar_wait(tmem_full, local_tile & 1, s_abort, kTimeoutTmemFull);
             if (!ok) break;
             tc_fence_after();
@@ -561,17 +587,46 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
 #pragma unroll
             for (int ch = 0; ch < 4; ++ch) {
                 if (ch < n_chunks) {
+                    // the residual values this lane's row needs for the chunk (its 32 columns = 64 bytes), fetched
+                    // before the staging buffer is waited for
+                    uint4 xres[4];
+                    if (fuse_res) {
+                        const int64_t row = row0 + lane;
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            const int col = n0 + ch * 32 + 8 * j;
+                            xres[j] = make_uint4(0u, 0u, 0u, 0u);
+                            if (row < p.M && col < p.N)
+                                xres[j] = *reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(p.residual) + row * p.N + col);
+                        }
+                    }
                     if (lane == 0) bulk_wait_read_all();
                     __syncwarp();
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {   // one 16-byte piece: 8 columns (16-bit) or 4 (fp32)
                         uint32_t w[4];
                         if (p.out_code != CK_F32) {
+                            const uint32_t xw[4] = {xres[j].x, xres[j].y, xres[j].z, xres[j].w};
 #pragma unroll
                             for (int i = 0; i < 4; ++i) {
                                 const int c = 32 * (ch & 1) + 8 * j + 2 * i;
-                                const float a = fmaf(__uint_as_float(r[c >> 5][c & 31]), alpha, bias_at(c));
-                                const float b = fmaf(__uint_as_float(r[c >> 5][(c & 31) + 1]), alpha, bias_at(c + 1));
+                                float a = fmaf(__uint_as_float(r[c >> 5][c & 31]), alpha, bias_at(c));
+                                float b = fmaf(__uint_as_float(r[c >> 5][(c & 31) + 1]), alpha, bias_at(c + 1));
+                                if (fuse_res) {
+                                    // y rounded as it would have been stored, then x + gate * y with the product and the
+                                    // sum rounded separately (an elementwise addcmul on the stored tensors)
+                                    float x0, x1;
+                                    if (p.out_code == CK_BF16) {
+                                        a = __bfloat162float(__float2bfloat16_rn(a)); b = __bfloat162float(__float2bfloat16_rn(b));
+                                        x0 = __uint_as_float(xw[i] << 16); x1 = __uint_as_float(xw[i] & 0xffff0000u);
+                                    } else {
+                                        a = __half2float(__float2half_rn(a)); b = __half2float(__float2half_rn(b));
+                                        const float2 xf = __half22float2(*reinterpret_cast<const __half2*>(&xw[i]));
+                                        x0 = xf.x; x1 = xf.y;
+                                    }
+                                    a = __fadd_rn(x0, __fmul_rn(gate_at(c), a));
+                                    b = __fadd_rn(x1, __fmul_rn(gate_at(c + 1), b));
+                                }
                                 w[i] = p.out_code == CK_BF16 ? pack_pair<__nv_bfloat16>(a, b) : pack_pair<__half>(a, b);
                             }
                         } else {
@@ -654,6 +709,39 @@ int make_output_map(CUtensorMap* map, void* base, int64_t rows, int64_t cols, in
     return CK_OK;
 }
 
+// Encoded tensor maps are a pure function of (base, rows, row length, box, element size); a model calls the
+// GEMM with the same few weights and activation buffers over and over, so the three driver calls per launch
+// are replaced by a lookup.  (ck_set_option("gemm_map_cache", 0) turns the cache off.)
+struct MapKey {
+    const void* base; int64_t rows, cols; int kind;   // kind: box rows for operands, -(element bytes) for outputs
+    bool operator==(const MapKey& o) const { return base == o.base && rows == o.rows && cols == o.cols && kind == o.kind; }
+};
+struct MapKeyHash {
+    size_t operator()(const MapKey& k) const {
+        uint64_t h = reinterpret_cast<uintptr_t>(k.base) * 0x9E3779B97F4A7C15ull;
+        h ^= (uint64_t)k.rows * 0xC2B2AE3D27D4EB4Full + ((uint64_t)k.cols << 7) + (uint64_t)(k.kind + 64);
+        return (size_t)(h ^ (h >> 29));
+    }
+};
+int cached_map(CUtensorMap* map, const void* base, int64_t rows, int64_t cols, int kind) {
+    static std::mutex mu;
+    static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
+    const MapKey key{base, rows, cols, kind};
+    if (g_gemm_map_cache) {
+        std::lock_guard<std::mutex> lock(mu);
+        auto it = cache.find(key);
+        if (it != cache.end()) { *map = it->second; return CK_OK; }
+    }
+    const int rc = kind > 0 ? make_operand_map(map, base, rows, cols, kind)
+                            : make_output_map(map, const_cast<void*>(base), rows, cols, -kind);
+    if (rc == CK_OK && g_gemm_map_cache) {
+        std::lock_guard<std::mutex> lock(mu);
+        if (cache.size() >= 8192) cache.clear();   // bounded: a long-running process with ever-new buffers starts over
+        cache.emplace(key, *map);
+    }
+    return rc;
+}
+
 int sm_count() {
     static int cached[64] = {};
     int dev = 0;
@@ -667,10 +755,14 @@ int sm_count() {
     return cached[dev];
 }
 
-template <bool kFp4>
+template <bool kFp4, bool kRes = false>
 int launch_gemm(const void* a, const void* sfa, const void* b, const void* sfb, void* d, const void* bias,
-                int bias_code, int64_t M, int64_t N, int64_t K, const float* alpha, int out_code, cudaStream_t stream) {
+                int bias_code, int64_t M, int64_t N, int64_t K, const float* alpha, int out_code, cudaStream_t stream,
+                const void* residual = nullptr, const void* gate = nullptr) {
     const char* what = kFp4 ? "scaled_mm_nvfp4" : "scaled_mm_mxfp8";
+    if ((residual != nullptr) != (gate != nullptr)) CK_FAIL(CK_ERR_NULL, "%s: residual and gate go together", what);
+    if (residual && out_code == CK_F32) CK_FAIL(CK_ERR_DTYPE, "%s: the fused residual update needs a 16-bit output", what);
+    if (residual && (!aligned16(residual) || !aligned16(gate))) CK_FAIL(CK_ERR_ALIGN, "%s: residual and gate must be 16-byte aligned", what);
     if (!a || !sfa || !b || !sfb || !d) CK_FAIL(CK_ERR_NULL, "%s: null pointer", what);
     if (M <= 0 || N <= 0 || K <= 0 || M > INT32_MAX || N > INT32_MAX || K > INT32_MAX)
         CK_FAIL(CK_ERR_SHAPE, "%s: bad shape M=%lld N=%lld K=%lld", what, (long long)M, (long long)N, (long long)K);
@@ -685,12 +777,12 @@ int launch_gemm(const void* a, const void* sfa, const void* b, const void* sfb, 
         CK_FAIL(CK_ERR_ALIGN, "%s: operands, scales and output must be 16-byte aligned (row pitch too)", what);
 
     // per device: shared-memory opt-in, and how many CTA pairs can be resident at once
-    static int max_pairs[2][64] = {};
+    static int max_pairs[64] = {};   // (one table per instantiation of this function)
     int dev = 0;
     cudaGetDevice(&dev);
-    int pairs_cap = (dev >= 0 && dev < 64) ? max_pairs[kFp4][dev] : 0;
+    int pairs_cap = (dev >= 0 && dev < 64) ? max_pairs[dev] : 0;
     if (pairs_cap == 0) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_blockscaled_kernel<kFp4>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+        cudaError_t e = cudaFuncSetAttribute(gemm_blockscaled_kernel<kFp4, kRes>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
         if (e != cudaSuccess) CK_FAIL((int)e, "%s: cannot reserve %d bytes of shared memory: %s", what, kSmemBytes, cudaGetErrorString(e));
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = dim3(2 * (unsigned)(sm_count() / 2));
@@ -702,19 +794,19 @@ int launch_gemm(const void* a, const void* sfa, const void* b, const void* sfb, 
         cfg.attrs = &attr;
         cfg.numAttrs = 1;
         int n = 0;
-        e = cudaOccupancyMaxActiveClusters(&n, gemm_blockscaled_kernel<kFp4>, &cfg);
+        e = cudaOccupancyMaxActiveClusters(&n, gemm_blockscaled_kernel<kFp4, kRes>, &cfg);
         if (e != cudaSuccess || n <= 0) {
             cudaGetLastError();
             n = sm_count() / 2;
         }
         pairs_cap = n < sm_count() / 2 ? n : sm_count() / 2;
-        if (dev >= 0 && dev < 64) max_pairs[kFp4][dev] = pairs_cap;
+        if (dev >= 0 && dev < 64) max_pairs[dev] = pairs_cap;
     }
 
     CUtensorMap map_a, map_b, map_out;
-    if (int rc = make_operand_map(&map_a, a, M, row_bytes, BM)) return rc;
-    if (int rc = make_operand_map(&map_b, b, N, row_bytes, BN / 2)) return rc;
-    if (int rc = make_output_map(&map_out, d, M, N, out_code == CK_F32 ? 4 : 2)) return rc;
+    if (int rc = cached_map(&map_a, a, M, row_bytes, BM)) return rc;
+    if (int rc = cached_map(&map_b, b, N, row_bytes, BN / 2)) return rc;
+    if (int rc = cached_map(&map_out, d, M, N, out_code == CK_F32 ? -4 : -2)) return rc;
 
     GemmParams p{};
     p.sfa = static_cast<const uint8_t*>(sfa);
@@ -730,9 +822,11 @@ int launch_gemm(const void* a, const void* sfa, const void* b, const void* sfb, 
     p.bias_code = bias_code;
     p.tiles_m = (int)ceil_div(M, 2 * BM);
     p.tiles_n = (int)ceil_div(N, BN);
+    p.residual = residual;
+    p.gate = gate;
     const int64_t tiles = (int64_t)p.tiles_m * p.tiles_n;
     const int grid = 2 * (int)(tiles < pairs_cap ? tiles : pairs_cap);   // clusters of two CTAs
-    gemm_blockscaled_kernel<kFp4><<<grid, kThreads, kSmemBytes, stream>>>(map_a, map_b, map_out, p);
+    gemm_blockscaled_kernel<kFp4, kRes><<<grid, kThreads, kSmemBytes, stream>>>(map_a, map_b, map_out, p);
     return launch_status(what);
 }
 
@@ -747,6 +841,18 @@ extern "C" int launch_scaled_mm_nvfp4_kernel(const void* A, const void* A_scale,
                                              cudaStream_t stream) {
     return ck::launch_gemm<true>(A, A_scale, B, B_scale, D, bias, bias_dtype_code, M, N, K, alpha_device_ptr,
                                  out_dtype_code, stream);
+}
+
+// launch_scaled_mm_nvfp4_kernel followed by  D = residual + gate[n] * D  (an elementwise addcmul on the stored
+// 16-bit tensors), in the GEMM's epilogue.  residual: [M, N] in the output dtype, may be D itself (in place);
+// gate: [N] in the output dtype.  No counterpart in the reference.
+extern "C" int launch_scaled_mm_nvfp4_residual_kernel(const void* A, const void* A_scale, const void* B, const void* B_scale,
+                                                      void* D, const void* bias, int bias_dtype_code, const void* residual,
+                                                      const void* gate, int64_t M, int64_t N, int64_t K,
+                                                      const float* alpha_device_ptr, int out_dtype_code, cudaStream_t stream) {
+    if (!residual || !gate) CK_FAIL(CK_ERR_NULL, "scaled_mm_nvfp4_residual: null residual or gate");
+    return ck::launch_gemm<true, true>(A, A_scale, B, B_scale, D, bias, bias_dtype_code, M, N, K, alpha_device_ptr,
+                                       out_dtype_code, stream, residual, gate);
 }
 
 // Same contraction, MXFP8 operands: A: [M, K] E4M3, W: [N, K] E4M3, scales tiled E8M0.

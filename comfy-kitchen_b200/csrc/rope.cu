@@ -59,17 +59,40 @@ __device__ __forceinline__ void load_table(const TF* __restrict__ f, float (&m)[
     }
 }
 
+// 16 bytes through the read-only path without allocating in L1 (every byte is used once).
+__device__ __forceinline__ uint4 ldg128(const void* p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
+template <typename T>
+__device__ __forceinline__ void unpack8_16(const uint4& u, float (&v)[8]) {
+    const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        if (sizeof(T) == 2 && Elem<T>::code == CK_BF16) {
+            v[2 * i] = __uint_as_float(w[i] << 16);
+            v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+        } else {
+            const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
+            v[2 * i] = f.x; v[2 * i + 1] = f.y;
+        }
+    }
+}
+
 template <typename TX, typename TF, bool kSplit>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, 3)
 rope_vec_kernel(const TX* __restrict__ xq, const TX* __restrict__ xk, const TF* __restrict__ freqs,
                 TX* __restrict__ oq, TX* __restrict__ ok, const RopeParams p) {
     constexpr int kPairs = kSplit ? 8 : 4;
-    const int64_t gid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    // work item = (vector of the row, site, chunk of the broadcast walk); the grid is sized to the machine
+    // (a whole number of resident blocks per SM) and strides over the items
+    const int64_t n_items = (int64_t)p.n_vec * p.n_sites * p.n_chunks;
+    for (int64_t gid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; gid < n_items; gid += (int64_t)gridDim.x * blockDim.x) {
     const int v = (int)(gid % p.n_vec);
     int64_t t = gid / p.n_vec;
     const int64_t site = t % p.n_sites;
     const int64_t c = t / p.n_sites;
-    if (c >= p.n_chunks) return;
 
     // site -> indices of the non-broadcast dims
     int64_t s = site, xoff = 0, foff = 0;
@@ -100,7 +123,47 @@ rope_vec_kernel(const TX* __restrict__ xq, const TX* __restrict__ xk, const TF* 
     const int64_t col = kSplit ? (int64_t)v * 8 : (int64_t)v * 8;
     const int64_t half = p.D / 2;
 
-#pragma unroll 4
+    // Interleaved layout with 16-bit activations (the shape a DiT runs): steps are taken four at a time, with the
+    // eight 16-byte loads (q and k of four steps) issued before anything is computed or stored, so that each
+    // thread keeps 128 bytes of reads in flight.
+    if (!kSplit && sizeof(TX) == 2) {
+        constexpr int kBatch = 4;
+        for (; j + kBatch <= j_end; j += kBatch) {
+            int64_t offs[kBatch];
+            uint4 raw[2][kBatch];
+#pragma unroll
+            for (int b = 0; b < kBatch; ++b) {
+                offs[b] = xoff + idx[0] * p.sx[0] + idx[1] * p.sx[1] + idx[2] * p.sx[2] + col;
+                if (++idx[2] == lim[2]) {
+                    idx[2] = 0;
+                    if (++idx[1] == lim[1]) { idx[1] = 0; ++idx[0]; }
+                }
+            }
+#pragma unroll
+            for (int b = 0; b < kBatch; ++b) {
+                raw[0][b] = ldg128(xq + offs[b]);
+                if (xk != nullptr) raw[1][b] = ldg128(xk + offs[b]);
+            }
+#pragma unroll
+            for (int b = 0; b < kBatch; ++b) {
+#pragma unroll
+                for (int which = 0; which < 2; ++which) {
+                    TX* __restrict__ dst = which ? ok : oq;
+                    if ((which ? xk : xq) == nullptr) continue;
+                    float x[8], o[8];
+                    unpack8_16<TX>(raw[which][b], x);
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        const float a = Elem<TF>::round(x[2 * q]), bb = Elem<TF>::round(x[2 * q + 1]);
+                        o[2 * q] = rot<TF>(m[q][0], m[q][1], a, bb);
+                        o[2 * q + 1] = rot<TF>(m[q][2], m[q][3], a, bb);
+                    }
+                    store8<TX>(dst + offs[b], o);
+                }
+            }
+        }
+    }
+#pragma unroll 2
     for (; j < j_end; ++j) {
         const int64_t off = xoff + idx[0] * p.sx[0] + idx[1] * p.sx[1] + idx[2] * p.sx[2] + col;
 #pragma unroll
@@ -137,6 +200,7 @@ rope_vec_kernel(const TX* __restrict__ xq, const TX* __restrict__ xk, const TF* 
             idx[2] = 0;
             if (++idx[1] == lim[1]) { idx[1] = 0; ++idx[0]; }
         }
+    }
     }
 }
 
@@ -175,6 +239,17 @@ rope_generic_kernel(const TX* __restrict__ xq, const TX* __restrict__ xk, const 
     }
 }
 
+inline int sm_count_cached() {
+    static int n = 0;
+    if (n == 0) {
+        int dev = 0, v = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev);
+        n = v > 0 ? v : 148;
+    }
+    return n;
+}
+
 template <typename TX, typename TF>
 int launch(const void* xq, const void* xk, const void* freqs, void* oq, void* ok, RopeParams p, bool split_half,
            bool vec_ok, cudaStream_t stream) {
@@ -183,19 +258,20 @@ int launch(const void* xq, const void* xk, const void* freqs, void* oq, void* ok
     auto o1 = static_cast<TX*>(oq), o2 = static_cast<TX*>(ok);
     if (vec_ok) {
         p.n_vec = split_half ? p.D / 16 : p.D / 8;
-        // A thread loads its 2x2 matrices once and reuses them for every broadcast step it walks, so long walks
-        // are cheapest: the walk is split into chunks only as far as needed to give every SM ~512 threads
-        // (measured on [2, 24, 4608, 128]: 4.46 TB/s when aiming for 4096 threads per SM, 4.67 for 512).
-        const int64_t base_threads = p.n_sites * p.n_vec;
-        const int64_t want_threads = 148LL * (g_rope_threads_per_sm > 0 ? g_rope_threads_per_sm : 512);
-        int64_t n_chunks = ceil_div(want_threads, base_threads);
-        if (n_chunks > p.n_bcast) n_chunks = p.n_bcast;
-        if (n_chunks < 1) n_chunks = 1;
-        p.chunk = ceil_div(p.n_bcast, n_chunks);
+        // A thread loads its 2x2 matrices once per work item and reuses them for the item's broadcast steps.  Items
+        // are chunks of 8 steps where the broadcast extent allows (two batches of four in the kernel), and the grid
+        // is three resident blocks per SM striding over the items: on [B, 24, 4608, 128] that is 2, 4 or 8 items
+        // per thread for B = 1, 2, 4 with at most 3 % of the last round idle.
+        int64_t chunk = g_rope_threads_per_sm > 0 ? ceil_div(p.n_bcast, ceil_div(148LL * g_rope_threads_per_sm, p.n_sites * p.n_vec))
+                                                  : (p.n_bcast >= 8 ? 8 : p.n_bcast);
+        if (chunk < 1) chunk = 1;
+        if (chunk > p.n_bcast) chunk = p.n_bcast;
+        p.chunk = chunk;
         p.n_chunks = ceil_div(p.n_bcast, p.chunk);
-        const int64_t threads = base_threads * p.n_chunks;
-        const int64_t blocks = ceil_div(threads, 256);
-        if (blocks > 0x7fffffffLL) CK_FAIL(CK_ERR_SHAPE, "apply_rope: tensor too large");
+        const int64_t threads = p.n_sites * p.n_vec * p.n_chunks;
+        int64_t blocks = ceil_div(threads, 256);
+        const int64_t resident = 3LL * sm_count_cached();
+        if (blocks > resident) blocks = resident;
         if (split_half)
             rope_vec_kernel<TX, TF, true><<<(unsigned)blocks, 256, 0, stream>>>(q, k, f, o1, o2, p);
         else

@@ -126,6 +126,13 @@ int launch_cublas_gemm_blockwise_fp4_kernel(const void* B_ptr, const void* B_dec
 int launch_scaled_mm_nvfp4_kernel(const void* A, const void* A_scale, const void* B, const void* B_scale, void* D,
                                   const void* bias, int bias_dtype_code, int64_t M, int64_t N, int64_t K,
                                   const float* alpha_device_ptr, int out_dtype_code, ck_stream_t stream);
+/* launch_scaled_mm_nvfp4_kernel followed by D = residual + gate[n] * D in the same kernel (the residual update
+ * of a transformer block; no counterpart in the reference).  residual: [M, N] in the output dtype (bf16 / fp16),
+ * may be D itself; gate: [N] in the output dtype.  Bytes equal GEMM -> elementwise addcmul on the stored tensors. */
+int launch_scaled_mm_nvfp4_residual_kernel(const void* A, const void* A_scale, const void* B, const void* B_scale,
+                                           void* D, const void* bias, int bias_dtype_code, const void* residual,
+                                           const void* gate, int64_t M, int64_t N, int64_t K,
+                                           const float* alpha_device_ptr, int out_dtype_code, ck_stream_t stream);
 int launch_scaled_mm_mxfp8_kernel(const void* A, const void* A_scale, const void* B, const void* B_scale, void* D,
                                   const void* bias, int bias_dtype_code, int64_t M, int64_t N, int64_t K,
                                   int out_dtype_code, ck_stream_t stream);

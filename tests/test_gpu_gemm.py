@@ -172,3 +172,46 @@ def test_reference_argument_order_entry_point(ck):
                  P(alpha), 2, ctypes.c_void_p(0), False, ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
     assert torch.equal(out, want)
     assert ck.gemm_device_status() == 0
+
+
+@pytest.mark.parametrize("M,N,K", [(300, 520, 192), (1024, 3072, 3072), (4608, 3072, 12288)])
+@pytest.mark.parametrize("odt", [torch.bfloat16, torch.float16])
+def test_fused_residual_epilogue_equals_gemm_then_addcmul(ck, M, N, K, odt):
+    """scaled_mm_nvfp4(residual=x, gate=g) must return the bytes of torch.addcmul(x, g, scaled_mm_nvfp4(...)), written
+    to a fresh tensor or over the residual itself."""
+    x, w, bias = _operands(M, N, K, 6)
+    g = torch.Generator().manual_seed(7)
+    res = torch.randn(M, N, generator=g).to(odt).cuda()
+    gate = torch.randn(1, N, generator=g).to(odt).cuda()
+    gx = (x.float().abs().max() / (6 * 448)).float().cuda()
+    gw = (w.float().abs().max() / (6 * 448)).float().cuda()
+    qx, sx = ck.quantize_nvfp4(x.cuda(), gx)
+    qw, sw = ck.quantize_nvfp4(w.cuda(), gw)
+    y = ck.scaled_mm_nvfp4(qx, qw, gx, gw, sx, sw, bias=bias.cuda(), out_dtype=odt)
+    want = torch.addcmul(res, gate, y)
+    got = ck.scaled_mm_nvfp4(qx, qw, gx, gw, sx, sw, bias=bias.cuda(), out_dtype=odt, residual=res, gate=gate)
+    assert torch.equal(got, want)
+    inplace = res.clone()
+    ck.scaled_mm_nvfp4(qx, qw, gx, gw, sx, sw, bias=bias.cuda(), out_dtype=odt, out=inplace, residual=inplace, gate=gate)
+    assert torch.equal(inplace, want)
+    assert ck.gemm_device_status() == 0
+
+
+def test_tensor_map_cache_is_transparent(ck):
+    """Encoded tensor maps are cached per (pointer, shape): a buffer that is freed and reallocated with another
+    shape at the same address, and the cache switched off, must give the same results."""
+    outs = []
+    for use_cache in (1, 0, 1):
+        ck.set_option("gemm_map_cache", use_cache)
+        for (M, N, K) in [(256, 384, 512), (384, 256, 512), (256, 384, 512)]:
+            x, w, bias = _operands(M, N, K, 8)
+            gx = (x.float().abs().max() / (6 * 448)).float().cuda()
+            gw = (w.float().abs().max() / (6 * 448)).float().cuda()
+            qx, sx = ck.quantize_nvfp4(x.cuda(), gx)
+            qw, sw = ck.quantize_nvfp4(w.cuda(), gw)
+            outs.append((use_cache, M, N, ck.scaled_mm_nvfp4(qx, qw, gx, gw, sx, sw, out_dtype=torch.float32).cpu()))
+            del qx, sx, qw, sw
+    ck.set_option("gemm_map_cache", 1)
+    base = {(m, n): o for c, m, n, o in outs[:3]}
+    for c, m, n, o in outs:
+        assert torch.equal(o, base[(m, n)])
