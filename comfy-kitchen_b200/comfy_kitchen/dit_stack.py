@@ -138,6 +138,17 @@ class QuantLinear:
         self.qdata, self.block_scales = ops.quantize_nvfp4(w.contiguous(), self.tensor_scale)
         self.bias = bias
 
+    @classmethod
+    def from_shard(cls, ops, shard, bias: torch.Tensor | None) -> "QuantLinear":
+        """From a QuantizedTensor cut out of a checkpoint (comfy_kitchen/sharding.py): nothing is re-quantized."""
+        self = cls.__new__(cls)
+        self.ops = ops
+        self.n, self.k = shard._params.orig_shape
+        self.tensor_scale = shard._params.scale.float().reshape(())
+        self.qdata, self.block_scales = shard._qdata, shard._params.block_scale
+        self.bias = bias
+        return self
+
     def __call__(self, qx: torch.Tensor, sx: torch.Tensor, act_scale: torch.Tensor, out=None, residual=None, gate=None) -> torch.Tensor:
         alpha = (act_scale * self.tensor_scale).reshape(1)
         extra = {} if residual is None else {"residual": residual, "gate": gate}
@@ -163,7 +174,11 @@ class DiTStack:
     ops: a module or object with the package's operator names (default: the CUDA backend).
     """
 
-    def __init__(self, cfg: DiTConfig, device, tp: TensorParallel | None = None, ops=None):
+    def __init__(self, cfg: DiTConfig, device, tp: TensorParallel | None = None, ops=None, state: dict | None = None):
+        """``state``: a checkpoint of the whole (unsharded) model in the reference's key contract, as
+        ``make_checkpoint`` writes it; each rank then cuts its shards out of the packed codes and tiled scales
+        (no re-quantization).  Without it the weights are drawn and quantized here."""
+        self._state = state
         if ops is None:
             from comfy_kitchen.backends import cuda as ops  # raises if the native library is missing
         self.cfg, self.ops, self.device = cfg, ops, torch.device(device)
@@ -181,6 +196,7 @@ class DiTStack:
         self.double = [self._make_double(i) for i in range(cfg.n_double)]
         self.single = [self._make_single(i) for i in range(cfg.n_single)]
         self._pack_modulation()
+        self._state = None
 
     # ------------------------------------------------------------------ weights
 
@@ -190,57 +206,82 @@ class DiTStack:
         g.manual_seed((self.cfg.seed * 1_000_003 + layer * 101 + sum(map(ord, name))) & 0x7FFFFFFF)
         return (std * torch.randn(shape, generator=g, device=dev, dtype=torch.float32)).bfloat16().to(self.device)
 
-    def _head_rows(self, per_part_rows: int) -> torch.Tensor:
-        """Row indices of this rank's heads inside one of q / k / v (each heads * head_dim rows)."""
+    def _head_range(self) -> tuple[int, int]:
+        """This rank's heads as a row range inside one of q / k / v (each heads * head_dim rows)."""
         hd = self.cfg.head_dim
         lo = self.tp.rank * self.heads_local * hd
-        return torch.arange(lo, lo + self.heads_local * hd, device=self.device)
+        return lo, lo + self.heads_local * hd
 
-    def _qkv_rows(self) -> torch.Tensor:
+    def _qkv_ranges(self) -> list[tuple[int, int]]:
         h = self.cfg.hidden
-        r = self._head_rows(h)
-        return torch.cat([r, r + h, r + 2 * h])
+        lo, hi = self._head_range()
+        return [(lo, hi), (h + lo, h + hi), (2 * h + lo, 2 * h + hi)]
 
-    def _mlp_slice(self) -> slice:
+    def _mlp_range(self, base: int = 0) -> tuple[int, int]:
         n = self.cfg.mlp_hidden // self.tp.world
-        return slice(self.tp.rank * n, (self.tp.rank + 1) * n)
+        return base + self.tp.rank * n, base + (self.tp.rank + 1) * n
 
-    def _linear(self, w_full: torch.Tensor, rows=None, cols=None, bias_full=None, row_parallel=False) -> QuantLinear:
-        ts = _weight_scale(w_full)
-        w = w_full
-        if rows is not None:
-            w = w[rows]
-        if cols is not None:
-            w = w[:, cols]
-        bias = None
-        if bias_full is not None:
-            if row_parallel:  # the partial results are summed: the bias goes in once
-                bias = bias_full if self.tp.rank == 0 else None
-            else:
-                bias = bias_full[rows] if rows is not None else bias_full
-        return QuantLinear(self.ops, w, ts, None if bias is None else bias.float().contiguous())
+    def _index(self, ranges) -> torch.Tensor:
+        return torch.cat([torch.arange(lo, hi, device=self.device) for lo, hi in ranges])
+
+    def _linear(self, name: str, layer: int, shape, rows=None, cols=None, row_parallel=False) -> QuantLinear:
+        """One quantized linear of this rank: the shard [rows (ranges) x cols (ranges)] of the full weight `name`
+        of block `layer` ([N, K] = shape).  From the checkpoint when there is one, else drawn and quantized here
+        with the per-tensor scale of the unsliced weight."""
+        c = self.cfg
+        key = f"{layer}.{name}."
+        if self._state is not None:
+            from comfy_kitchen.sharding import take_ranges
+            from comfy_kitchen.tensor import QuantizedTensor, TensorCoreNVFP4Layout
+
+            st = self._state
+            params = TensorCoreNVFP4Layout.Params(scale=st[key + "weight_scale_2"].to(self.device), orig_dtype=torch.bfloat16,
+                                                  orig_shape=tuple(shape),
+                                                  block_scale=st[key + "weight_scale"].to(self.device).view(torch.float8_e4m3fn))
+            qt = QuantizedTensor(st[key + "weight"].to(self.device), "TensorCoreNVFP4Layout", params)
+            if rows is not None:
+                qt = take_ranges(qt, 0, rows)
+            if cols is not None:
+                qt = take_ranges(qt, 1, cols)
+            bias_full = st[key + "bias"].to(self.device)
+        else:
+            w_full = self._randn(shape, layer, name, c.weight_std)
+            bias_full = self._randn((shape[0],), layer, name + "_b", c.weight_std)
+            ts = _weight_scale(w_full)
+            w = w_full
+            if rows is not None:
+                w = w[self._index(rows)]
+            if cols is not None:
+                w = w[:, self._index(cols)]
+            qt = None
+        if row_parallel:  # the partial results are summed: the bias goes in once
+            bias = bias_full if self.tp.rank == 0 else None
+        else:
+            bias = bias_full[self._index(rows)] if rows is not None else bias_full
+        bias = None if bias is None else bias.float().contiguous()
+        if qt is not None:
+            return QuantLinear.from_shard(self.ops, qt, bias)
+        return QuantLinear(self.ops, w, ts, bias)
+
+    def _mod(self, layer: int, n: int):
+        if self._state is not None:
+            return self._state[f"{layer}.mod_w"].to(self.device), self._state[f"{layer}.mod_b"].to(self.device)
+        h = self.cfg.hidden
+        return self._randn((n * h, h), layer, "mod_w", self.cfg.weight_std), self._randn((n * h,), layer, "mod_b", self.cfg.weight_std)
 
     def _make_double(self, i: int) -> dict:
         c, blk = self.cfg, {}
         h, hd = c.hidden, c.head_dim
-        attn_cols = self._head_rows(h)
         for s in ("img", "txt"):
             L = 1000 + 2 * i + (s == "txt")
             p = {}
-            p["mod_w"] = self._randn((6 * h, h), L, "mod_w", c.weight_std)
-            p["mod_b"] = self._randn((6 * h,), L, "mod_b", c.weight_std)
-            p["qkv"] = self._linear(self._randn((3 * h, h), L, "qkv", c.weight_std), rows=self._qkv_rows(),
-                                    bias_full=self._randn((3 * h,), L, "qkv_b", c.weight_std))
+            p["mod_w"], p["mod_b"] = self._mod(L, 6)
+            p["qkv"] = self._linear("qkv", L, (3 * h, h), rows=self._qkv_ranges())
             p["q_norm"] = torch.ones(hd, device=self.device, dtype=torch.bfloat16)
             p["k_norm"] = torch.ones(hd, device=self.device, dtype=torch.bfloat16)
-            p["proj"] = self._linear(self._randn((h, h), L, "proj", c.weight_std), cols=attn_cols,
-                                     bias_full=self._randn((h,), L, "proj_b", c.weight_std), row_parallel=True)
-            ms = self._mlp_slice()
-            mrows = torch.arange(ms.start, ms.stop, device=self.device)
-            p["up"] = self._linear(self._randn((c.mlp_hidden, h), L, "up", c.weight_std), rows=mrows,
-                                   bias_full=self._randn((c.mlp_hidden,), L, "up_b", c.weight_std))
-            p["down"] = self._linear(self._randn((h, c.mlp_hidden), L, "down", c.weight_std), cols=mrows,
-                                     bias_full=self._randn((h,), L, "down_b", c.weight_std), row_parallel=True)
+            p["proj"] = self._linear("proj", L, (h, h), cols=[self._head_range()], row_parallel=True)
+            p["up"] = self._linear("up", L, (c.mlp_hidden, h), rows=[self._mlp_range()])
+            p["down"] = self._linear("down", L, (h, c.mlp_hidden), cols=[self._mlp_range()], row_parallel=True)
             blk[s] = p
         return blk
 
@@ -248,21 +289,15 @@ class DiTStack:
         c = self.cfg
         h = c.hidden
         L = 5000 + i
-        ms = self._mlp_slice()
-        mrows = torch.arange(ms.start, ms.stop, device=self.device)
         p = {}
-        p["mod_w"] = self._randn((3 * h, h), L, "mod_w", c.weight_std)
-        p["mod_b"] = self._randn((3 * h,), L, "mod_b", c.weight_std)
+        p["mod_w"], p["mod_b"] = self._mod(L, 3)
         # linear1 rows: [q | k | v | mlp]; this rank keeps its heads of q, k, v and its slice of the MLP
-        rows1 = torch.cat([self._qkv_rows(), 3 * h + mrows])
-        p["linear1"] = self._linear(self._randn((3 * h + c.mlp_hidden, h), L, "linear1", c.weight_std), rows=rows1,
-                                    bias_full=self._randn((3 * h + c.mlp_hidden,), L, "linear1_b", c.weight_std))
+        p["linear1"] = self._linear("linear1", L, (3 * h + c.mlp_hidden, h), rows=self._qkv_ranges() + [self._mlp_range(3 * h)])
         p["q_norm"] = torch.ones(c.head_dim, device=self.device, dtype=torch.bfloat16)
         p["k_norm"] = torch.ones(c.head_dim, device=self.device, dtype=torch.bfloat16)
         # linear2 columns: [attention output | MLP activations], sliced the same way
-        cols2 = torch.cat([self._head_rows(h), h + mrows])
-        p["linear2"] = self._linear(self._randn((h, h + c.mlp_hidden), L, "linear2", c.weight_std), cols=cols2,
-                                    bias_full=self._randn((h,), L, "linear2_b", c.weight_std), row_parallel=True)
+        p["linear2"] = self._linear("linear2", L, (h, h + c.mlp_hidden), cols=[self._head_range(), self._mlp_range(h)],
+                                    row_parallel=True)
         return p
 
     def _pack_modulation(self) -> None:
@@ -637,6 +672,43 @@ class DiTStack:
 
     def expected_all_reduces(self) -> int:
         return 2 * self.cfg.n_double + self.cfg.n_single
+
+
+def make_checkpoint(cfg: DiTConfig, device, ops=None) -> dict:
+    """The whole synthetic model as a checkpoint in the reference's key contract (samples/nvfp4_linear.py:39-80):
+    per linear ``<layer>.<name>.weight`` (packed NVFP4 codes [N, K/2]), ``.weight_scale`` (tiled E4M3 block scales
+    as uint8), ``.weight_scale_2`` (fp32 per-tensor scale), ``.bias``; per block ``<layer>.mod_w`` / ``.mod_b``.
+    Every weight is quantized as a whole, on ``device``, from the same random draws DiTStack makes itself, so a
+    stack built from this checkpoint on any number of ranks equals one built directly."""
+    one = DiTStack.__new__(DiTStack)
+    if ops is None:
+        from comfy_kitchen.backends import cuda as ops
+    one.cfg, one.ops, one.device, one._state = cfg, ops, torch.device(device), None
+    h, m = cfg.hidden, cfg.mlp_hidden
+    out = {}
+
+    def put(layer, name, shape):
+        w = one._randn(shape, layer, name, cfg.weight_std)
+        ts = _weight_scale(w).float().reshape(1)
+        q, sf = ops.quantize_nvfp4(w.contiguous(), ts)
+        key = f"{layer}.{name}."
+        out[key + "weight"], out[key + "weight_scale"], out[key + "weight_scale_2"] = q, sf.view(torch.uint8), ts
+        out[key + "bias"] = one._randn((shape[0],), layer, name + "_b", cfg.weight_std)
+
+    for i in range(cfg.n_double):
+        for s in ("img", "txt"):
+            layer = 1000 + 2 * i + (s == "txt")
+            out[f"{layer}.mod_w"] = one._randn((6 * h, h), layer, "mod_w", cfg.weight_std)
+            out[f"{layer}.mod_b"] = one._randn((6 * h,), layer, "mod_b", cfg.weight_std)
+            for name, shape in (("qkv", (3 * h, h)), ("proj", (h, h)), ("up", (m, h)), ("down", (h, m))):
+                put(layer, name, shape)
+    for i in range(cfg.n_single):
+        layer = 5000 + i
+        out[f"{layer}.mod_w"] = one._randn((3 * h, h), layer, "mod_w", cfg.weight_std)
+        out[f"{layer}.mod_b"] = one._randn((3 * h,), layer, "mod_b", cfg.weight_std)
+        put(layer, "linear1", (3 * h + m, h))
+        put(layer, "linear2", (h, h + m))
+    return out
 
 
 def gemm_flops_per_forward(cfg: DiTConfig) -> float:

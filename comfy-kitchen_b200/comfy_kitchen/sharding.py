@@ -112,3 +112,46 @@ def shard_linear_state(state: dict, prefix: str, parallel: str, rank: int, world
         elif rank != 0:
             bias = None
     return {"weight": shard, "bias": bias, "input_scale": state.get(prefix + "input_scale")}
+
+
+def take_ranges(qt: QuantizedTensor, dim: int, ranges) -> QuantizedTensor:
+    """Concatenation, along ``dim``, of several [lo, hi) ranges of a 2-D NVFP4 / MXFP8 QuantizedTensor
+    (0 = rows, 1 = columns).  Every range starts and ends on a scale-tile boundary (128 rows; 64 NVFP4 or 128
+    MXFP8 columns), so the result is assembled from whole tiles of codes and scales: a rank's heads of a fused
+    q | k | v weight, or its attention and MLP columns of a fused second linear, without re-quantizing."""
+    name = qt._layout_cls
+    if name not in _FORMATS:
+        raise ValueError(f"take_ranges: unsupported layout {name}")
+    block, per_byte = _FORMATS[name]
+    params = qt._params
+    if getattr(params, "transposed", False):
+        raise ValueError("take_ranges: slice the stored (untransposed) weight")
+    n, k = params.orig_shape
+    unit = 128 if dim == 0 else 4 * block
+    size = (n, k)[dim]
+    scale_field = "block_scale" if hasattr(params, "block_scale") else "scale"
+    qdata, scales = qt._qdata, getattr(params, scale_field)
+    qs, ss, total = [], [], 0
+    for lo, hi in ranges:
+        if not (0 <= lo < hi <= size) or lo % unit or hi % unit:
+            raise ValueError(f"range {lo}:{hi} along dim {dim} must lie in 0:{size} on multiples of {unit}")
+        if dim == 0:
+            qs.append(qdata[lo:hi])
+            ss.append(slice_tiled_scales(scales, (lo, hi), (0, scales.shape[1])))
+        else:
+            qs.append(qdata[:, lo // per_byte:hi // per_byte])
+            ss.append(slice_tiled_scales(scales, (0, scales.shape[0]), (lo // block, hi // block)))
+        total += hi - lo
+    q = torch.cat(qs, dim=dim).contiguous()
+    if dim == 0:
+        s = torch.cat([t.view(torch.uint8) for t in ss], dim=0)      # whole 128-row tiles stack along the rows
+        shape = (total, k)
+    else:
+        # tiles of one row block are contiguous along the scale columns: interleave per row block
+        parts = [t.view(torch.uint8).reshape(t.shape[0] // 128, t.shape[1] // 4, 512) for t in ss]
+        tiles = torch.cat(parts, dim=1)
+        s = tiles.reshape(tiles.shape[0] * 128, tiles.shape[1] * 4)
+        shape = (n, total)
+    fields = {f: getattr(params, f) for f in params.__dataclass_fields__}
+    fields.update({scale_field: s.contiguous().view(scales.dtype), "orig_shape": shape})
+    return QuantizedTensor(q, name, type(params)(**fields))

@@ -10,9 +10,12 @@ residual into every rank's buffer:
     ex.exchange(gate0, gate1, split_row)     # ex.residual += gate * sum_over_ranks(partial), on every rank
 
 Buffers: each rank allocates one block holding [partial | residual | flag pad] and maps the other ranks'
-blocks into its address space, through torch's symmetric memory when that is available and otherwise
-through CUDA IPC handles of an ordinary allocation (exchanged over the process group).  Nothing here is
-NCCL; the process group is used for the one-time handle exchange and for host-side barriers only.
+blocks into its address space through torch's symmetric memory (virtual-memory handles exchanged over the
+group's store, every peer's block mapped for this rank's device).  A mapping through torch's storage-sharing
+IPC handles is deliberately not offered: such a storage is opened in the owning device's context, and a
+kernel on another device may only touch it once peer access between the two devices is enabled in this
+process, which nothing on that route guarantees.  Nothing here is NCCL; the process group is used for the
+one-time rendezvous and for host-side barriers only.
 """
 from __future__ import annotations
 
@@ -51,20 +54,13 @@ class PeerExchange:
         mode = mode or os.environ.get("CK_TP_PEER_MEMORY", "auto")
         self._keep = []          # objects that own the mappings
         bases = None
-        errors = []
         if self.world == 1:
             self._block = torch.zeros(total, dtype=torch.uint8, device=self.device)
             bases, self.mode = [self._block.data_ptr()], "local"
         else:
-            for m in (("symm", "ipc") if mode == "auto" else (mode,)):
-                try:
-                    bases = self._map_symmetric(total) if m == "symm" else self._map_ipc(total)
-                    self.mode = m
-                    break
-                except Exception as e:  # fall through to the next way of sharing memory
-                    errors.append(f"{m}: {type(e).__name__}: {e}")
-            if bases is None:
-                raise RuntimeError("no way to share device memory between the ranks: " + "; ".join(errors))
+            if mode not in ("auto", "symm"):
+                raise ValueError(f"unknown peer memory mode {mode!r} (only torch symmetric memory is supported)")
+            bases, self.mode = self._map_symmetric(total), "symm"
         self._block.zero_()
         torch.cuda.synchronize(self.device)
         if self.world > 1:
@@ -89,23 +85,6 @@ class PeerExchange:
         self._keep.append(handle)
         ptrs = [int(p) for p in handle.buffer_ptrs]
         assert len(ptrs) == self.world and ptrs[self.rank] == self._block.data_ptr()
-        return ptrs
-
-    def _map_ipc(self, total: int):
-        # an allocation of its own (large enough that the caching allocator gives it a private segment)
-        self._block = torch.empty(max(total, 32 << 20), dtype=torch.uint8, device=self.device)
-        storage = self._block.untyped_storage()
-        meta = storage._share_cuda_()
-        gathered = [None] * self.world
-        self._dist.all_gather_object(gathered, (self.rank, meta), group=self.group)
-        ptrs = []
-        for r, m in sorted(gathered, key=lambda t: t[0]):
-            if r == self.rank:
-                ptrs.append(self._block.data_ptr())
-                continue
-            peer = torch.UntypedStorage._new_shared_cuda(*m)
-            self._keep.append(peer)
-            ptrs.append(peer.data_ptr())
         return ptrs
 
     # ---- the exchange

@@ -122,7 +122,10 @@ __device__ __forceinline__ uint32_t pack2<__half>(float a, float b) {
     return *reinterpret_cast<const uint32_t*>(&v);
 }
 
-template <typename T>
+// kWorld > 0: the rank count is known at compile time (2, 4, 8: the loops over ranks unroll and kUnroll is
+// chosen so that a thread keeps (kWorld + 1) * kUnroll 16-byte loads in flight within ~100 registers);
+// kWorld = 0: any rank count up to kMaxRanks.
+template <typename T, int kWorld, int kUnroll>
 __global__ void __launch_bounds__(kThreads)
 tp_exchange_kernel(const ExchangeParams p) {
     __shared__ uint32_t s_epoch;
@@ -130,25 +133,26 @@ tp_exchange_kernel(const ExchangeParams p) {
     if (threadIdx.x == 0) s_epoch = *pad_epoch(my_pad, blockIdx.x) + 1u;
     __syncthreads();
     const uint32_t epoch = s_epoch;
+    const int world = kWorld > 0 ? kWorld : p.world;
+    constexpr int kRanks = kWorld > 0 ? kWorld : kMaxRanks;
 
     block_barrier(p, false, epoch);   // every rank's partial result is complete
 
     // this rank's slice, and this block's part of it
-    const int64_t lo = p.total_vec * p.rank / p.world, hi = p.total_vec * (p.rank + 1) / p.world;
+    const int64_t lo = p.total_vec * p.rank / world, hi = p.total_vec * (p.rank + 1) / world;
     const int64_t per_block = (hi - lo + gridDim.x - 1) / gridDim.x;
     const int64_t b0 = lo + per_block * blockIdx.x;
     const int64_t b1 = b0 + per_block < hi ? b0 + per_block : hi;
-    constexpr int kUnroll = 2;
     for (int64_t base = b0 + threadIdx.x; base < b1; base += (int64_t)kThreads * kUnroll) {
-        uint4 part[kUnroll][kMaxRanks];
+        uint4 part[kUnroll][kRanks];
         uint4 xv[kUnroll];
 #pragma unroll
         for (int u = 0; u < kUnroll; ++u) {
             const int64_t idx = base + (int64_t)u * kThreads;
             if (idx < b1) {
 #pragma unroll
-                for (int i = 0; i < kMaxRanks; ++i)
-                    if (i < p.world) part[u][i] = ld_cg(p.partial[i] + idx);
+                for (int i = 0; i < kRanks; ++i)
+                    if (i < world) part[u][i] = ld_cg(p.partial[i] + idx);
                 xv[u] = ld_cg(p.residual[p.rank] + idx);
             }
         }
@@ -160,8 +164,8 @@ tp_exchange_kernel(const ExchangeParams p) {
 #pragma unroll
             for (int j = 0; j < 8; ++j) sum[j] = 0.0f;
 #pragma unroll
-            for (int i = 0; i < kMaxRanks; ++i) {
-                if (i < p.world) {
+            for (int i = 0; i < kRanks; ++i) {
+                if (i < world) {
                     float f[8];
                     unpack8<T>(part[u][i], f);
 #pragma unroll
@@ -183,13 +187,24 @@ tp_exchange_kernel(const ExchangeParams p) {
             }
             const uint4 out = make_uint4(w[0], w[1], w[2], w[3]);
 #pragma unroll
-            for (int i = 0; i < kMaxRanks; ++i)
-                if (i < p.world) p.residual[i][idx] = out;
+            for (int i = 0; i < kRanks; ++i)
+                if (i < world) p.residual[i][idx] = out;
         }
     }
     __threadfence_system();           // this thread's pushes are visible system-wide before the block signals
     block_barrier(p, true, epoch);    // every peer has finished pushing its slice into my residual buffer
     if (threadIdx.x == 0) *pad_epoch(my_pad, blockIdx.x) = epoch;
+}
+
+template <typename T>
+void launch_exchange(const ExchangeParams& p, int blocks, cudaStream_t stream) {
+    switch (p.world) {
+    case 1: tp_exchange_kernel<T, 1, 8><<<blocks, kThreads, 0, stream>>>(p); break;
+    case 2: tp_exchange_kernel<T, 2, 6><<<blocks, kThreads, 0, stream>>>(p); break;
+    case 4: tp_exchange_kernel<T, 4, 4><<<blocks, kThreads, 0, stream>>>(p); break;
+    case 8: tp_exchange_kernel<T, 8, 2><<<blocks, kThreads, 0, stream>>>(p); break;
+    default: tp_exchange_kernel<T, 0, 2><<<blocks, kThreads, 0, stream>>>(p); break;
+    }
 }
 
 }  // namespace
@@ -229,8 +244,8 @@ extern "C" int launch_tp_exchange_kernel(const void* const* partials, void* cons
     p.world = world;
     if (blocks <= 0) blocks = 148;   // one per SM: 114 registers x 512 threads leave room for one block per SM
     if (blocks > kMaxBlocks) blocks = kMaxBlocks;
-    if (dtype_code == CK_BF16) tp_exchange_kernel<__nv_bfloat16><<<blocks, kThreads, 0, stream>>>(p);
-    else tp_exchange_kernel<__half><<<blocks, kThreads, 0, stream>>>(p);
+    if (dtype_code == CK_BF16) launch_exchange<__nv_bfloat16>(p, blocks, stream);
+    else launch_exchange<__half>(p, blocks, stream);
     return launch_status("tp_exchange");
 }
 

@@ -199,7 +199,7 @@ int ck_norm_device_status(void);
  * then an elementwise kernel:  x <- x + gate * (sum over ranks of partial), on every rank, in one
  * kernel over NVLink peer memory.  Every rank launches it with the same arguments but its own `rank`.
  * partials / residuals / pads: HOST arrays of `world` device pointers, entry i being rank i's buffer
- * as mapped into this process (peer-accessible memory: CUDA IPC or symmetric memory); partial and
+ * as mapped into this process (memory mapped for this device: CUDA virtual-memory handles, i.e. symmetric memory); partial and
  * residual are [rows, cols] of the 16-bit dtype; a pad is ck_tp_pad_bytes() bytes, zeroed once before
  * first use, written by the kernel only.  Rows below split_row use gate0, the others gate1 (each [cols];
  * gate1 NULL = gate0 for all).  blocks: grid size, the same on every rank (0 = default).  All ranks'

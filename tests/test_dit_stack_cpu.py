@@ -163,3 +163,33 @@ def test_single_rank_stack_inside_a_process_group_does_not_wait_for_peers():
         assert p.exitcode == 0
     assert world == 1 and heads_local == cfg.heads
     assert torch.equal(y, want)
+
+
+@pytest.mark.parametrize("world", [1, 2])
+def test_stack_from_checkpoint_equals_stack_built_directly(world):
+    """Every rank's shards cut out of a whole-model checkpoint (reference key contract) are byte-identical to the
+    shards the stack quantizes itself after slicing, and the forward agrees bit for bit."""
+    from comfy_kitchen.dit_stack import make_checkpoint
+    from tests import dit_oracle_ops as ops
+
+    cfg = DiTConfig(**TINY)
+    ckpt = make_checkpoint(cfg, "cpu", ops)
+    assert {"1000.qkv.weight", "1000.qkv.weight_scale", "1000.qkv.weight_scale_2", "1000.qkv.bias", "5000.linear2.weight",
+            "1001.mod_w"} <= set(ckpt)
+    assert ckpt["1000.qkv.weight"].dtype == torch.uint8 and ckpt["1000.qkv.weight_scale"].dtype == torch.uint8
+    for rank in range(world):
+        tp = TensorParallel(single=True)
+        tp.rank, tp.world = rank, world      # weights only: no collective is entered
+        direct = DiTStack(cfg, "cpu", tp=tp, ops=ops)
+        loaded = DiTStack(cfg, "cpu", tp=tp, ops=ops, state=ckpt)
+        pairs = [(direct.double[0][s][n], loaded.double[0][s][n]) for s in ("img", "txt") for n in ("qkv", "proj", "up", "down")]
+        pairs += [(direct.single[0][n], loaded.single[0][n]) for n in ("linear1", "linear2")]
+        for a, b in pairs:
+            assert torch.equal(a.qdata, b.qdata)
+            assert torch.equal(a.block_scales.view(torch.uint8), b.block_scales.view(torch.uint8))
+            assert torch.equal(a.tensor_scale, b.tensor_scale)
+            assert (a.bias is None) == (b.bias is None) and (a.bias is None or torch.equal(a.bias, b.bias))
+        assert torch.equal(direct.mod_w, loaded.mod_w)
+        if world == 1:
+            img, txt, vec = _inputs(cfg)
+            assert torch.equal(direct.forward(img, txt, vec), loaded.forward(img, txt, vec))

