@@ -592,7 +592,8 @@ class DiTStack:
 
         if self.exchange is not None:
             per = timed(lambda: self.exchange.exchange(gate))
-            what = "fused all-reduce + residual kernel over peer memory (" + self.exchange.mode + ")"
+            what = ("fused all-reduce + residual kernel, " +
+                    ("NVLink-switch reduction and broadcast (multimem)" if self.exchange.multimem else "peer loads and stores"))
         else:
             y = torch.zeros_like(x)
 

@@ -72,6 +72,15 @@ class PeerExchange:
         self._partials = arr(*[b + self._offsets[0] for b in bases])
         self._residuals = arr(*[b + self._offsets[1] for b in bases])
         self._pads = arr(*[b + self._offsets[2] for b in bases])
+        # NVLink-switch multicast address of the block, when the symmetric allocation has one (0 = none)
+        mc = int(getattr(self, "_multicast_base", 0) or 0)
+        # Off unless asked for (CK_TP_MULTIMEM=1): measured on 8 B200s the switch path takes the same 107 us per
+        # 28 MB exchange as plain peer loads and stores, and on 2 it is slower (101 against 64 us).
+        if os.environ.get("CK_TP_MULTIMEM", "0") != "1":
+            mc = 0
+        self.multimem = mc != 0
+        self._mc_partial = ctypes.c_void_p(mc + self._offsets[0] if mc else 0)
+        self._mc_residual = ctypes.c_void_p(mc + self._offsets[1] if mc else 0)
         self.calls = 0
 
     # ---- ways of making one allocation per rank visible to all ranks
@@ -83,6 +92,7 @@ class PeerExchange:
         group = self.group if self.group is not None else self._dist.group.WORLD
         handle = symm_mem.rendezvous(self._block, group)
         self._keep.append(handle)
+        self._multicast_base = int(getattr(handle, "multicast_ptr", 0) or 0)
         ptrs = [int(p) for p in handle.buffer_ptrs]
         assert len(ptrs) == self.world and ptrs[self.rank] == self._block.data_ptr()
         return ptrs
@@ -99,7 +109,8 @@ class PeerExchange:
             g1 = gate1.reshape(-1)
             assert g1.numel() == self.cols and g1.dtype == self.dtype and g1.is_contiguous()
         code = 2 if self.dtype == torch.bfloat16 else 1
-        _native.call("launch_tp_exchange_kernel", self._partials, self._residuals, self._pads, self.world, self.rank,
+        _native.call("launch_tp_exchange_kernel", self._partials, self._residuals, self._pads, self._mc_partial,
+                     self._mc_residual, self.world, self.rank,
                      ctypes.c_void_p(g0.data_ptr()), ctypes.c_void_p(0 if g1 is None else g1.data_ptr()),
                      int(split_row), self.rows, self.cols, code, int(blocks),
                      ctypes.c_void_p(torch.cuda.current_stream(self.device).cuda_stream))

@@ -39,6 +39,8 @@ struct ExchangeParams {
     const uint4* partial[kMaxRanks];
     uint4* residual[kMaxRanks];
     uint32_t* pad[kMaxRanks];     // each rank's flag pad: start[kMaxBlocks][kMaxRanks], end[...], then epoch[kMaxBlocks]
+    const uint4* mc_partial;      // multicast (NVLS) address of the partial buffers, or null
+    uint4* mc_residual;           // multicast address of the residual buffers, or null
     const void* gate0;
     const void* gate1;
     int64_t split_vec;            // vectors (of 8 elements) before this index use gate0, the rest gate1
@@ -70,6 +72,25 @@ __device__ __forceinline__ uint4 ld_cg(const uint4* p) {
     uint4 v;
     asm volatile("ld.global.cg.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
     return v;
+}
+
+// NVLink-switch reduction: one load returns the sum over all ranks of the 8 values at this multicast address,
+// accumulated in fp32 inside the switch and rounded once to the 16-bit type.
+template <typename T>
+__device__ __forceinline__ uint4 multimem_ld_reduce(const uint4* mc) {
+    uint4 v;
+    if (Elem<T>::code == CK_BF16)
+        asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
+                     : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(mc) : "memory");
+    else
+        asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.f16x2 {%0, %1, %2, %3}, [%4];"
+                     : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(mc) : "memory");
+    return v;
+}
+// One store that the switch delivers to every rank's copy of the buffer.
+__device__ __forceinline__ void multimem_st(uint4* mc, const uint4& v) {
+    asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};"
+                 ::"l"(mc), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
 }
 
 // Threads 0 .. world-1 of the block: signal peer `threadIdx.x`, then wait for its signal.
@@ -196,8 +217,64 @@ tp_exchange_kernel(const ExchangeParams p) {
     if (threadIdx.x == 0) *pad_epoch(my_pad, blockIdx.x) = epoch;
 }
 
+// The same exchange through the NVLink switch: the reduction happens in the switch (multimem.ld_reduce: this
+// rank receives only its slice, already summed) and the updated slice is broadcast by the switch
+// (multimem.st), so each GPU's links carry 1 / world of the matrix in each direction instead of
+// (world - 1) / world.  The sum's accumulation order inside the switch is not specified; it is fp32 with one
+// rounding, computed once per element by the slice's owner, so all ranks still end with identical bits.
+template <typename T>
+__global__ void __launch_bounds__(kThreads)
+tp_exchange_multimem_kernel(const ExchangeParams p) {
+    __shared__ uint32_t s_epoch;
+    uint32_t* my_pad = p.pad[p.rank];
+    if (threadIdx.x == 0) s_epoch = *pad_epoch(my_pad, blockIdx.x) + 1u;
+    __syncthreads();
+    const uint32_t epoch = s_epoch;
+    block_barrier(p, false, epoch);
+
+    const int64_t lo = p.total_vec * p.rank / p.world, hi = p.total_vec * (p.rank + 1) / p.world;
+    const int64_t per_block = (hi - lo + gridDim.x - 1) / gridDim.x;
+    const int64_t b0 = lo + per_block * blockIdx.x;
+    const int64_t b1 = b0 + per_block < hi ? b0 + per_block : hi;
+    constexpr int kUnroll = 4;
+    for (int64_t base = b0 + threadIdx.x; base < b1; base += (int64_t)kThreads * kUnroll) {
+        uint4 yv[kUnroll], xv[kUnroll];
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u) {
+            const int64_t idx = base + (int64_t)u * kThreads;
+            if (idx < b1) {
+                yv[u] = multimem_ld_reduce<T>(p.mc_partial + idx);
+                xv[u] = ld_cg(p.residual[p.rank] + idx);
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u) {
+            const int64_t idx = base + (int64_t)u * kThreads;
+            if (idx >= b1) continue;
+            const int col_vec = (int)(idx % p.vec_per_row);
+            const uint4* gate = reinterpret_cast<const uint4*>(idx < p.split_vec ? p.gate0 : p.gate1) + col_vec;
+            float g[8], x[8], y[8];
+            unpack8<T>(__ldg(gate), g);
+            unpack8<T>(xv[u], x);
+            unpack8<T>(yv[u], y);
+            uint32_t w[4];
+#pragma unroll
+            for (int j = 0; j < 8; j += 2)
+                w[j >> 1] = pack2<T>(__fadd_rn(x[j], __fmul_rn(g[j], y[j])), __fadd_rn(x[j + 1], __fmul_rn(g[j + 1], y[j + 1])));
+            multimem_st(p.mc_residual + idx, make_uint4(w[0], w[1], w[2], w[3]));
+        }
+    }
+    __threadfence_system();
+    block_barrier(p, true, epoch);
+    if (threadIdx.x == 0) *pad_epoch(my_pad, blockIdx.x) = epoch;
+}
+
 template <typename T>
 void launch_exchange(const ExchangeParams& p, int blocks, cudaStream_t stream) {
+    if (p.mc_partial != nullptr && p.world > 1) {
+        tp_exchange_multimem_kernel<T><<<blocks, kThreads, 0, stream>>>(p);
+        return;
+    }
     switch (p.world) {
     case 1: tp_exchange_kernel<T, 1, 8><<<blocks, kThreads, 0, stream>>>(p); break;
     case 2: tp_exchange_kernel<T, 2, 6><<<blocks, kThreads, 0, stream>>>(p); break;
@@ -214,7 +291,8 @@ extern "C" int64_t ck_tp_pad_bytes(void) {
     return (int64_t)sizeof(uint32_t) * (2 * ck::kMaxBlocks * ck::kMaxRanks + ck::kMaxBlocks);
 }
 
-extern "C" int launch_tp_exchange_kernel(const void* const* partials, void* const* residuals, void* const* pads, int world,
+extern "C" int launch_tp_exchange_kernel(const void* const* partials, void* const* residuals, void* const* pads,
+                                         const void* mc_partial, void* mc_residual, int world,
                                          int rank, const void* gate0, const void* gate1, int64_t split_row, int64_t rows,
                                          int64_t cols, int dtype_code, int blocks, cudaStream_t stream) {
     using namespace ck;
@@ -234,6 +312,10 @@ extern "C" int launch_tp_exchange_kernel(const void* const* partials, void* cons
         p.pad[i] = static_cast<uint32_t*>(pads[i]);
     }
     if (!aligned16(gate0) || (gate1 && !aligned16(gate1))) CK_FAIL(CK_ERR_ALIGN, "tp_exchange: gates must be 16-byte aligned");
+    if ((mc_partial == nullptr) != (mc_residual == nullptr)) CK_FAIL(CK_ERR_NULL, "tp_exchange: the two multicast addresses go together");
+    if (mc_partial && (!aligned16(mc_partial) || !aligned16(mc_residual))) CK_FAIL(CK_ERR_ALIGN, "tp_exchange: multicast addresses must be 16-byte aligned");
+    p.mc_partial = static_cast<const uint4*>(mc_partial);
+    p.mc_residual = static_cast<uint4*>(mc_residual);
     p.gate0 = gate0;
     p.gate1 = gate1 ? gate1 : gate0;
     p.vec_per_row = (int)(cols / 8);

@@ -202,11 +202,14 @@ int ck_norm_device_status(void);
  * as mapped into this process (memory mapped for this device: CUDA virtual-memory handles, i.e. symmetric memory); partial and
  * residual are [rows, cols] of the 16-bit dtype; a pad is ck_tp_pad_bytes() bytes, zeroed once before
  * first use, written by the kernel only.  Rows below split_row use gate0, the others gate1 (each [cols];
- * gate1 NULL = gate0 for all).  blocks: grid size, the same on every rank (0 = default).  All ranks'
+ * gate1 NULL = gate0 for all).  mc_partial / mc_residual: the NVLink-switch multicast addresses of the same
+ * two buffers (both or neither; NULL = plain peer loads and stores): with them the sum is formed inside the
+ * switch (multimem.ld_reduce, fp32 accumulation, one rounding) and the result is broadcast by it (multimem.st).
+ * blocks: grid size, the same on every rank (0 = default).  All ranks'
  * residual buffers end bit-identical.  Waits for peers are bounded (seconds); see ck_tp_device_status. */
 int64_t ck_tp_pad_bytes(void);
-int launch_tp_exchange_kernel(const void* const* partials, void* const* residuals, void* const* pads, int world,
-                              int rank, const void* gate0, const void* gate1, int64_t split_row, int64_t rows,
+int launch_tp_exchange_kernel(const void* const* partials, void* const* residuals, void* const* pads,
+                              const void* mc_partial, void* mc_residual, int world, int rank, const void* gate0, const void* gate1, int64_t split_row, int64_t rows,
                               int64_t cols, int dtype_code, int blocks, ck_stream_t stream);
 /* Synchronises the device, reads and clears the exchange kernel's status word: 0, or
  * CK_ERR_DEVICE_TIMEOUT when a wait for a peer ran out since the last call. */

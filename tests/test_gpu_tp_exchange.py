@@ -60,9 +60,9 @@ def test_argument_errors():
     lib = _native.load()
     assert lib.ck_tp_pad_bytes() >= 4 * (2 * 512 * 8 + 512)
     arr = (ctypes.c_void_p * 1)(0)
-    rc = lib.launch_tp_exchange_kernel(arr, arr, arr, 1, 0, None, None, 0, 16, 64, 2, 0, None)
+    rc = lib.launch_tp_exchange_kernel(arr, arr, arr, None, None, 1, 0, None, None, 0, 16, 64, 2, 0, None)
     assert rc == -4
-    rc = lib.launch_tp_exchange_kernel(arr, arr, arr, 9, 0, ctypes.c_void_p(256), None, 0, 16, 64, 2, 0, None)
+    rc = lib.launch_tp_exchange_kernel(arr, arr, arr, None, None, 9, 0, ctypes.c_void_p(256), None, 0, 16, 64, 2, 0, None)
     assert rc == -2 and b"ranks" in lib.ck_last_error()
 
 

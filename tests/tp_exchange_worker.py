@@ -20,17 +20,13 @@ def main() -> None:
     from comfy_kitchen.dit_stack import DiTConfig, DiTStack, TensorParallel
     from comfy_kitchen.tp_exchange import PeerExchange
 
-    # ---- the kernel against an all-gather + fp32 sum + addcmul
+    # ---- the kernel against an all-gather + fp32 sum + addcmul: plain peer loads, then the NVLink-switch path
     rows, cols, split = 1000, 3072, 256
-    for mode in ("symm",):
-        try:
-            ex = PeerExchange(None, dev, rows, cols, torch.bfloat16, mode=mode)
-            ok = torch.ones(1, device=dev)
-        except Exception as e:  # noqa: BLE001
-            print(f"[rank {rank}] peer memory mode {mode} unavailable: {type(e).__name__}: {e}", flush=True)
-            ex, ok = None, torch.zeros(1, device=dev)
-        dist.all_reduce(ok, op=dist.ReduceOp.MIN)
-        if ok.item() < 1:
+    for multimem in ("0", "1"):
+        os.environ["CK_TP_MULTIMEM"] = multimem
+        ex = PeerExchange(None, dev, rows, cols, torch.bfloat16)
+        if multimem == "1" and not ex.multimem:
+            print(f"[rank {rank}] no multicast address on this allocation: switch path not exercised", flush=True)
             continue
         g = torch.Generator(device=dev).manual_seed(100 + rank)
         gs = torch.Generator(device=dev).manual_seed(7)      # the same on every rank
@@ -38,6 +34,8 @@ def main() -> None:
         g0 = torch.randn(cols, device=dev, generator=gs).bfloat16()
         g1 = torch.randn(cols, device=dev, generator=gs).bfloat16()
         ex.residual.copy_(x0)
+        torch.cuda.synchronize()
+        dist.barrier()
         want = x0.clone()
         for it in range(3):
             part = torch.randn(rows, cols, device=dev, generator=g).bfloat16()
@@ -52,15 +50,24 @@ def main() -> None:
             y = s.bfloat16()
             want[:split] = torch.addcmul(want[:split], g0, y[:split])
             want[split:] = torch.addcmul(want[split:], g1, y[split:])
-            assert torch.equal(ex.residual, want), f"rank {rank} mode {mode} call {it}: residual differs"
+            if not ex.multimem:
+                assert torch.equal(ex.residual, want), f"rank {rank} call {it}: residual differs"
+            else:
+                # the switch adds in an order of its own: the fp32 sum may differ in its last bits, hence the bf16
+                # value of y in rare elements by one step
+                diff = (ex.residual.float() - want.float()).abs()
+                assert diff.max() <= 2.0 ** -6 * want.float().abs().max(), f"rank {rank} call {it}: {diff.max().item()}"
+                assert (diff > 0).float().mean() < 0.02
+                want = ex.residual.clone()
         # all ranks hold the same bits
         mine = ex.residual.clone()
         ref = mine.clone()
         dist.broadcast(ref, 0)
         assert torch.equal(mine, ref)
         assert ex.status() == 0
-        print(f"[rank {rank}] exchange kernel ok with peer memory mode {mode}", flush=True)
+        print(f"[rank {rank}] exchange kernel ok ({'NVLink-switch multimem' if ex.multimem else 'peer loads'})", flush=True)
         del ex
+    os.environ.pop("CK_TP_MULTIMEM", None)
 
     # ---- the stack: peer-exchange forward (eager and one graph) against the NCCL forward
     cfg = DiTConfig(n_double=2, n_single=2, txt_tokens=128, img_grid=(16, 24))
