@@ -25,6 +25,7 @@ SIGNATURES: dict[str, list] = {
     "ck_norm_device_status": [],
     "ck_set_option": [c_char_p, I],
     "ck_tp_device_status": [],
+    "launch_tp_exchange_noalloc_kernel": [P, P, P, P, I64, I64, I64, I, I, P],
     "launch_tp_exchange_kernel": [P, P, P, P, P, I, I, P, P, I64, I64, I64, I, I, P],
     "launch_quantize_fp8_kernel": [P, P, P, I64, I, I, P],
     "launch_dequantize_fp8_kernel": [P, P, P, I64, I, I, P],

@@ -331,6 +331,53 @@ extern "C" int launch_tp_exchange_kernel(const void* const* partials, void* cons
     return launch_status("tp_exchange");
 }
 
+// ---------------------------------------------------------------------------------------------------
+// Allocation-free variant for a single rank.
+//
+// Some hosts of this library cannot allocate device memory when they call it: an inference runtime that
+// hands out one fixed arena at start-up and forbids cudaMalloc afterwards, or a plugin running inside
+// someone else's stream-ordered pipeline where an allocation would synchronise the device.  The exchange
+// kernel needs a flag pad besides its inputs and outputs; this entry point keeps that pad in a
+// file-scope device array instead of taking it from the caller, for the one-rank case (no peers to map
+// it for): residual <- residual + gate * partial.
+//
+// Limits and rules:
+//   - the pad serves at most kMaxBlocks (512) blocks: a larger `blocks` is refused (CK_ERR_SHAPE);
+//     it occupies 34 816 bytes on every GPU that loads the library, until the process exits;
+//   - the first call on a device looks the array's device address up (cudaGetSymbolAddress, with that
+//     device current) and remembers it; make that first call outside any stream capture;
+//   - all calls on a device share the pad, which keeps the epochs the previous call left: nothing needs
+//     clearing (the kernel only ever compares against "the epoch I am about to write"), but two calls
+//     that overlap on the GPU (different streams) race on it -- keep them on one stream;
+//   - nothing here calls cudaMalloc, cudaFree or any allocating routine.
+static __device__ __align__(256) uint32_t g_noalloc_pad[2 * ck::kMaxBlocks * ck::kMaxRanks + ck::kMaxBlocks];
+
+extern "C" int launch_tp_exchange_noalloc_kernel(const void* partial, void* residual, const void* gate0, const void* gate1,
+                                                 int64_t split_row, int64_t rows, int64_t cols, int dtype_code, int blocks,
+                                                 cudaStream_t stream) {
+    using namespace ck;
+    if (blocks > kMaxBlocks)
+        CK_FAIL(CK_ERR_SHAPE, "tp_exchange_noalloc: %d blocks asked for, the built-in flag pad serves at most %d", blocks, kMaxBlocks);
+    // In host code the array's name is only a handle: the kernel needs its device address, per device.
+    static uint32_t* pad_of_device[64] = {};
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) CK_FAIL((int)e, "tp_exchange_noalloc: cudaGetDevice: %s", cudaGetErrorString(e));
+    if (dev < 0 || dev >= 64) CK_FAIL(CK_ERR_UNSUPPORTED, "tp_exchange_noalloc: device index %d out of range", dev);
+    if (pad_of_device[dev] == nullptr) {
+        void* p = nullptr;
+        e = cudaGetSymbolAddress(&p, g_noalloc_pad);
+        if (e != cudaSuccess || p == nullptr)
+            CK_FAIL(e != cudaSuccess ? (int)e : CK_ERR_UNSUPPORTED, "tp_exchange_noalloc: cudaGetSymbolAddress: %s", cudaGetErrorString(e));
+        pad_of_device[dev] = static_cast<uint32_t*>(p);
+    }
+    const void* partials[1] = {partial};
+    void* residuals[1] = {residual};
+    void* pads[1] = {pad_of_device[dev]};
+    return launch_tp_exchange_kernel(partials, residuals, pads, nullptr, nullptr, 1, 0, gate0, gate1, split_row, rows, cols,
+                                     dtype_code, blocks, stream);
+}
+
 // Reads and clears the exchange kernel's status word (synchronises the device): 0, or
 // CK_ERR_DEVICE_TIMEOUT when a wait for a peer ran out since the last call.
 extern "C" int ck_tp_device_status(void) {

@@ -211,6 +211,15 @@ int64_t ck_tp_pad_bytes(void);
 int launch_tp_exchange_kernel(const void* const* partials, void* const* residuals, void* const* pads,
                               const void* mc_partial, void* mc_residual, int world, int rank, const void* gate0, const void* gate1, int64_t split_row, int64_t rows,
                               int64_t cols, int dtype_code, int blocks, ck_stream_t stream);
+/* No counterpart in the reference.  The one-rank exchange (residual <- residual + gate * partial) for callers
+ * that must not allocate device memory at call time -- a runtime with a fixed arena, a plugin inside a pipeline
+ * where cudaMalloc would synchronise: the flag pad the kernel needs lives in a device array inside the library
+ * (34 816 bytes per GPU, held until exit) instead of being passed in.  blocks > 512 is refused with
+ * CK_ERR_SHAPE.  The first call on a device resolves the array's address; make it outside stream capture.  All
+ * calls on a device share the pad: keep them on one stream (calls that overlap on the GPU race on it). */
+int launch_tp_exchange_noalloc_kernel(const void* partial, void* residual, const void* gate0, const void* gate1,
+                                      int64_t split_row, int64_t rows, int64_t cols, int dtype_code, int blocks,
+                                      ck_stream_t stream);
 /* Synchronises the device, reads and clears the exchange kernel's status word: 0, or
  * CK_ERR_DEVICE_TIMEOUT when a wait for a peer ran out since the last call. */
 int ck_tp_device_status(void);
