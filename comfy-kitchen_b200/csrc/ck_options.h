@@ -18,8 +18,10 @@
 //                         over the broadcast dimension (0: default)
 //   "gelu_table_min"      the gather quantizer tabulates GELU per CTA from n activated elements on
 //                         (default 16 Mi; negative: never; same bytes either way)
-//   "gemm_tile"           0: the launcher chooses the GEMM tile variant per shape; other values force
-//                         one (see gemm_blockscaled.cu)
+//   "gemm_tile"           GEMM pipeline: 0 or 1 = scale movers (default); 2 = scales moved by tcgen05.cp from
+//                         the MMA issuer, copies of both CTAs signalling the leader's barrier (1-3 % faster for
+//                         NVFP4 at K = 3072, up to 13 % for MXFP8, but the two issuers' k-tiles then reach the
+//                         tensor pipe in varying order: MXFP8 sums can differ in the last fp32 bit between runs)
 //   "gemm_map_cache"      0 disables the cache of encoded tensor maps (1: default)
 #pragma once
 

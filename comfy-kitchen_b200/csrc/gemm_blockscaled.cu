@@ -65,6 +65,7 @@ constexpr int kFirstMoverWarp = kFirstEpiWarp + kEpiWarps;
 constexpr int kSecondMmaWarp = kFirstMoverWarp + 4;   // issues the odd k-tiles; warp 1 the even ones
 constexpr int kThreads = 32 * (kSecondMmaWarp + 1);
 constexpr int kSfBufs = 3;
+constexpr bool kDefaultCp = false;   // which pipeline variant the launcher takes when not told (see launch_gemm)
 constexpr int kKbPerTile = 4;  // MMAs per k-tile
 
 constexpr int kSmemA = BM * 128;            // 16 KB
@@ -170,6 +171,22 @@ __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, i
         "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
         ::"r"(smem_u32(dst)), "l"(map), "r"(c0), "r"(c1), "r"(smem_u32(bar)) : "memory");
 }
+// Address of the same shared-memory location in CTA `rank` of the cluster (shared::cluster window).
+__device__ __forceinline__ uint32_t cluster_addr(const void* p, uint32_t rank) {
+    uint32_t a;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(a) : "r"(smem_u32(p)), "r"(rank));
+    return a;
+}
+__device__ __forceinline__ void mbar_expect_tx_cluster(uint32_t bar_cluster_addr, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cluster.b64 _, [%0], %1;" ::"r"(bar_cluster_addr), "r"(bytes) : "memory");
+}
+// Tile load whose completion is signalled on a barrier that may live in the peer CTA of the pair (no multicast:
+// the data still lands in the executing CTA's shared memory only).
+__device__ __forceinline__ void tma_load_2d_pair(void* dst, const CUtensorMap* map, int c0, int c1, uint32_t bar_cluster_addr) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(smem_u32(dst)), "l"(map), "r"(c0), "r"(c1), "r"(bar_cluster_addr) : "memory");
+}
 __device__ __forceinline__ void bulk_load(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
     asm volatile(
         "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
@@ -203,6 +220,18 @@ __device__ __forceinline__ void tc_commit_pair(uint64_t* bar) {
 //                  -> hi = SBO 64 | version 1 (bit 46) | layout SWIZZLE_128B (bits 61-63)
 constexpr uint32_t kDescHiOperand = 64u | (1u << 14) | (2u << 29);
 constexpr uint32_t kDescLoLbo1 = 1u << 16;
+
+//   scale tiles: 32 rows x 16 bytes, no swizzle, 8-row groups 128 bytes apart -> hi = SBO 8 | version 1
+constexpr uint32_t kDescHiScale = 8u | (1u << 14);
+// One 512-byte scale tile, shared memory -> TMEM columns [taddr, taddr + 4), replicated into the four 32-lane
+// quarters, in both CTAs of the pair (each from its own shared memory at the same offset).
+__device__ __forceinline__ void tc_cp_scale_pair(uint32_t taddr, uint32_t desc_lo) {
+    if (elect_one())
+    asm volatile(
+        "{ .reg .b64 d; mov.b64 d, {%1, %2};\n"
+        "tcgen05.cp.cta_group::2.32x128b.warpx4 [%0], d; }"
+        ::"r"(taddr), "r"(desc_lo), "n"(kDescHiScale) : "memory");
+}
 
 template <bool kFp4>
 __device__ __forceinline__ void tc_mma(uint32_t d, uint32_t a_lo, uint32_t b_lo, uint32_t idesc, uint32_t accumulate,
@@ -299,10 +328,17 @@ __device__ __forceinline__ uint32_t pack_pair<__half>(float a, float b) {
     return *reinterpret_cast<const uint32_t*>(&v);
 }
 
-template <bool kFp4, bool kRes>
+// kCp = false: scale movers (warps 18-21) as described at the top of the file.
+// kCp = true:  no movers.  The scale tiles arrive through tensor maps (map_sfa, map_sfb) like the operands, every
+//              copy of both CTAs signals the LEADER's full[] barrier (cp.async.bulk.tensor with .cta_group::2, no
+//              multicast), and the MMA issuer itself moves the stage's scale tiles into TMEM with tcgen05.cp
+//              (.cta_group::2: one instruction copies in both CTAs, each from its own shared memory) right before
+//              the stage's MMAs; the scale buffer in TMEM is indexed by the stage, so it is free when the stage is.
+template <bool kFp4, bool kRes, bool kCp>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
 gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                        const __grid_constant__ CUtensorMap map_out, const GemmParams p) {
+                        const __grid_constant__ CUtensorMap map_out, const __grid_constant__ CUtensorMap map_sfa,
+                        const __grid_constant__ CUtensorMap map_sfb, const GemmParams p) {
     extern __shared__ uint8_t smem_raw[];
     // 1024-byte alignment for the swizzled tiles (the same offset in both CTAs of the pair)
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -330,7 +366,7 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
     const int num_tiles = p.tiles_m * p.tiles_n;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < kStages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 5); }
+        for (int s = 0; s < kStages; ++s) { mbar_init(&full[s], kCp ? 2 : 1); mbar_init(&empty[s], kCp ? 1 : 5); }
         for (int b = 0; b < kSfBufs; ++b) mbar_init(&sf_full[b], 8);
         mbar_init(tmem_full, 2);   // one commit per tile from each MMA issuer
         mbar_init(tile_open, 1);
@@ -376,6 +412,18 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
                 const uint32_t sf_bytes = (uint32_t)n_sf * 512u;
                 const size_t sf_off = (size_t)kt * (kSfTilesPerStage * 512);
                 const uint32_t tx_bytes = kSmemA + kSmemB + sf_bytes * ((have_a ? 1 : 0) + b_tiles);
+                if constexpr (kCp) {
+                    // every box is transferred whole (zero-filled outside the tensor): a fixed byte count per stage
+                    constexpr uint32_t kSfBox = kSfTilesPerStage * 512u;
+                    const uint32_t lead_full = cluster_addr(&full[s], 0);
+                    if (elect_one()) {
+                        mbar_expect_tx_cluster(lead_full, kSmemA + kSmemB + 3u * kSfBox);
+                        tma_load_2d_pair(st, &map_a, kt * 128, tm * 256 + (int)rank * BM, lead_full);
+                        tma_load_2d_pair(st + kSmemA, &map_b, kt * 128, tn * BN + (int)rank * (BN / 2), lead_full);
+                        tma_load_2d_pair(st + kSmemA + kSmemB, &map_sfa, kt * kSfTilesPerStage * 64, row_tile_a, lead_full);
+                        tma_load_2d_pair(st + kSmemA + kSmemB + kSmemSfA, &map_sfb, kt * kSfTilesPerStage * 64, row_tile_b, lead_full);
+                    }
+                } else
                 if (elect_one()) {
                     mbar_expect_tx(&full[s], tx_bytes);
                     tma_load_2d(st, &map_a, kt * 128, tm * 256 + (int)rank * BM, &full[s]);
@@ -389,12 +437,17 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
                 __syncwarp();
             }
         }
-        // drain: every copy this warp issued must have landed before the CTA may exit
+        // drain: every copy this warp issued must have landed before the CTA may exit.  (kCp: completion is
+        // signalled in the leader only; a finished kernel has consumed every stage, and a CTA that gave up waits
+        // long enough below for copies in flight to land.)
+        if (kCp && !ok) __nanosleep(50000);
         const uint32_t first = it > (uint32_t)kStages ? it - kStages : 0;
-        for (uint32_t j = first; j < it; ++j) {
+        for (uint32_t j = (kCp && rank != 0) ? it : first; j < it; ++j) {
             const int s = j % kStages;
             (void)mbar_wait(&full[s], (j / kStages) & 1, s_abort, kTimeoutFull);
         }
+    } else if (kCp && warp >= kFirstMoverWarp && warp < kSecondMmaWarp) {
+        // (these warps have no work in this variant)
     } else if (warp >= kFirstMoverWarp && warp < kSecondMmaWarp) {
         // ------------------------------------------------------------ scale movers (smem -> registers -> TMEM)
         // A 512-byte scale tile is 32 rows x 16 bytes: row i holds, for the four 32-row groups g of a
@@ -481,10 +534,13 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
             for (int kt = 0; kt < k_tiles && ok; ++kt, ++it) {
                 if ((uint32_t)(kt & 1) != which) continue;
                 const int s = it % kStages;
-                const uint32_t sb = it % kSfBufs;
+                const uint32_t sb = kCp ? (uint32_t)s : it % kSfBufs;
                 // The movers of both CTAs publish sf_full only after they saw their full[s], so this one wait
                 // covers the operands too.  `ready` is an early look taken while the previous k-tile was issued.
-                if (!__all_sync(0xffffffffu, ready)) ok = mbar_wait(&sf_full[sb], (it / kSfBufs) & 1, s_abort, kTimeoutSfFull);
+                // (kCp: full[s] here in the leader collects the copies of both CTAs.)
+                if (!__all_sync(0xffffffffu, ready))
+                    ok = kCp ? mbar_wait(&full[s], (it / kStages) & 1, s_abort, kTimeoutFull)
+                             : mbar_wait(&sf_full[sb], (it / kSfBufs) & 1, s_abort, kTimeoutSfFull);
                 if (!ok) break;
                 tc_fence_after();
                 // every descriptor of this stage is "stage start >> 4" plus a constant (the same in both CTAs)
@@ -493,6 +549,17 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
                 const uint32_t t_sfa = tmem_base + tmem_sfa_col(sb), t_sfb = tmem_base + tmem_sfb_col(sb);
                 int n_kb = kKbPerTile;
                 if (kt + 1 == k_tiles && !tail_full) n_kb = (p.K - kt * kElemsPerTile + kMmaK - 1) / kMmaK;
+                if constexpr (kCp) {
+                    // this stage's scale tiles: shared memory -> TMEM, in both CTAs, ahead of the MMAs in the same pipe
+                    const uint32_t sfa16 = (st16 + ((kSmemA + kSmemB) >> 4)) | kDescLoLbo1;
+                    const uint32_t sfb16 = (st16 + ((kSmemA + kSmemB + kSmemSfA) >> 4)) | kDescLoLbo1;
+#pragma unroll
+                    for (int t = 0; t < kSfTilesPerStage; ++t) {
+                        tc_cp_scale_pair(t_sfa + 4 * t, sfa16 + t * 32);
+                        tc_cp_scale_pair(t_sfb + 8 * t, sfb16 + t * 32);
+                        tc_cp_scale_pair(t_sfb + 8 * t + 4, sfb16 + kSfTilesPerStage * 32 + t * 32);
+                    }
+                }
 #pragma unroll
                 for (int kb = 0; kb < kKbPerTile; ++kb) {
                     if (kb < n_kb) {
@@ -505,7 +572,8 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
                     }
                     // the pipe is busy with these for a while: look at my next k-tile's barrier now
                     if (kb == 1) ready = kt + 2 < k_tiles &&
-                                         mbar_test_wait(&sf_full[(it + 2) % kSfBufs], ((it + 2) / kSfBufs) & 1);
+                                         (kCp ? mbar_test_wait(&full[(it + 2) % kStages], ((it + 2) / kStages) & 1)
+                                              : mbar_test_wait(&sf_full[(it + 2) % kSfBufs], ((it + 2) / kSfBufs) & 1));
                 }
                 tc_commit_pair(&empty[s]);                      // stage and scale buffer reusable once these MMAs are done
             }
@@ -723,6 +791,22 @@ struct MapKeyHash {
         return (size_t)(h ^ (h >> 29));
     }
 };
+// Tiled scale buffer as a 2-D tensor: one row per 128-row scale tile row, tiles_k * 512 bytes long (64-bit
+// elements, so that a box can span four 512-byte tiles); box = box_tiles tiles x box_rows tile rows, no swizzle.
+int make_scale_map(CUtensorMap* map, const void* base, int64_t row_tiles, int64_t tiles_k, int box_tiles, int box_rows) {
+    EncodeFn enc = get_encode();
+    if (!enc) CK_FAIL(CK_ERR_UNSUPPORTED, "scaled_mm: cuTensorMapEncodeTiled is not available from the driver");
+    cuuint64_t dims[2] = {(cuuint64_t)tiles_k * 64u, (cuuint64_t)row_tiles};
+    cuuint64_t strides[1] = {(cuuint64_t)tiles_k * 512u};
+    cuuint32_t box[2] = {(cuuint32_t)box_tiles * 64u, (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1u, 1u};
+    CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT64, 2, const_cast<void*>(base), dims, strides, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) CK_FAIL(CK_ERR_UNSUPPORTED, "scaled_mm: cuTensorMapEncodeTiled (scales) failed with %d", (int)r);
+    return CK_OK;
+}
+
 int cached_map(CUtensorMap* map, const void* base, int64_t rows, int64_t cols, int kind) {
     static std::mutex mu;
     static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
@@ -732,8 +816,10 @@ int cached_map(CUtensorMap* map, const void* base, int64_t rows, int64_t cols, i
         auto it = cache.find(key);
         if (it != cache.end()) { *map = it->second; return CK_OK; }
     }
-    const int rc = kind > 0 ? make_operand_map(map, base, rows, cols, kind)
-                            : make_output_map(map, const_cast<void*>(base), rows, cols, -kind);
+    // kind: 1 .. 999 operand (box rows), -2 / -4 output (element bytes), 1000 + 10 * box_tiles + box_rows scales
+    const int rc = kind >= 1000 ? make_scale_map(map, base, rows, cols, (kind - 1000) / 10, (kind - 1000) % 10)
+                 : kind > 0     ? make_operand_map(map, base, rows, cols, kind)
+                                : make_output_map(map, const_cast<void*>(base), rows, cols, -kind);
     if (rc == CK_OK && g_gemm_map_cache) {
         std::lock_guard<std::mutex> lock(mu);
         if (cache.size() >= 8192) cache.clear();   // bounded: a long-running process with ever-new buffers starts over
@@ -776,13 +862,16 @@ int launch_gemm(const void* a, const void* sfa, const void* b, const void* sfb, 
     if (!aligned16(a) || !aligned16(b) || !aligned16(sfa) || !aligned16(sfb) || !aligned16(d) || row_bytes % 16 != 0)
         CK_FAIL(CK_ERR_ALIGN, "%s: operands, scales and output must be 16-byte aligned (row pitch too)", what);
 
-    // per device: shared-memory opt-in, and how many CTA pairs can be resident at once
-    static int max_pairs[64] = {};   // (one table per instantiation of this function)
+    // Which pipeline: 1 = scale movers, 2 = tcgen05.cp by the MMA issuer (ck_set_option("gemm_tile", ...); 0 = default).
+    const bool use_cp = g_gemm_tile == 2 || (g_gemm_tile == 0 && kDefaultCp);
+    auto kern = use_cp ? gemm_blockscaled_kernel<kFp4, kRes, true> : gemm_blockscaled_kernel<kFp4, kRes, false>;
+    // per device and variant: shared-memory opt-in, and how many CTA pairs can be resident at once
+    static int max_pairs[2][64] = {};   // (one table per instantiation of this function)
     int dev = 0;
     cudaGetDevice(&dev);
-    int pairs_cap = (dev >= 0 && dev < 64) ? max_pairs[dev] : 0;
+    int pairs_cap = (dev >= 0 && dev < 64) ? max_pairs[use_cp][dev] : 0;
     if (pairs_cap == 0) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_blockscaled_kernel<kFp4, kRes>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
         if (e != cudaSuccess) CK_FAIL((int)e, "%s: cannot reserve %d bytes of shared memory: %s", what, kSmemBytes, cudaGetErrorString(e));
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = dim3(2 * (unsigned)(sm_count() / 2));
@@ -794,13 +883,13 @@ int launch_gemm(const void* a, const void* sfa, const void* b, const void* sfb, 
         cfg.attrs = &attr;
         cfg.numAttrs = 1;
         int n = 0;
-        e = cudaOccupancyMaxActiveClusters(&n, gemm_blockscaled_kernel<kFp4, kRes>, &cfg);
+        e = cudaOccupancyMaxActiveClusters(&n, kern, &cfg);
         if (e != cudaSuccess || n <= 0) {
             cudaGetLastError();
             n = sm_count() / 2;
         }
         pairs_cap = n < sm_count() / 2 ? n : sm_count() / 2;
-        if (dev >= 0 && dev < 64) max_pairs[dev] = pairs_cap;
+        if (dev >= 0 && dev < 64) max_pairs[use_cp][dev] = pairs_cap;
     }
 
     CUtensorMap map_a, map_b, map_out;
@@ -826,7 +915,13 @@ int launch_gemm(const void* a, const void* sfa, const void* b, const void* sfb, 
     p.gate = gate;
     const int64_t tiles = (int64_t)p.tiles_m * p.tiles_n;
     const int grid = 2 * (int)(tiles < pairs_cap ? tiles : pairs_cap);   // clusters of two CTAs
-    gemm_blockscaled_kernel<kFp4, kRes><<<grid, kThreads, kSmemBytes, stream>>>(map_a, map_b, map_out, p);
+    CUtensorMap map_sfa = map_a, map_sfb = map_a;   // (placeholders for the mover variant, which does not read them)
+    if (use_cp) {
+        const int box_tiles = kFp4 ? 4 : 1;
+        if (int rc = cached_map(&map_sfa, sfa, p.sf_row_tiles_a, p.sf_tiles_k, 1000 + 10 * box_tiles + 1)) return rc;
+        if (int rc = cached_map(&map_sfb, sfb, p.sf_row_tiles_b, p.sf_tiles_k, 1000 + 10 * box_tiles + 2)) return rc;
+    }
+    kern<<<grid, kThreads, kSmemBytes, stream>>>(map_a, map_b, map_out, map_sfa, map_sfb, p);
     return launch_status(what);
 }
 

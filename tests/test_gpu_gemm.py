@@ -215,3 +215,31 @@ def test_tensor_map_cache_is_transparent(ck):
     base = {(m, n): o for c, m, n, o in outs[:3]}
     for c, m, n, o in outs:
         assert torch.equal(o, base[(m, n)])
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 192, 256), (300, 520, 192), (513, 264, 3104), (1024, 3072, 3072), (4608, 3072, 12288),
+                                   (2344, 1160, 6176)])
+def test_pipeline_variants_agree(ck, M, N, K):
+    """The two pipelines of the GEMM kernel (scales moved into TMEM by dedicated warps -- the default -- or by
+    tcgen05.cp from the MMA issuer with all copies signalling the pair leader's barrier) issue the same MMAs: one
+    tile or many per CTA pair, ragged edges, partial last k-tile.  NVFP4 results are identical; with MXFP8 the
+    second pipeline lets the two issuing warps' k-tiles reach the tensor pipe in varying order, so fp32 sums may
+    differ in the last bit (1e-6 relative allowed), which is why it is not the default."""
+    x, w, bias = _operands(M, N, K, 9)
+    gx = (x.float().abs().max() / (6 * 448)).float().cuda()
+    gw = (w.float().abs().max() / (6 * 448)).float().cuda()
+    qx, sx = ck.quantize_nvfp4(x.cuda(), gx)
+    qw, sw = ck.quantize_nvfp4(w.cuda(), gw)
+    q8x, s8x = ck.quantize_mxfp8(x.cuda())
+    q8w, s8w = ck.quantize_mxfp8(w.cuda())
+    outs = {}
+    try:
+        for variant in (1, 2):
+            ck.set_option("gemm_tile", variant)
+            outs[variant] = (ck.scaled_mm_nvfp4(qx, qw, gx, gw, sx, sw, bias=bias.cuda(), out_dtype=torch.bfloat16),
+                             ck.scaled_mm_mxfp8(q8x, q8w, s8x, s8w, bias=bias.cuda(), out_dtype=torch.float32))
+            assert ck.gemm_device_status() == 0
+    finally:
+        ck.set_option("gemm_tile", 0)
+    assert torch.equal(outs[1][0], outs[2][0])
+    assert (outs[1][1] - outs[2][1]).abs().max() <= 1e-6 * outs[1][1].abs().max()
