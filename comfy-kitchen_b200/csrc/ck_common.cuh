@@ -45,6 +45,7 @@ __host__ __device__ inline int64_t round_up(int64_t x, int64_t m) { return (x + 
 __host__ __device__ inline int64_t ceil_div(int64_t x, int64_t m) { return (x + m - 1) / m; }
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+inline bool aligned32(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 31u) == 0; }
 
 // ---------------------------------------------------------------- element types
 

@@ -13,9 +13,9 @@
 // (|amax| < 2^-118) is reproduced explicitly.
 //
 // Work decomposition (HBM-bound, 3.03125 algorithmic bytes per element for
-// bf16): CTA = 256 threads = 128 rows x 256 columns; a warp reads one 512-byte
-// row segment per step (one 128-bit load per lane = 8 elements, four lanes per
-// block, two shuffles for the amax) and writes 8 bytes per lane.  Scale bytes
+// bf16): CTA = 256 threads = 128 rows x 256 columns; a thread owns 16 consecutive
+// elements (one 256-bit load), two lanes a block (one shuffle for the amax), and
+// writes 16 bytes; 16 rows per step, four steps in flight.  Scale bytes
 // are staged in shared memory in the GEMM's 128x4 tiled order (two 512-byte
 // tiles per CTA) and leave as 16-byte stores, padding included.
 #include "ck_common.cuh"
@@ -29,59 +29,69 @@ constexpr int kThreads = 256;
 constexpr int kWarps = kThreads / 32;
 constexpr int kSfTiles = kTileCols / 128;
 
+// Scalar loader: 16 elements with bounds checks, zero beyond the source.
 template <typename T>
-__device__ __forceinline__ void load8_guarded(const T* __restrict__ x, int64_t row, int64_t col, int64_t orig_rows,
-                                              int64_t orig_cols, float (&v)[8]) {
+__device__ __forceinline__ void load16_guarded(const T* __restrict__ x, int64_t row, int64_t col, int64_t orig_rows,
+                                               int64_t orig_cols, float (&v)[16]) {
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
+    for (int i = 0; i < 16; ++i) {
         int64_t c = col + i;
         v[i] = (row < orig_rows && c < orig_cols) ? Elem<T>::to_f32(x[row * orig_cols + c]) : 0.0f;
     }
 }
 
+// A thread owns 16 consecutive elements (one 256-bit load for 16-bit inputs), two neighbouring lanes a
+// 32-element block (one shuffle for its amax); 16 threads cover a 256-column row segment, so a 256-thread CTA
+// takes 16 rows per step and four steps are in flight per thread.
 template <typename T, bool kVec>
 __global__ void __launch_bounds__(kThreads)
 quantize_mxfp8_kernel(const T* __restrict__ x, uint8_t* __restrict__ q, uint8_t* __restrict__ sf, int64_t rows,
                       int64_t cols, int64_t orig_rows, int64_t orig_cols, int64_t sf_cpad) {
     __shared__ __align__(16) uint8_t s_sf[kSfTiles * 512];
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int tid = threadIdx.x;
+    const int seg = tid & 15;          // 16-element segment inside the 256-column tile
+    const int sub = tid >> 4;          // row inside one step
+    constexpr int kRowsPerStep = kThreads / 16;
     const int64_t row0 = (int64_t)blockIdx.y * kTileRows;
-    const int64_t col0 = (int64_t)blockIdx.x * kTileCols;
+    const int64_t col = (int64_t)blockIdx.x * kTileCols + seg * 16;
 
     reinterpret_cast<uint32_t*>(s_sf)[tid] = 0u;
     __syncthreads();
 
-    const int64_t col = col0 + lane * 8;
     const bool col_ok = col < cols;
-    const int blk_in_tile = lane >> 2;  // 32-element block index inside the tile (0..7)
+    const int blk_in_tile = seg >> 1;  // 32-element block index inside the tile (0..7)
 
     constexpr int kUnroll = 4;
 #pragma unroll 1
-    for (int it = 0; it < kTileRows / kWarps; it += kUnroll) {
-        float v[kUnroll][8];
+    for (int it = 0; it < kTileRows / kRowsPerStep; it += kUnroll) {
+        Raw16<T> raw[kUnroll];
 #pragma unroll
         for (int u = 0; u < kUnroll; ++u) {
-            const int64_t row = row0 + (it + u) * kWarps + warp;
+            const int64_t row = row0 + (it + u) * kRowsPerStep + sub;
             if (kVec) {
-                if (col < orig_cols && row < orig_rows) {
-                    load8<T>(x + row * orig_cols + col, v[u]);
-                } else {
-#pragma unroll
-                    for (int i = 0; i < 8; ++i) v[u][i] = 0.0f;
-                }
-            } else {
-                load8_guarded<T>(x, row, col, orig_rows, orig_cols, v[u]);
+                if (col < orig_cols && row < orig_rows) load_raw16<T>(x + row * orig_cols + col, raw[u]);
+                else zero_raw16<T>(raw[u]);
             }
         }
 #pragma unroll
         for (int u = 0; u < kUnroll; ++u) {
-            const int r_in_tile = (it + u) * kWarps + warp;
+            const int r_in_tile = (it + u) * kRowsPerStep + sub;
             const int64_t row = row0 + r_in_tile;
+            float v[16];
+            if (kVec) unpack16(raw[u], v);
+            else load16_guarded<T>(x, row, col, orig_rows, orig_cols, v);
+            float amax = 0.0f;
+#pragma unroll
+            for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(v[i]));
+            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+            float lo[8], hi[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) { lo[i] = v[i]; hi[i] = v[8 + i]; }
             uint32_t e;
-            const uint2 packed = mxfp8_encode_quarter_block(v[u], e);
+            const uint2 p0 = mxfp8_encode8(lo, amax, e), p1 = mxfp8_encode8(hi, amax, e);
             if (col_ok && row < rows) {
-                *reinterpret_cast<uint2*>(q + row * cols + col) = packed;
-                if ((lane & 3) == 0)
+                *reinterpret_cast<uint4*>(q + row * cols + col) = make_uint4(p0.x, p0.y, p1.x, p1.y);
+                if ((seg & 1) == 0)
                     s_sf[(blk_in_tile >> 2) * 512 + sf_tile_offset(r_in_tile, blk_in_tile & 3)] = (uint8_t)e;
             }
         }
@@ -90,7 +100,7 @@ quantize_mxfp8_kernel(const T* __restrict__ x, uint8_t* __restrict__ q, uint8_t*
 
     if (tid < kSfTiles * 32) {
         const int t = tid >> 5;
-        const int64_t tile_col = (col0 >> 7) + t;
+        const int64_t tile_col = ((int64_t)blockIdx.x * kTileCols >> 7) + t;
         if (tile_col < (sf_cpad >> 2)) {
             uint8_t* dst = sf + ((int64_t)blockIdx.y * (sf_cpad >> 2) + tile_col) * 512 + (tid & 31) * 16;
             *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(s_sf + t * 512 + (tid & 31) * 16);
@@ -149,7 +159,7 @@ int launch_quantize(const void* x, uint8_t* q, uint8_t* sf, int64_t rows, int64_
                     int64_t orig_cols, cudaStream_t stream) {
     const int64_t sf_cpad = round_up(cols / 32, 4);
     dim3 grid((unsigned)ceil_div(sf_cpad * 32, kTileCols), (unsigned)ceil_div(rows, kTileRows));
-    const bool vec = aligned16(x) && (orig_cols % 8 == 0);
+    const bool vec = aligned32(x) && (orig_cols % 16 == 0);   // 256-bit loads of whole 16-element segments
     if (vec)
         quantize_mxfp8_kernel<T, true><<<grid, kThreads, 0, stream>>>((const T*)x, q, sf, rows, cols, orig_rows, orig_cols, sf_cpad);
     else

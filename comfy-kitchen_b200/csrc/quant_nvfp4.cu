@@ -359,7 +359,6 @@ dequantize_nvfp4_kernel(const uint8_t* __restrict__ q, const float* __restrict__
     }
 }
 
-inline bool aligned32(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 31u) == 0; }
 
 template <typename T>
 int launch_quantize(const void* x, const float* g, uint8_t* q, uint8_t* sf, int64_t rows, int64_t cols,
