@@ -351,6 +351,48 @@ def front_end_and_rope(device, hbm_gbs: float) -> dict:
     return out
 
 
+def host_overhead(device, calls: int = 3000) -> dict:
+    """Host microseconds per call on tiny tensors (the GPU keeps up, so wall time is host time): the public API
+    as it is (dispatcher bypassed for plain eager tensors), the same call forced through torch's custom-op
+    dispatcher (what every call cost before, and what the reference's call path pays:
+    comfy_kitchen/registry.py:180-233 plus torch.library), the backend function alone, and the GEMM launcher
+    with and without its cache of encoded tensor maps."""
+    import comfy_kitchen as ckp
+    from comfy_kitchen.backends import cuda as ck
+
+    x = torch.randn(128, 256, device=device).bfloat16()
+    g = torch.tensor([0.01], device=device)
+
+    def per_call(fn):
+        for _ in range(50):
+            fn()
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        for _ in range(calls):
+            fn()
+        dt = time.perf_counter() - t0
+        torch.cuda.synchronize()
+        return round(dt / calls * 1e6, 1)
+
+    out = {"unit": "us per call (host)", "calls": calls}
+    out["quantize_nvfp4_public_api"] = per_call(lambda: ckp.quantize_nvfp4(x, g))
+    out["quantize_nvfp4_through_dispatcher"] = per_call(lambda: torch.ops.comfy_kitchen.quantize_nvfp4(x, g, 0.0, False, True))
+    out["quantize_nvfp4_backend_function"] = per_call(lambda: ck.quantize_nvfp4(x, g))
+    qx, sx = ck.quantize_nvfp4(x, g)
+    w = torch.randn(256, 256, device=device).bfloat16()
+    qw, sw = ck.quantize_nvfp4(w, g)
+    alpha = g * g
+    y = torch.empty(128, 256, device=device, dtype=torch.bfloat16)
+    gemm = lambda: ck.scaled_mm_nvfp4(qx, qw, g, g, sx, sw, out_dtype=torch.bfloat16, alpha=alpha, out=y)  # noqa: E731
+    out["scaled_mm_nvfp4_backend_function"] = per_call(gemm)
+    ck.set_option("gemm_map_cache", 0)
+    try:
+        out["scaled_mm_nvfp4_backend_function_no_map_cache"] = per_call(gemm)
+    finally:
+        ck.set_option("gemm_map_cache", 1)
+    return out
+
+
 def _library_scaled_mm(kind: str, qa, qb, sa, sb, ga, gb, bias):
     """The reference's eager path for the block-scaled GEMMs on a CUDA device: torch's scaled_mm, i.e. the
     cuBLASLt kernel (comfy_kitchen/backends/eager/quantization.py:224-248 and :369-404 through
@@ -928,6 +970,8 @@ def main() -> None:
         line["roofline"]["vs_library"] = vs["nvfp4"].get("ratio_geomean")
         line["roofline"]["vs_library_min"] = vs["nvfp4"].get("ratio_min")
         line["gemm_vs_library"] = vs
+        # ---- host cost of a call (dispatch overhead)
+        line["host_overhead"] = host_overhead(device)
         # ---- the DiT stack of configs[4] on this GPU (tp1; `--workload dit` runs it tensor-parallel)
         if not args.no_dit:
             line["dit_stack"] = dit_forward_ms(device, steps=3)

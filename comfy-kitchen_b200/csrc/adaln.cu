@@ -439,11 +439,11 @@ int launch_warp(const NormArgs& a, cudaStream_t stream) {
     auto kern = group == 4 ? norm_stream_kernel<T, kMode, 512, 0, 4>
               : group == 2 ? norm_stream_kernel<T, kMode, 512, 0, 2>
               : warps > 24 ? (iters == 6 ? norm_stream_kernel<T, kMode, 1024, 6> : norm_stream_kernel<T, kMode, 1024, 0>)
-              : warps > 16 ? (iters == 8 ? norm_stream_kernel<T, kMode, 768, 8> : norm_stream_kernel<T, kMode, 768, 0>)
+              : warps > 16 ? (iters == 8 ? norm_stream_kernel<T, kMode, 768, 8> : (iters == 6 ? norm_stream_kernel<T, kMode, 768, 6> : norm_stream_kernel<T, kMode, 768, 0>))
                            : (iters == 6 ? norm_stream_kernel<T, kMode, 512, 6>
                                          : (iters == 8 ? norm_stream_kernel<T, kMode, 512, 8> : norm_stream_kernel<T, kMode, 512, 0>));
-    const int attr_idx = group == 4 ? 5 : (group == 2 ? 4 : (warps > 24 ? (iters == 6 ? 6 : 7) : (warps > 16 ? (iters == 8 ? 8 : 3) : (iters == 6 ? 1 : (iters == 8 ? 2 : 0)))));
-    static bool attr_set[9][64] = {};
+    const int attr_idx = group == 4 ? 5 : (group == 2 ? 4 : (warps > 24 ? (iters == 6 ? 6 : 7) : (warps > 16 ? (iters == 8 ? 8 : (iters == 6 ? 9 : 3)) : (iters == 6 ? 1 : (iters == 8 ? 2 : 0)))));
+    static bool attr_set[10][64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev < 0 || dev >= 64 || !attr_set[attr_idx][dev]) {
