@@ -681,6 +681,8 @@ def dit_tp_leg(args, dist, device, rank: int, world: int) -> dict:
     vec = torch.randn(1, cfg.hidden, generator=g).bfloat16().to(device)
     why_not = None if args.nccl else stack.try_enable_peer_exchange()
     stack.calibrate(img, txt, vec)
+    if stack.exchange is not None and not args.no_sp:
+        stack.enable_sequence_parallel()
     run, launch = stack.capture_best(img, txt, vec)
     for _ in range(3):
         out = run(img, txt, vec)
@@ -741,6 +743,8 @@ def run_dit(args) -> None:
             torch.randn(1, cfg.hidden, generator=g).bfloat16().pin_memory()]
     img, txt, vec = (t.to(device) for t in host)
     stack.calibrate(img, txt, vec)
+    if stack.exchange is not None and not args.no_sp:
+        stack.enable_sequence_parallel()
     eager = args.no_graph
     # one graph on a single rank; with tensor parallelism a chain of graphs with the all-reduces between them
     run, how = (stack.forward, "eager") if eager else stack.capture_best(img, txt, vec)
@@ -820,6 +824,9 @@ def main() -> None:
     ap.add_argument("--no-dit", action="store_true", help="skip the DiT-stack leg of the default line")
     ap.add_argument("--nccl", action="store_true",
                     help="tensor-parallel DiT stack: NCCL all-reduce + addcmul instead of the fused peer-memory exchange kernel")
+    ap.add_argument("--no-sp", action="store_true",
+                    help="tensor-parallel DiT stack with the peer exchange: keep the norm -> quantize front end replicated "
+                         "on every rank instead of sequence-parallel")
     ap.add_argument("--no-graph", action="store_true", help="--workload dit: launch eagerly instead of replaying a CUDA graph")
     ap.add_argument("--m", type=int, default=9216)
     ap.add_argument("--n", type=int, default=9216)

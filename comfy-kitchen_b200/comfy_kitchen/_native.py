@@ -25,6 +25,8 @@ SIGNATURES: dict[str, list] = {
     "ck_norm_device_status": [],
     "ck_set_option": [c_char_p, I],
     "ck_tp_device_status": [],
+    "launch_tp_reduce_rows_kernel": [P, P, P, I, I, P, P, I64, I64, I64, I64, I64, I, I, P],
+    "launch_tp_gather_kernel": [P, P, I, I, I64, I64, I64, I64, I, P],
     "launch_tp_exchange_noalloc_kernel": [P, P, P, P, I64, I64, I64, I, I, P],
     "launch_tp_exchange_kernel": [P, P, P, P, P, I, I, P, P, I64, I64, I64, I, I, P],
     "launch_quantize_fp8_kernel": [P, P, P, I64, I, I, P],
@@ -44,6 +46,7 @@ SIGNATURES: dict[str, list] = {
     "launch_adaln_kernel": [P, P, P, P, I64, I64, I64, I64, F, I, P],
     "launch_rmsnorm_kernel": [P, P, P, I64, I64, F, I, P],
     "launch_adaln_quantize_nvfp4_kernel": [P, P, P, P, P, P, I64, I64, I64, I64, F, I, B, I, P],
+    "launch_adaln_quantize_nvfp4_rows_kernel": [P, P, P, P, P, P, I64, I64, I64, I64, F, I, B, I, I64, I64, P],
     "launch_adaln_quantize_mxfp8_kernel": [P, P, P, P, P, I64, I64, I64, I64, F, I, I, P],
 }
 _RESTYPES = {"ck_last_error": c_char_p, "ck_tp_pad_bytes": c_int64}

@@ -513,6 +513,32 @@ def adaln_quantize_nvfp4(
     return qx, sx.view(torch.float8_e4m3fn)
 
 
+def adaln_quantize_nvfp4_rows(
+    x: torch.Tensor,
+    scale: torch.Tensor,
+    shift: torch.Tensor,
+    per_tensor_scale: torch.Tensor,
+    qx: torch.Tensor,
+    sx: torch.Tensor,
+    row_begin: int,
+    row_end: int,
+    eps: float = 1e-6,
+    hi_first: bool = True,
+) -> None:
+    """adaln_quantize_nvfp4 for rows [row_begin, row_end) of x only, written into the caller's whole-tensor buffers
+    ``qx`` [N, D/2] uint8 and ``sx`` [roundup(N, 128), roundup(D/16, 4)] (the bytes of other rows are left alone).
+    For sequence-parallel callers: each rank quantizes its rows of a shared activation."""
+    xf, sc, sg, sh, hg, n, d = _norm_inputs(x, scale, shift)
+    assert d % 16 == 0, f"last dim must be divisible by 16, got {d}"
+    assert qx.shape == (n, d // 2) and qx.dtype == torch.uint8 and qx.is_contiguous()
+    assert tuple(sx.shape) == (roundup(n, 128), roundup(d // 16, 4)) and sx.element_size() == 1 and sx.is_contiguous()
+    g = _scalar_on(per_tensor_scale, x.device)
+    _native.call(
+        "launch_adaln_quantize_nvfp4_rows_kernel", _ptr(xf), _ptr(sc), _ptr(sh), _ptr(g), _ptr(qx), _ptr(sx), n, d, sg, hg,
+        float(eps), _code(x.dtype, "adaln_quantize_nvfp4"), bool(hi_first), 0, int(row_begin), int(row_end), _stream(x.device),
+    )
+
+
 def adaln_quantize_mxfp8(
     x: torch.Tensor, scale: torch.Tensor, shift: torch.Tensor, eps: float = 1e-6
 ) -> tuple[torch.Tensor, torch.Tensor]:

@@ -190,6 +190,10 @@ class DiTStack:
         # the tests have no such argument)
         self.fuse_residual_in_gemm = self.device.type == "cuda" and hasattr(ops, "launch_residual_supported")
         self._xbuf = None      # the residual stream [tokens, hidden], text tokens first; updated in place
+        # Sequence-parallel front end (needs the peer exchange): each rank keeps the residual stream, and runs the
+        # norm -> quantize in front of the column-parallel GEMMs, for its own rows only; the quantized rows are
+        # then gathered.  Switched on by enable_sequence_parallel() after calibrate().
+        self.sequence_parallel = False
         self._mods = None   # all blocks' modulation vectors during a forward
         self.heads_local = cfg.heads // self.tp.world
         self.freqs = rope_freqs(cfg, self.device)
@@ -366,6 +370,25 @@ class DiTStack:
         qx, sx = self.ops.adaln_quantize_nvfp4(x[None], scale, shift, g, self.cfg.eps)
         return qx, sx, g
 
+    def _front_end(self, parts):
+        """Norm + modulation + NVFP4 for consecutive row ranges of the residual stream.
+        parts: (site, row_begin, row_end, scale, shift) per range, in row order, covering the stream.
+        Returns (qx, sx, g) per part.  Replicated form: one fused kernel per part over all its rows.
+        Sequence-parallel form: each rank runs the kernel on its rows of each part, writing into the shared
+        activation buffers, and one gather distributes all ranks' rows before the GEMMs read them."""
+        if not self.sequence_parallel:
+            return [self._norm_quant(site, self._xbuf[a:b], scale, shift) for site, a, b, scale, shift in parts]
+        ex, out = self.exchange, []
+        for site, a, b, scale, shift in parts:
+            g = self.sites.static[site]
+            qx, sx = ex.qx[a:b], ex.sx[a:(b + 127) // 128 * 128]      # this part's rows of the shared buffers
+            lo, hi = max(ex.row_lo, a), min(ex.row_hi, b)
+            if lo < hi:
+                self.ops.adaln_quantize_nvfp4_rows(self._xbuf[a:b][None], scale, shift, g, qx, sx, lo - a, hi - a, self.cfg.eps)
+            out.append((qx, sx.view(torch.float8_e4m3fn), g))
+        ex.gather_quantized()
+        return out
+
     def _quant(self, site: str, segments):
         """NVFP4 of the column concatenation of the segments ((tensor, activation) pairs: see
         quantize_nvfp4_gather), read in place.  Without a static scale the maximum is taken from the
@@ -404,6 +427,16 @@ class DiTStack:
         assert self.device.type == "cuda"
         self.exchange = PeerExchange(self.tp.group, self.device, self.cfg.tokens, self.cfg.hidden, torch.bfloat16, mode)
         self._xbuf = self.exchange.residual
+
+    def enable_sequence_parallel(self) -> None:
+        """From now on every rank updates and normalises only its rows of the residual stream (whole 128-row scale
+        tiles, PeerExchange.row_bounds) and the ranks exchange the NVFP4 activation (0.56 bytes per element) instead
+        of the bf16 residual.  Needs static activation scales (calibrate() runs in the replicated form, where every
+        rank sees whole tensors) and a text length that is a multiple of 128 rows."""
+        assert self.exchange is not None, "enable_peer_exchange() first"
+        assert self.sites.static, "calibrate() first: the sequence-parallel front end needs static activation scales"
+        assert self.cfg.txt_tokens % 128 == 0, "text tokens must fill whole 128-row scale tiles"
+        self.sequence_parallel = True
 
     def try_enable_peer_exchange(self, mode: str | None = None) -> str | None:
         """enable_peer_exchange() with agreement between the ranks: the exchange is kept only if every rank
@@ -453,7 +486,11 @@ class DiTStack:
             off += r
         if fused:
             self.tp.all_reduce_calls += 1
-            self.exchange.exchange(gates[0], gates[1] if len(gates) > 1 else None, rows[0] if len(gates) > 1 else 0)
+            two = len(gates) > 1
+            if self.sequence_parallel:
+                self.exchange.reduce_rows(gates[0], gates[1] if two else None, rows[0] if two else 0)
+            else:
+                self.exchange.exchange(gates[0], gates[1] if two else None, rows[0] if two else 0)
             return
         y = self.tp.all_reduce_sum(y)
         off = 0
@@ -465,19 +502,18 @@ class DiTStack:
         blk, tt = self.double[i], self._tt
         order = ("txt", "img")   # token order of the residual stream
         mods = {s: self._modulation(blk[s], vec, 6) for s in order}
-        xs = {"txt": self._xbuf[:tt], "img": self._xbuf[tt:]}
+        total = self._xbuf.shape[0]
+        span = {"txt": (0, tt), "img": (tt, total)}
+        acts = self._front_end([(f"d{i}.{s}.attn_in", *span[s], mods[s][1], mods[s][0]) for s in order])
         parts = []
-        for s in order:
-            shift1, scale1 = mods[s][0], mods[s][1]
-            qx, sx, g = self._norm_quant(f"d{i}.{s}.attn_in", xs[s], scale1, shift1)
+        for s, (qx, sx, g) in zip(order, acts):
             parts.append((blk[s]["qkv"](qx, sx, g), blk[s]["q_norm"], blk[s]["k_norm"]))
         o = self._attend(parts)
         self._row_parallel_update([blk[s]["proj"] for s in order], [[(o[:, :tt], None)], [(o[:, tt:], None)]],
                                   [f"d{i}.{s}.attn_out" for s in order], [mods[s][2] for s in order])
+        acts = self._front_end([(f"d{i}.{s}.mlp_in", *span[s], mods[s][4], mods[s][3]) for s in order])
         mids = []
-        for s in order:
-            shift2, scale2 = mods[s][3], mods[s][4]
-            qx, sx, g = self._norm_quant(f"d{i}.{s}.mlp_in", xs[s], scale2, shift2)
+        for s, (qx, sx, g) in zip(order, acts):
             mids.append([(blk[s]["up"](qx, sx, g), "gelu_tanh")])   # GELU happens inside the quantizer
         self._row_parallel_update([blk[s]["down"] for s in order], mids, [f"d{i}.{s}.mlp_mid" for s in order],
                                   [mods[s][5] for s in order])
@@ -485,7 +521,7 @@ class DiTStack:
     def _single_block(self, i: int, vec: torch.Tensor) -> None:
         p, c, hl = self.single[i], self.cfg, self.heads_local
         shift, scale, gate = self._modulation(p, vec, 3)
-        qx, sx, g = self._norm_quant(f"s{i}.in", self._xbuf, scale, shift)
+        (qx, sx, g), = self._front_end([(f"s{i}.in", 0, self._xbuf.shape[0], scale, shift)])
         h1 = p["linear1"](qx, sx, g)   # [tokens, q | k | v | mlp]: the fused kernel reads the first part in place
         n_qkv = 3 * hl * c.head_dim
         o = self._attend([(h1, p["q_norm"], p["k_norm"])])
@@ -506,6 +542,8 @@ class DiTStack:
                 self._double_block(i, vec)
             for i in range(self.cfg.n_single):
                 self._single_block(i, vec)
+            if self.sequence_parallel:
+                self.exchange.gather_residual()   # every rank ends with the whole stream again
         finally:
             self._mods = None
         return x.clone()   # the residual buffer is reused by the next forward
@@ -561,7 +599,9 @@ class DiTStack:
         if self.tp.world == 1:
             return self.capture(img, txt, vec), "one CUDA graph per forward"
         if self.exchange is not None:
-            return self.capture(img, txt, vec), "one CUDA graph per forward, fused all-reduce + residual kernels (peer memory) inside"
+            how = ("sequence-parallel front end: reduce of the rank's rows, norm -> NVFP4 of those rows, gather of the quantized rows"
+                   if self.sequence_parallel else "fused all-reduce + residual kernels")
+            return self.capture(img, txt, vec), "one CUDA graph per forward, exchange over peer memory inside (" + how + ")"
         return self.capture_segments(img, txt, vec), "CUDA graphs between NCCL all-reduces"
 
     @torch.no_grad()
@@ -590,6 +630,25 @@ class DiTStack:
                 self.tp._dist.all_reduce(t, op=self.tp._dist.ReduceOp.MAX, group=self.tp.group)
             return float(t.item())
 
+        if self.exchange is not None and self.sequence_parallel:
+            ex = self.exchange
+            scale0 = torch.zeros(1, 1, self.cfg.hidden, device=self.device, dtype=torch.bfloat16)
+            g0 = torch.ones((), device=self.device)
+
+            def sp_step():
+                ex.reduce_rows(gate)
+                if ex.row_lo < ex.row_hi:
+                    self.ops.adaln_quantize_nvfp4_rows(x[None], scale0, scale0, g0, ex.qx, ex.sx, ex.row_lo, ex.row_hi, self.cfg.eps)
+                ex.gather_quantized()
+            per = timed(sp_step)
+            per_reduce = timed(lambda: ex.reduce_rows(gate))
+            per_gather = timed(ex.gather_quantized)
+            return {"all_reduce_ms": round(per * n, 3), "all_reduce_us_each": round(per * 1e3, 1),
+                    "all_reduce_how": "sequence parallel: reduce of the rank's rows over peer loads + norm -> NVFP4 of those rows + "
+                                      "gather of the quantized rows (peer stores)",
+                    "reduce_rows_us_each": round(per_reduce * 1e3, 1), "gather_quantized_us_each": round(per_gather * 1e3, 1),
+                    "all_reduce_bytes_each": int(x.numel() * 2), "elementwise_ms": 0.0,
+                    "elementwise_what": "the norm -> NVFP4 front end runs on each rank's rows only (inside all_reduce_ms)"}
         if self.exchange is not None:
             per = timed(lambda: self.exchange.exchange(gate))
             what = ("fused all-reduce + residual kernel, " +

@@ -49,8 +49,12 @@ class PeerExchange:
         lib = _native.load()
         mat = _align(rows * cols * 2)
         self._pad_bytes = _align(int(lib.ck_tp_pad_bytes()))
-        self._offsets = (0, mat, 2 * mat)
-        total = 2 * mat + self._pad_bytes
+        # one block per rank: [partial | residual | NVFP4 codes of the activation | its tiled block scales | flag pad]
+        rows_pad, sf_cols = (rows + 127) // 128 * 128, (cols // 16 + 3) // 4 * 4
+        q_bytes, sf_bytes = _align(rows * (cols // 2)), _align(rows_pad * sf_cols)
+        self._offsets = (0, mat, 2 * mat + q_bytes + sf_bytes)
+        self._q_off, self._sf_off = 2 * mat, 2 * mat + q_bytes
+        total = self._offsets[2] + self._pad_bytes
         mode = mode or os.environ.get("CK_TP_PEER_MEMORY", "auto")
         self._keep = []          # objects that own the mappings
         bases = None
@@ -68,10 +72,20 @@ class PeerExchange:
         n = rows * cols
         self.partial = self._block[:n * 2].view(dtype).view(rows, cols)
         self.residual = self._block[mat:mat + n * 2].view(dtype).view(rows, cols)
+        # sequence-parallel pieces: the quantized activation every rank assembles from all ranks' rows, and the row
+        # ranges (whole 128-row scale tiles, as even as they come) each rank is responsible for
+        self.qx = self._block[self._q_off:self._q_off + rows * (cols // 2)].view(rows, cols // 2)
+        self.sx = self._block[self._sf_off:self._sf_off + rows_pad * sf_cols].view(rows_pad, sf_cols)
+        self._sf_cols = sf_cols
+        tiles = rows_pad // 128
+        cuts = [min(rows, 128 * (tiles * r // self.world)) for r in range(self.world)] + [rows]
+        self.row_bounds = cuts
+        self.row_lo, self.row_hi = cuts[self.rank], cuts[self.rank + 1]
         arr = ctypes.c_void_p * self.world
         self._partials = arr(*[b + self._offsets[0] for b in bases])
         self._residuals = arr(*[b + self._offsets[1] for b in bases])
         self._pads = arr(*[b + self._offsets[2] for b in bases])
+        self._bases = arr(*bases)
         # NVLink-switch multicast address of the block, when the symmetric allocation has one (0 = none)
         mc = int(getattr(self, "_multicast_base", 0) or 0)
         # Off unless asked for (CK_TP_MULTIMEM=1): measured on 8 B200s the switch path takes the same 107 us per
@@ -116,6 +130,37 @@ class PeerExchange:
                      ctypes.c_void_p(torch.cuda.current_stream(self.device).cuda_stream))
         self.calls += 1
         return self.residual
+
+    # ---- sequence-parallel form: reduce my rows only, then distribute what I derived from them
+
+    def reduce_rows(self, gate0: torch.Tensor, gate1: torch.Tensor | None = None, split_row: int = 0, blocks: int = 0) -> None:
+        """residual[row_lo:row_hi] += gate * sum_over_ranks(partial[row_lo:row_hi]) in this rank's buffer only."""
+        g0 = gate0.reshape(-1)
+        g1 = None if gate1 is None else gate1.reshape(-1)
+        assert g0.numel() == self.cols and g0.dtype == self.dtype and g0.is_contiguous()
+        code = 2 if self.dtype == torch.bfloat16 else 1
+        _native.call("launch_tp_reduce_rows_kernel", self._partials, self._residuals, self._pads, self.world, self.rank,
+                     ctypes.c_void_p(g0.data_ptr()), ctypes.c_void_p(0 if g1 is None else g1.data_ptr()), int(split_row),
+                     self.rows, self.cols, self.row_lo, self.row_hi, code, int(blocks),
+                     ctypes.c_void_p(torch.cuda.current_stream(self.device).cuda_stream))
+        self.calls += 1
+
+    def _gather(self, r0, r1, blocks: int = 0) -> None:
+        _native.call("launch_tp_gather_kernel", self._bases, self._pads, self.world, self.rank, r0[0], r0[1], r1[0], r1[1],
+                     int(blocks), ctypes.c_void_p(torch.cuda.current_stream(self.device).cuda_stream))
+
+    def gather_quantized(self) -> None:
+        """Every rank's rows of ``qx`` (codes) and ``sx`` (whole scale tiles) reach every rank's copy."""
+        lo, hi = self.row_lo, self.row_hi
+        half = self.cols // 2
+        tile_lo, tile_hi = lo // 128, (hi + 127) // 128
+        self._gather((self._q_off + lo * half, self._q_off + hi * half),
+                     (self._sf_off + tile_lo * 128 * self._sf_cols, self._sf_off + tile_hi * 128 * self._sf_cols))
+
+    def gather_residual(self) -> None:
+        """Every rank's rows of the residual stream reach every rank's copy (end of a sequence-parallel forward)."""
+        row = self.cols * 2
+        self._gather((self._offsets[1] + self.row_lo * row, self._offsets[1] + self.row_hi * row), (0, 0))
 
     def status(self) -> int:
         """Synchronise and read (then clear) the kernel's status word: 0, or -6 after a wait for a peer ran out."""

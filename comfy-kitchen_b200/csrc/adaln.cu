@@ -37,6 +37,7 @@ struct NormArgs {
     float eps;
     int rms;
     int hi_first;
+    int64_t row_begin, row_end;   // rows to process (row_end = 0: all N rows; the launcher resolves it)
 };
 
 __device__ __forceinline__ float warp_sum(float v) {
@@ -118,8 +119,10 @@ norm_stream_kernel(const NormArgs a, const int ring, const int64_t rows_per_cta,
     }
     __syncwarp();
 
-    const int64_t total_rows = kMode == kOutPlain ? a.N : round_up(a.N, 128);
-    const int64_t r0 = (int64_t)blockIdx.x * rows_per_cta;
+    // (a.row_end is resolved by the launcher: N, or N rounded up to 128 where the scale buffer's padding rows belong
+    // to this call, or the end of the caller's row range)
+    const int64_t total_rows = a.row_end;
+    const int64_t r0 = a.row_begin + (int64_t)blockIdx.x * rows_per_cta;
     const int64_t r1 = min(r0 + rows_per_cta, total_rows);
     const T* __restrict__ xg = static_cast<const T*>(a.x);
 
@@ -451,7 +454,13 @@ int launch_warp(const NormArgs& a, cudaStream_t stream) {
         if (e != cudaSuccess) CK_FAIL((int)e, "adaln: cannot reserve shared memory: %s", cudaGetErrorString(e));
         if (dev >= 0 && dev < 64) attr_set[attr_idx][dev] = true;
     }
-    const int64_t rows = kMode == kOutPlain ? a.N : round_up(a.N, 128);
+    // rows of this call: all of them (fused modes: plus the scale buffer's padding rows), or the caller's range
+    // (the padding rows go with the range that ends at N)
+    NormArgs ar = a;
+    if (ar.row_end == 0) { ar.row_begin = 0; ar.row_end = a.N; }
+    if (kMode != kOutPlain && ar.row_end == a.N) ar.row_end = round_up(a.N, 128);
+    const int64_t rows = ar.row_end - ar.row_begin;
+    if (rows <= 0) return CK_OK;
     int sms = 148;
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     // one CTA per SM, each with a contiguous range of rows (at least one row per warp or group of warps)
@@ -460,7 +469,7 @@ int launch_warp(const NormArgs& a, cudaStream_t stream) {
     const int64_t rows_per_cta = ceil_div(rows, grid);
     grid = ceil_div(rows, rows_per_cta);
     const uint32_t poll_limit = g_norm_poll_limit == 0 ? kRowWaitLimit : (g_norm_poll_limit < 0 ? 0u : (uint32_t)g_norm_poll_limit);
-    kern<<<(unsigned)grid, warps * 32, smem, stream>>>(a, ring, rows_per_cta, cache_mod, poll_limit);
+    kern<<<(unsigned)grid, warps * 32, smem, stream>>>(ar, ring, rows_per_cta, cache_mod, poll_limit);
     return launch_status("adaln");
 }
 
@@ -546,6 +555,26 @@ extern "C" int launch_adaln_quantize_nvfp4_kernel(const void* x, const void* sca
     if (norm_kind == 0 && (!scale || !shift)) CK_FAIL(CK_ERR_NULL, "adaln_quantize_nvfp4: null modulation pointer");
     NormArgs a{x, scale, shift, output, static_cast<uint8_t*>(block_scales), static_cast<const float*>(global_scale),
                N, D, scale_group, shift_group, 0, eps, norm_kind != 0, hi_first ? 1 : 0};
+    return launch_fused<kOutNvfp4>(a, dtype_code, stream);
+}
+
+// launch_adaln_quantize_nvfp4_kernel restricted to rows [row_begin, row_end) of the N rows: codes and scale bytes of
+// those rows only are written, at the positions the whole-tensor call writes them (a range that ends at N also
+// writes the scale buffer's padding rows).  For sequence-parallel callers: each rank quantizes its rows of a shared
+// activation.  Ranges whose bounds are multiples of 128 rows touch disjoint scale tiles.
+extern "C" int launch_adaln_quantize_nvfp4_rows_kernel(const void* x, const void* scale, const void* shift,
+                                                       const void* global_scale, void* output, void* block_scales,
+                                                       int64_t N, int64_t D, int64_t scale_group, int64_t shift_group,
+                                                       float eps, int dtype_code, bool hi_first, int norm_kind,
+                                                       int64_t row_begin, int64_t row_end, cudaStream_t stream) {
+    using namespace ck;
+    if (norm_kind == 0 && (!scale || !shift)) CK_FAIL(CK_ERR_NULL, "adaln_quantize_nvfp4_rows: null modulation pointer");
+    if (row_begin < 0 || row_end < row_begin || row_end > N)
+        CK_FAIL(CK_ERR_SHAPE, "adaln_quantize_nvfp4_rows: rows %lld..%lld outside 0..%lld", (long long)row_begin, (long long)row_end, (long long)N);
+    if (row_begin == row_end) return CK_OK;
+    NormArgs a{x, scale, shift, output, static_cast<uint8_t*>(block_scales), static_cast<const float*>(global_scale),
+               N, D, scale_group, shift_group, 0, eps, norm_kind != 0, hi_first ? 1 : 0, row_begin, row_end};
+    if (!warp_path_ok(a)) CK_FAIL(CK_ERR_UNSUPPORTED, "adaln_quantize_nvfp4_rows: needs 16-byte aligned rows of a multiple of 16 elements");
     return launch_fused<kOutNvfp4>(a, dtype_code, stream);
 }
 

@@ -47,11 +47,17 @@ struct ExchangeParams {
     int64_t total_vec;            // rows * cols / 8
     int vec_per_row;              // cols / 8
     int rank, world;
+    int64_t slice_lo_vec, slice_hi_vec;   // this rank's slice in vectors (< 0: equal shares of total_vec)
+    int local_only;               // 1: the updated slice stays in this rank's residual buffer, and there is no end barrier
 };
 
 __device__ __forceinline__ uint32_t* pad_start(uint32_t* pad, int block, int src) { return pad + (block * kMaxRanks + src); }
 __device__ __forceinline__ uint32_t* pad_end(uint32_t* pad, int block, int src) { return pad + kMaxBlocks * kMaxRanks + (block * kMaxRanks + src); }
 __device__ __forceinline__ uint32_t* pad_epoch(uint32_t* pad, int block) { return pad + 2 * kMaxBlocks * kMaxRanks + block; }
+// (the gather kernel's own flags and epochs follow: gather_end[kMaxBlocks][kMaxRanks], gather_epoch[kMaxBlocks])
+constexpr int kGatherPadOffset = 2 * kMaxBlocks * kMaxRanks + kMaxBlocks;
+__device__ __forceinline__ uint32_t* pad_gather_end(uint32_t* pad, int block, int src) { return pad + kGatherPadOffset + (block * kMaxRanks + src); }
+__device__ __forceinline__ uint32_t* pad_gather_epoch(uint32_t* pad, int block) { return pad + kGatherPadOffset + kMaxBlocks * kMaxRanks + block; }
 
 __device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
     asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
@@ -94,18 +100,23 @@ __device__ __forceinline__ void multimem_st(uint4* mc, const uint4& v) {
 }
 
 // Threads 0 .. world-1 of the block: signal peer `threadIdx.x`, then wait for its signal.
-__device__ __forceinline__ void block_barrier(const ExchangeParams& p, bool end_phase, uint32_t epoch) {
+__device__ __forceinline__ uint32_t* pad_flag(uint32_t* pad, int which, int block, int src) {
+    return which == 0 ? pad_start(pad, block, src) : (which == 1 ? pad_end(pad, block, src) : pad_gather_end(pad, block, src));
+}
+// which: 0 = start flags, 1 = end flags, 2 = the gather kernel's flags
+__device__ __forceinline__ void block_barrier(uint32_t* const* pads, int rank, int world, int which, uint32_t epoch) {
     __syncthreads();
-    if ((int)threadIdx.x < p.world) {
+    if ((int)threadIdx.x < world) {
         const int peer = threadIdx.x;
-        uint32_t* theirs = end_phase ? pad_end(p.pad[peer], blockIdx.x, p.rank) : pad_start(p.pad[peer], blockIdx.x, p.rank);
-        st_release_sys(theirs, epoch);
-        const uint32_t* mine = end_phase ? pad_end(p.pad[p.rank], blockIdx.x, peer) : pad_start(p.pad[p.rank], blockIdx.x, peer);
+        const bool end_phase = which != 0;
+        st_release_sys(pad_flag(pads[peer], which, blockIdx.x, rank), epoch);
+        const uint32_t* mine = pad_flag(pads[rank], which, blockIdx.x, peer);
         const unsigned long long t0 = now_ns();
         uint32_t spins = 0;
         while ((int32_t)(ld_acquire_sys(mine) - epoch) < 0) {
             if ((++spins & 255u) == 0 && now_ns() - t0 > kWaitNs) {
                 atomicCAS(&g_tp_status, 0, ((end_phase ? 2 : 1) << 16) | (int)blockIdx.x);
+                (void)which;
                 break;
             }
         }
@@ -157,10 +168,11 @@ tp_exchange_kernel(const ExchangeParams p) {
     const int world = kWorld > 0 ? kWorld : p.world;
     constexpr int kRanks = kWorld > 0 ? kWorld : kMaxRanks;
 
-    block_barrier(p, false, epoch);   // every rank's partial result is complete
+    block_barrier(p.pad, p.rank, p.world, 0, epoch);   // every rank's partial result is complete
 
     // this rank's slice, and this block's part of it
-    const int64_t lo = p.total_vec * p.rank / world, hi = p.total_vec * (p.rank + 1) / world;
+    const int64_t lo = p.slice_lo_vec >= 0 ? p.slice_lo_vec : p.total_vec * p.rank / world;
+    const int64_t hi = p.slice_lo_vec >= 0 ? p.slice_hi_vec : p.total_vec * (p.rank + 1) / world;
     const int64_t per_block = (hi - lo + gridDim.x - 1) / gridDim.x;
     const int64_t b0 = lo + per_block * blockIdx.x;
     const int64_t b1 = b0 + per_block < hi ? b0 + per_block : hi;
@@ -207,13 +219,17 @@ tp_exchange_kernel(const ExchangeParams p) {
                 w[j >> 1] = pack2<T>(__fadd_rn(x[j], __fmul_rn(g[j], y0)), __fadd_rn(x[j + 1], __fmul_rn(g[j + 1], y1)));
             }
             const uint4 out = make_uint4(w[0], w[1], w[2], w[3]);
+            if (p.local_only) {
+                p.residual[p.rank][idx] = out;
+            } else {
 #pragma unroll
-            for (int i = 0; i < kRanks; ++i)
-                if (i < world) p.residual[i][idx] = out;
+                for (int i = 0; i < kRanks; ++i)
+                    if (i < world) p.residual[i][idx] = out;
+            }
         }
     }
     __threadfence_system();           // this thread's pushes are visible system-wide before the block signals
-    block_barrier(p, true, epoch);    // every peer has finished pushing its slice into my residual buffer
+    if (!p.local_only) block_barrier(p.pad, p.rank, p.world, 1, epoch);    // every peer has finished pushing its slice into my residual buffer
     if (threadIdx.x == 0) *pad_epoch(my_pad, blockIdx.x) = epoch;
 }
 
@@ -230,7 +246,7 @@ tp_exchange_multimem_kernel(const ExchangeParams p) {
     if (threadIdx.x == 0) s_epoch = *pad_epoch(my_pad, blockIdx.x) + 1u;
     __syncthreads();
     const uint32_t epoch = s_epoch;
-    block_barrier(p, false, epoch);
+    block_barrier(p.pad, p.rank, p.world, 0, epoch);
 
     const int64_t lo = p.total_vec * p.rank / p.world, hi = p.total_vec * (p.rank + 1) / p.world;
     const int64_t per_block = (hi - lo + gridDim.x - 1) / gridDim.x;
@@ -265,7 +281,7 @@ tp_exchange_multimem_kernel(const ExchangeParams p) {
         }
     }
     __threadfence_system();
-    block_barrier(p, true, epoch);
+    block_barrier(p.pad, p.rank, p.world, 1, epoch);
     if (threadIdx.x == 0) *pad_epoch(my_pad, blockIdx.x) = epoch;
 }
 
@@ -288,14 +304,18 @@ void launch_exchange(const ExchangeParams& p, int blocks, cudaStream_t stream) {
 }  // namespace ck
 
 extern "C" int64_t ck_tp_pad_bytes(void) {
-    return (int64_t)sizeof(uint32_t) * (2 * ck::kMaxBlocks * ck::kMaxRanks + ck::kMaxBlocks);
+    // start + end flags and epochs of the exchange kernel, then the gather kernel's flags and epochs
+    return (int64_t)sizeof(uint32_t) * (3 * ck::kMaxBlocks * ck::kMaxRanks + 2 * ck::kMaxBlocks);
 }
 
-extern "C" int launch_tp_exchange_kernel(const void* const* partials, void* const* residuals, void* const* pads,
-                                         const void* mc_partial, void* mc_residual, int world,
-                                         int rank, const void* gate0, const void* gate1, int64_t split_row, int64_t rows,
-                                         int64_t cols, int dtype_code, int blocks, cudaStream_t stream) {
+static int exchange_impl(const void* const* partials, void* const* residuals, void* const* pads,
+                         const void* mc_partial, void* mc_residual, int world,
+                         int rank, const void* gate0, const void* gate1, int64_t split_row, int64_t rows,
+                         int64_t cols, int dtype_code, int blocks, cudaStream_t stream, int64_t row_lo, int64_t row_hi,
+                         int local_only) {
     using namespace ck;
+    if (local_only && (row_lo < 0 || row_hi < row_lo || row_hi > rows))
+        CK_FAIL(CK_ERR_SHAPE, "tp_reduce_rows: rows %lld..%lld outside 0..%lld", (long long)row_lo, (long long)row_hi, (long long)rows);
     if (!partials || !residuals || !pads || !gate0) CK_FAIL(CK_ERR_NULL, "tp_exchange: null pointer");
     if (world < 1 || world > kMaxRanks || rank < 0 || rank >= world)
         CK_FAIL(CK_ERR_SHAPE, "tp_exchange: rank %d of %d (at most %d ranks)", rank, world, kMaxRanks);
@@ -324,11 +344,93 @@ extern "C" int launch_tp_exchange_kernel(const void* const* partials, void* cons
     if (!gate1) p.split_vec = p.total_vec;
     p.rank = rank;
     p.world = world;
+    p.local_only = local_only;
+    p.slice_lo_vec = local_only ? row_lo * (cols / 8) : -1;
+    p.slice_hi_vec = local_only ? row_hi * (cols / 8) : -1;
+    if (local_only) { p.mc_partial = nullptr; p.mc_residual = nullptr; }
     if (blocks <= 0) blocks = 148;   // one per SM: 114 registers x 512 threads leave room for one block per SM
     if (blocks > kMaxBlocks) blocks = kMaxBlocks;
     if (dtype_code == CK_BF16) launch_exchange<__nv_bfloat16>(p, blocks, stream);
     else launch_exchange<__half>(p, blocks, stream);
     return launch_status("tp_exchange");
+}
+
+namespace ck {
+namespace {
+
+// All-gather by pushing: every rank copies up to two byte ranges of its own buffer to the same offsets of every
+// peer's buffer (16-byte stores), then waits until all peers have done the same.  Used for the quantized
+// activation of the sequence-parallel stack (codes and scale tiles of the rank's rows) and for the residual
+// stream at the end of a forward.  Flags and epochs of its own, so it can follow the reduction kernel freely.
+struct GatherParams {
+    uint4* buf[kMaxRanks];
+    uint32_t* pad[kMaxRanks];
+    int64_t lo[2], hi[2];    // ranges in 16-byte vectors (hi <= lo: empty)
+    int rank, world;
+};
+
+__global__ void __launch_bounds__(kThreads)
+tp_gather_kernel(const GatherParams p) {
+    __shared__ uint32_t s_epoch;
+    uint32_t* my_pad = p.pad[p.rank];
+    if (threadIdx.x == 0) s_epoch = *pad_gather_epoch(my_pad, blockIdx.x) + 1u;
+    __syncthreads();
+    const uint32_t epoch = s_epoch;
+    const uint4* src = p.buf[p.rank];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        const int64_t n = p.hi[r] - p.lo[r];
+        if (n <= 0) continue;
+        const int64_t per_block = (n + gridDim.x - 1) / gridDim.x;
+        const int64_t b0 = p.lo[r] + per_block * blockIdx.x;
+        const int64_t b1 = b0 + per_block < p.hi[r] ? b0 + per_block : p.hi[r];
+        constexpr int kUnroll = 4;
+        for (int64_t base = b0 + threadIdx.x; base < b1; base += (int64_t)kThreads * kUnroll) {
+            uint4 v[kUnroll];
+#pragma unroll
+            for (int u = 0; u < kUnroll; ++u) {
+                const int64_t idx = base + (int64_t)u * kThreads;
+                if (idx < b1) v[u] = ld_cg(src + idx);
+            }
+#pragma unroll
+            for (int u = 0; u < kUnroll; ++u) {
+                const int64_t idx = base + (int64_t)u * kThreads;
+                if (idx >= b1) continue;
+                for (int i = 0; i < p.world; ++i)
+                    if (i != p.rank) p.buf[i][idx] = v[u];
+            }
+        }
+    }
+    __threadfence_system();
+    block_barrier(p.pad, p.rank, p.world, 2, epoch);   // every peer's ranges have landed in my buffer
+    if (threadIdx.x == 0) *pad_gather_epoch(my_pad, blockIdx.x) = epoch;
+}
+
+}  // namespace
+}  // namespace ck
+
+extern "C" int launch_tp_gather_kernel(void* const* bufs, void* const* pads, int world, int rank, int64_t lo0, int64_t hi0,
+                                       int64_t lo1, int64_t hi1, int blocks, cudaStream_t stream) {
+    using namespace ck;
+    if (!bufs || !pads) CK_FAIL(CK_ERR_NULL, "tp_gather: null pointer");
+    if (world < 1 || world > kMaxRanks || rank < 0 || rank >= world)
+        CK_FAIL(CK_ERR_SHAPE, "tp_gather: rank %d of %d (at most %d ranks)", rank, world, kMaxRanks);
+    if ((lo0 | hi0 | lo1 | hi1) & 15) CK_FAIL(CK_ERR_ALIGN, "tp_gather: range bounds must be multiples of 16 bytes");
+    if (lo0 < 0 || lo1 < 0) CK_FAIL(CK_ERR_SHAPE, "tp_gather: negative offset");
+    GatherParams p{};
+    for (int i = 0; i < world; ++i) {
+        if (!bufs[i] || !pads[i]) CK_FAIL(CK_ERR_NULL, "tp_gather: null buffer of rank %d", i);
+        if (!aligned16(bufs[i]) || !aligned16(pads[i])) CK_FAIL(CK_ERR_ALIGN, "tp_gather: buffers must be 16-byte aligned");
+        p.buf[i] = static_cast<uint4*>(bufs[i]);
+        p.pad[i] = static_cast<uint32_t*>(pads[i]);
+    }
+    p.lo[0] = lo0 / 16; p.hi[0] = hi0 / 16; p.lo[1] = lo1 / 16; p.hi[1] = hi1 / 16;
+    p.rank = rank;
+    p.world = world;
+    if (blocks <= 0) blocks = 148;
+    if (blocks > kMaxBlocks) blocks = kMaxBlocks;
+    tp_gather_kernel<<<blocks, kThreads, 0, stream>>>(p);
+    return launch_status("tp_gather");
 }
 
 // ---------------------------------------------------------------------------------------------------
@@ -376,6 +478,25 @@ extern "C" int launch_tp_exchange_noalloc_kernel(const void* partial, void* resi
     void* pads[1] = {pad_of_device[dev]};
     return launch_tp_exchange_kernel(partials, residuals, pads, nullptr, nullptr, 1, 0, gate0, gate1, split_row, rows, cols,
                                      dtype_code, blocks, stream);
+}
+
+extern "C" int launch_tp_exchange_kernel(const void* const* partials, void* const* residuals, void* const* pads,
+                                         const void* mc_partial, void* mc_residual, int world,
+                                         int rank, const void* gate0, const void* gate1, int64_t split_row, int64_t rows,
+                                         int64_t cols, int dtype_code, int blocks, cudaStream_t stream) {
+    return exchange_impl(partials, residuals, pads, mc_partial, mc_residual, world, rank, gate0, gate1, split_row, rows, cols,
+                         dtype_code, blocks, stream, 0, 0, 0);
+}
+
+// Sequence-parallel form of the exchange: this rank sums rows [row_lo, row_hi) of all ranks' partial results and
+// updates those rows of its OWN residual buffer only (nothing is pushed, no end barrier); the ranks' row ranges
+// partition the matrix.  launch_tp_gather_kernel later distributes whatever the ranks derive from their rows.
+extern "C" int launch_tp_reduce_rows_kernel(const void* const* partials, void* const* residuals, void* const* pads, int world,
+                                            int rank, const void* gate0, const void* gate1, int64_t split_row, int64_t rows,
+                                            int64_t cols, int64_t row_lo, int64_t row_hi, int dtype_code, int blocks,
+                                            cudaStream_t stream) {
+    return exchange_impl(partials, residuals, pads, nullptr, nullptr, world, rank, gate0, gate1, split_row, rows, cols,
+                         dtype_code, blocks, stream, row_lo, row_hi, 1);
 }
 
 // Reads and clears the exchange kernel's status word (synchronises the device): 0, or

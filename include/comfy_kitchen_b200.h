@@ -185,6 +185,14 @@ int launch_adaln_quantize_nvfp4_kernel(const void* x, const void* scale, const v
                                        void* output, void* block_scales, int64_t N, int64_t D, int64_t scale_group,
                                        int64_t shift_group, float eps, int dtype_code, bool hi_first, int norm_kind,
                                        ck_stream_t stream);
+/* launch_adaln_quantize_nvfp4_kernel restricted to rows [row_begin, row_end) of the N rows (same bytes at the same
+ * places as the whole-tensor call; a range ending at N also writes the scale buffer's padding rows).  For
+ * sequence-parallel callers; no counterpart in the reference. */
+int launch_adaln_quantize_nvfp4_rows_kernel(const void* x, const void* scale, const void* shift,
+                                            const void* global_scale, void* output, void* block_scales, int64_t N,
+                                            int64_t D, int64_t scale_group, int64_t shift_group, float eps,
+                                            int dtype_code, bool hi_first, int norm_kind, int64_t row_begin,
+                                            int64_t row_end, ck_stream_t stream);
 int launch_adaln_quantize_mxfp8_kernel(const void* x, const void* scale, const void* shift, void* output,
                                        void* block_scales, int64_t N, int64_t D, int64_t scale_group,
                                        int64_t shift_group, float eps, int dtype_code, int norm_kind,
@@ -211,6 +219,18 @@ int64_t ck_tp_pad_bytes(void);
 int launch_tp_exchange_kernel(const void* const* partials, void* const* residuals, void* const* pads,
                               const void* mc_partial, void* mc_residual, int world, int rank, const void* gate0, const void* gate1, int64_t split_row, int64_t rows,
                               int64_t cols, int dtype_code, int blocks, ck_stream_t stream);
+/* Sequence-parallel form (no counterpart in the reference): launch_tp_reduce_rows_kernel sums rows [row_lo, row_hi)
+ * of all ranks' partial results and updates those rows of this rank's own residual buffer only (the ranks' row ranges
+ * partition the matrix); launch_tp_gather_kernel then copies up to two byte ranges [lo, hi) (multiples of 16) of this
+ * rank's buffer to the same offsets of every peer's buffer and waits until all peers have done the same -- e.g. the
+ * quantized activation a rank computed for its rows.  bufs / pads: host arrays of `world` device pointers as above;
+ * both kernels use the flag pad (different parts of it) and every rank must issue the same sequence of calls. */
+int launch_tp_reduce_rows_kernel(const void* const* partials, void* const* residuals, void* const* pads, int world,
+                                 int rank, const void* gate0, const void* gate1, int64_t split_row, int64_t rows,
+                                 int64_t cols, int64_t row_lo, int64_t row_hi, int dtype_code, int blocks,
+                                 ck_stream_t stream);
+int launch_tp_gather_kernel(void* const* bufs, void* const* pads, int world, int rank, int64_t lo0, int64_t hi0,
+                            int64_t lo1, int64_t hi1, int blocks, ck_stream_t stream);
 /* No counterpart in the reference.  The one-rank exchange (residual <- residual + gate * partial) for callers
  * that must not allocate device memory at call time -- a runtime with a fixed arena, a plugin inside a pipeline
  * where cudaMalloc would synchronise: the flag pad the kernel needs lives in a device array inside the library
