@@ -75,3 +75,42 @@ def test_two_ranks_against_nccl():
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env, cwd=ROOT)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
     assert "TP_EXCHANGE_WORKER_OK" in r.stdout
+
+
+def test_row_range_front_end_and_single_rank_sequence_parallel_pieces():
+    """The pieces of the sequence-parallel front end on one GPU: the fused norm -> NVFP4 kernel restricted to row
+    ranges writes the same bytes at the same places as the whole-tensor call (ranges on 128-row boundaries, the last
+    one carrying the scale buffer's padding rows), and the reduce-my-rows / gather kernels with a world of one rank
+    reduce to the residual update."""
+    from comfy_kitchen.backends import cuda as ck
+    from comfy_kitchen.tp_exchange import PeerExchange
+
+    n, d = 1000, 3072
+    g = torch.Generator(device="cuda").manual_seed(31)
+    x = torch.randn(1, n, d, device="cuda", generator=g).bfloat16()
+    sc = (0.1 * torch.randn(1, 1, d, device="cuda", generator=g)).bfloat16()
+    sh = (0.1 * torch.randn(1, 1, d, device="cuda", generator=g)).bfloat16()
+    gs = torch.tensor([5.0 / (6 * 448)], device="cuda")
+    q_ref, s_ref = ck.adaln_quantize_nvfp4(x, sc, sh, gs, 1e-6)
+    q = torch.full_like(q_ref, 0xAA)
+    s = torch.full((1024, 192), 0xAA, dtype=torch.uint8, device="cuda")
+    for lo, hi in ((0, 256), (256, 256), (256, 768), (768, 1000)):
+        ck.adaln_quantize_nvfp4_rows(x, sc, sh, gs, q, s, lo, hi, 1e-6)
+    assert torch.equal(q, q_ref)
+    assert torch.equal(s, s_ref.view(torch.uint8))
+    assert ck.norm_device_status() == 0
+
+    ex = PeerExchange(None, "cuda", n, d, torch.bfloat16)
+    assert ex.row_bounds == [0, n] and (ex.row_lo, ex.row_hi) == (0, n)
+    x0 = torch.randn(n, d, device="cuda", generator=g).bfloat16()
+    y = torch.randn(n, d, device="cuda", generator=g).bfloat16()
+    gate = torch.randn(d, device="cuda", generator=g).bfloat16()
+    ex.residual.copy_(x0)
+    ex.partial.copy_(y)
+    ex.reduce_rows(gate)
+    ex.qx.fill_(7)
+    ex.gather_quantized()      # one rank: nothing to push, the barrier passes
+    ex.gather_residual()
+    assert torch.equal(ex.residual, torch.addcmul(x0, gate, y))
+    assert int(ex.qx.min()) == 7
+    assert ex.status() == 0
