@@ -402,6 +402,11 @@ int launch_warp(const NormArgs& a, cudaStream_t stream) {
     } else {
         const size_t need_cache = cache_mod ? (size_t)round_up(a.D, 512) * 8 : 0;
         while (group < 4 && 16 * (row_bytes / group) + need_cache > 225 * 1024) group *= 2;
+        // Few rows per SM (at most one per warp): a row's latency, not throughput, sets the time, so two warps
+        // share each row.  Measured on rows of 3072 elements: 512 rows 16.5 -> 8.8 us, 2304 rows 18.1 -> 13.4 us;
+        // from 4096 rows on one warp per row is as fast or faster.
+        const int64_t n_rows = (a.row_end > 0 ? a.row_end : a.N) - a.row_begin;
+        if (group == 1 && n_rows <= 16 * 148 && a.D % 64 == 0 && a.D >= 1024) group = 2;
     }
     if (group != 1 && group != 2 && group != 4) CK_FAIL(CK_ERR_SHAPE, "adaln: warps per row must be 1, 2 or 4");
     while (group > 1 && a.D % (32 * group) != 0) group /= 2;   // every share must be whole 32-element blocks

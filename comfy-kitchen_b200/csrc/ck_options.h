@@ -23,6 +23,8 @@
 //                         NVFP4 at K = 3072, up to 13 % for MXFP8, but the two issuers' k-tiles then reach the
 //                         tensor pipe in varying order: MXFP8 sums can differ in the last fp32 bit between runs)
 //   "gemm_map_cache"      0 disables the cache of encoded tensor maps (1: default)
+//   "tp_bulk"             1: launch_tp_reduce_rows_kernel pulls the peers' rows with bulk copies through shared memory
+//                         (0: 16-byte peer loads from every thread)
 #pragma once
 
 namespace ck {
@@ -35,4 +37,5 @@ extern int g_rope_threads_per_sm;
 extern int g_gelu_table_min;
 extern int g_gemm_tile;
 extern int g_gemm_map_cache;
+extern int g_tp_bulk;
 }  // namespace ck

@@ -285,8 +285,129 @@ tp_exchange_multimem_kernel(const ExchangeParams p) {
     if (threadIdx.x == 0) *pad_epoch(my_pad, blockIdx.x) = epoch;
 }
 
+// Reduce-my-rows with the peers' partial rows pulled by bulk copies (cp.async.bulk, no multicast) into a ring of
+// shared-memory stages instead of by per-thread loads: one elected thread keeps (stages - 1) x world copies of
+// kChunkBytes in flight, which fills the NVLink read path with far fewer outstanding instructions than 16-byte loads
+// from every thread.  local_only form (sequence parallel): the result goes to this rank's residual rows only.
+constexpr int kBulkThreads = 256;
+constexpr int kChunkVecs = 256;                 // vectors per chunk: one per thread
+constexpr int kChunkBytes = kChunkVecs * 16;    // 4 KB per source rank and chunk
+constexpr int kBulkStages = 4;
+
+__device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+template <typename T>
+__global__ void __launch_bounds__(kBulkThreads)
+tp_reduce_rows_bulk_kernel(const ExchangeParams p) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem);                       // [kBulkStages]
+    uint8_t* stage0 = smem + 128;
+    const int world = p.world;
+    const size_t stage_bytes = (size_t)world * kChunkBytes;
+    __shared__ uint32_t s_epoch;
+    uint32_t* my_pad = p.pad[p.rank];
+    if (threadIdx.x == 0) {
+        s_epoch = *pad_epoch(my_pad, blockIdx.x) + 1u;
+        for (int s = 0; s < kBulkStages; ++s)
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_addr(&bars[s])));
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    __syncthreads();
+    const uint32_t epoch = s_epoch;
+    block_barrier(p.pad, p.rank, p.world, 0, epoch);   // every rank's partial result is complete
+
+    const int64_t lo = p.slice_lo_vec, hi = p.slice_hi_vec;
+    const int64_t per_block = ((hi - lo + gridDim.x - 1) / gridDim.x + kChunkVecs - 1) / kChunkVecs * kChunkVecs;
+    const int64_t b0 = lo + per_block * blockIdx.x;
+    const int64_t b1 = b0 + per_block < hi ? b0 + per_block : hi;
+    const int64_t n_chunks = b1 > b0 ? (b1 - b0 + kChunkVecs - 1) / kChunkVecs : 0;
+
+    auto issue = [&](int64_t j) {   // thread 0: all ranks' copies of chunk j into stage j % kBulkStages
+        const int s = (int)(j % kBulkStages);
+        const int64_t v0 = b0 + j * kChunkVecs;
+        const uint32_t bytes = (uint32_t)((b1 - v0 < kChunkVecs ? b1 - v0 : kChunkVecs) * 16);
+        const uint32_t bar = smem_addr(&bars[s]);
+        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes * (uint32_t)world) : "memory");
+        for (int i = 0; i < world; ++i)
+            asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                         ::"r"(smem_addr(stage0 + s * stage_bytes + (size_t)i * kChunkBytes)), "l"(p.partial[i] + v0), "r"(bytes), "r"(bar)
+                         : "memory");
+    };
+    if (threadIdx.x == 0)
+        for (int64_t j = 0; j < kBulkStages - 1 && j < n_chunks; ++j) issue(j);
+
+    bool alive = true;
+    for (int64_t j = 0; j < n_chunks; ++j) {
+        const int s = (int)(j % kBulkStages);
+        const uint32_t bar = smem_addr(&bars[s]), parity = (uint32_t)((j / kBulkStages) & 1);
+        const int64_t idx = b0 + j * kChunkVecs + threadIdx.x;
+        uint4 xv = make_uint4(0u, 0u, 0u, 0u);
+        if (idx < b1) xv = ld_cg(p.residual[p.rank] + idx);      // my residual rows are local: plain load, in flight during the wait
+        if (alive) {
+            const unsigned long long t0 = now_ns();
+            uint32_t done = 0, spins = 0;
+            while (!done) {
+                asm volatile("{ .reg .pred q; mbarrier.try_wait.parity.shared::cta.b64 q, [%1], %2; selp.u32 %0, 1, 0, q; }"
+                             : "=r"(done) : "r"(bar), "r"(parity) : "memory");
+                if (!done && (++spins & 63u) == 0 && now_ns() - t0 > kWaitNs) {
+                    atomicCAS(&g_tp_status, 0, (3 << 16) | (int)blockIdx.x);
+                    alive = false;
+                    break;
+                }
+            }
+        }
+        if (idx < b1 && alive) {
+            float sum[8];
+#pragma unroll
+            for (int k = 0; k < 8; ++k) sum[k] = 0.0f;
+            const uint4* st = reinterpret_cast<const uint4*>(stage0 + s * stage_bytes) + threadIdx.x;
+            for (int i = 0; i < world; ++i) {
+                float f[8];
+                unpack8<T>(st[(size_t)i * kChunkVecs], f);
+#pragma unroll
+                for (int k = 0; k < 8; ++k) sum[k] += f[k];
+            }
+            const int col_vec = (int)(idx % p.vec_per_row);
+            const uint4* gate = reinterpret_cast<const uint4*>(idx < p.split_vec ? p.gate0 : p.gate1) + col_vec;
+            float g[8], x[8];
+            unpack8<T>(__ldg(gate), g);
+            unpack8<T>(xv, x);
+            uint32_t w[4];
+#pragma unroll
+            for (int k = 0; k < 8; k += 2) {
+                const float y0 = Elem<T>::round(sum[k]), y1 = Elem<T>::round(sum[k + 1]);
+                w[k >> 1] = pack2<T>(__fadd_rn(x[k], __fmul_rn(g[k], y0)), __fadd_rn(x[k + 1], __fmul_rn(g[k + 1], y1)));
+            }
+            p.residual[p.rank][idx] = make_uint4(w[0], w[1], w[2], w[3]);
+        }
+        __syncthreads();   // everyone has read stage s: it can be refilled
+        if (threadIdx.x == 0 && alive && j + kBulkStages - 1 < n_chunks) issue(j + kBulkStages - 1);
+    }
+    // (a block that gave up leaves its outstanding copies to land in shared memory it no longer reads; wait for them
+    // before the block ends)
+    if (!alive && threadIdx.x == 0) {
+        const unsigned long long t0 = now_ns();
+        while (now_ns() - t0 < 100000ull) { }
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) *pad_epoch(my_pad, blockIdx.x) = epoch;
+}
+
 template <typename T>
 void launch_exchange(const ExchangeParams& p, int blocks, cudaStream_t stream) {
+    if (p.local_only && p.world > 1 && g_tp_bulk) {
+        const size_t smem = 128 + (size_t)kBulkStages * p.world * kChunkBytes;
+        static bool attr_done = false;
+        if (!attr_done) {   // enough for kMaxRanks sources per stage
+            const cudaError_t e = cudaFuncSetAttribute(tp_reduce_rows_bulk_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                       128 + kBulkStages * kMaxRanks * kChunkBytes);
+            if (e != cudaSuccess) (void)cudaGetLastError();   // (the launch below then reports what is wrong)
+            attr_done = true;
+        }
+        tp_reduce_rows_bulk_kernel<T><<<blocks, kBulkThreads, smem, stream>>>(p);
+        return;
+    }
     if (p.mc_partial != nullptr && p.world > 1) {
         tp_exchange_multimem_kernel<T><<<blocks, kThreads, 0, stream>>>(p);
         return;

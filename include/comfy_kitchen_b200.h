@@ -185,9 +185,12 @@ int launch_adaln_quantize_nvfp4_kernel(const void* x, const void* scale, const v
                                        void* output, void* block_scales, int64_t N, int64_t D, int64_t scale_group,
                                        int64_t shift_group, float eps, int dtype_code, bool hi_first, int norm_kind,
                                        ck_stream_t stream);
-/* launch_adaln_quantize_nvfp4_kernel restricted to rows [row_begin, row_end) of the N rows (same bytes at the same
- * places as the whole-tensor call; a range ending at N also writes the scale buffer's padding rows).  For
- * sequence-parallel callers; no counterpart in the reference. */
+/* launch_adaln_quantize_nvfp4_kernel restricted to rows [row_begin, row_end) of the N rows, written at the places
+ * the whole-tensor call writes them (a range ending at N also writes the scale buffer's padding rows).  The bytes
+ * equal the whole-tensor call's whenever the launcher gives both the same number of warps per row, which it chooses
+ * from the number of rows processed (two below 2368 rows, else one); otherwise the row statistics are summed in
+ * another order and an activation may move by one rounding step.  For sequence-parallel callers; no counterpart in
+ * the reference. */
 int launch_adaln_quantize_nvfp4_rows_kernel(const void* x, const void* scale, const void* shift,
                                             const void* global_scale, void* output, void* block_scales, int64_t N,
                                             int64_t D, int64_t scale_group, int64_t shift_group, float eps,
