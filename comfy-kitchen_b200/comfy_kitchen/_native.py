@@ -38,6 +38,7 @@ SIGNATURES: dict[str, list] = {
     "launch_cublas_gemm_blockwise_fp4_kernel": [P, P, P, P, P, P, I64, I64, I64, P, I, P, B, P],
     "launch_scaled_mm_nvfp4_kernel": [P, P, P, P, P, P, I, I64, I64, I64, P, I, P],
     "launch_scaled_mm_nvfp4_residual_kernel": [P, P, P, P, P, P, I, P, P, I64, I64, I64, P, I, P],
+    "launch_scaled_mm_nvfp4_scatter_kernel": [P, P, P, P, P, P, I, I64, P, I, I64, I64, I64, P, I, P],
     "launch_scaled_mm_mxfp8_kernel": [P, P, P, P, P, P, I, I64, I64, I64, I, P],
     "launch_apply_rope_kernel": [P, P, P, P, P] + [I64] * 17 + [I, I, B, P],
     "launch_stochastic_rounding_fp8_kernel": [P, P, P, I64, I, I, P],

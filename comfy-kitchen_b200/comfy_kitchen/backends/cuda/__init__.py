@@ -239,11 +239,14 @@ def scaled_mm_nvfp4(
     out: torch.Tensor | None = None,
     residual: torch.Tensor | None = None,
     gate: torch.Tensor | None = None,
+    scatter=None,
 ) -> torch.Tensor:
     """``out`` (not in the reference's signature): a contiguous [M, N] tensor of ``out_dtype`` to write into,
     e.g. a row range of a larger buffer.  ``residual`` [M, N] and ``gate`` [N] (both of ``out_dtype``, bf16 or
     fp16; also additions): the kernel's epilogue returns ``residual + gate * y`` instead of ``y`` (bytes equal to
-    the GEMM followed by ``torch.addcmul``); ``out`` may be ``residual`` itself."""
+    the GEMM followed by ``torch.addcmul``); ``out`` may be ``residual`` itself.  ``scatter`` = (dests, bounds, world,
+    row_offset) with ctypes arrays of peer-mapped destination pointers and row bounds (a tensor-parallel group's
+    reduce-scatter fused into the epilogue, see ``launch_scaled_mm_nvfp4_scatter_kernel``): nothing is returned."""
     a, b = _plain(a), _plain(b)
     block_scale_a, block_scale_b = _plain(block_scale_a), _plain(block_scale_b)
     if alpha is None:
@@ -272,6 +275,15 @@ def scaled_mm_nvfp4(
         bias_code = DTYPE_TO_CODE[bias.dtype]
     else:
         bias = None
+    if scatter is not None:
+        dests, bounds, world, row_offset = scatter
+        assert out is None and residual is None and out_dtype in (torch.bfloat16, torch.float16)
+        _native.call(
+            "launch_scaled_mm_nvfp4_scatter_kernel", _ptr(a.contiguous()), _ptr(block_scale_a.contiguous().view(torch.uint8)),
+            _ptr(b.contiguous()), _ptr(block_scale_b.contiguous().view(torch.uint8)), dests, bounds, int(world), int(row_offset),
+            _ptr(bias), bias_code, m, n, k, _ptr(alpha), _code(out_dtype, "scaled_mm_nvfp4"), _stream(a.device),
+        )
+        return None
     if out is None:
         out = torch.empty(m, n, dtype=out_dtype, device=a.device)
     else:

@@ -149,9 +149,12 @@ class QuantLinear:
         self.bias = bias
         return self
 
-    def __call__(self, qx: torch.Tensor, sx: torch.Tensor, act_scale: torch.Tensor, out=None, residual=None, gate=None) -> torch.Tensor:
+    def __call__(self, qx: torch.Tensor, sx: torch.Tensor, act_scale: torch.Tensor, out=None, residual=None, gate=None,
+                 scatter=None) -> torch.Tensor:
         alpha = (act_scale * self.tensor_scale).reshape(1)
         extra = {} if residual is None else {"residual": residual, "gate": gate}
+        if scatter is not None:
+            extra["scatter"] = scatter
         return self.ops.scaled_mm_nvfp4(qx, self.qdata, act_scale, self.tensor_scale, sx, self.block_scales,
                                         bias=self.bias, out_dtype=torch.bfloat16, alpha=alpha, out=out, **extra)
 
@@ -478,6 +481,18 @@ class DiTStack:
                 lin(qx, sx, g, out=x[off:off + r], residual=x[off:off + r], gate=gate)
                 off += r
             return
+        if fused and self.sequence_parallel:
+            # the GEMMs' epilogues deliver each tile row to the rank that owns it (reduce-scatter over NVLink while
+            # the main loop runs); the owner then sums its slabs from local memory and updates its residual rows
+            self.tp.all_reduce_calls += 1
+            off = 0
+            for lin, segs, site, r in zip(linears, inputs, sites, rows):
+                qx, sx, g = self._quant(site, segs)
+                lin(qx, sx, g, scatter=self.exchange.scatter_args(off))
+                off += r
+            two = len(gates) > 1
+            self.exchange.reduce_rows(gates[0], gates[1] if two else None, rows[0] if two else 0, scattered=True)
+            return
         y = self.exchange.partial if fused else torch.empty_like(x)
         off = 0
         for lin, segs, site, r in zip(linears, inputs, sites, rows):
@@ -487,7 +502,7 @@ class DiTStack:
         if fused:
             self.tp.all_reduce_calls += 1
             two = len(gates) > 1
-            if self.sequence_parallel:
+            if self.sequence_parallel:   # (not reached: kept for a sequence-parallel run without the scattered GEMM)
                 self.exchange.reduce_rows(gates[0], gates[1] if two else None, rows[0] if two else 0)
             else:
                 self.exchange.exchange(gates[0], gates[1] if two else None, rows[0] if two else 0)
@@ -599,7 +614,8 @@ class DiTStack:
         if self.tp.world == 1:
             return self.capture(img, txt, vec), "one CUDA graph per forward"
         if self.exchange is not None:
-            how = ("sequence-parallel front end: reduce of the rank's rows, norm -> NVFP4 of those rows, gather of the quantized rows"
+            how = ("sequence parallel: row-parallel GEMMs scatter their tile rows to the owning ranks, each rank sums and "
+                   "normalises its rows, NVFP4 rows gathered"
                    if self.sequence_parallel else "fused all-reduce + residual kernels")
             return self.capture(img, txt, vec), "one CUDA graph per forward, exchange over peer memory inside (" + how + ")"
         return self.capture_segments(img, txt, vec), "CUDA graphs between NCCL all-reduces"

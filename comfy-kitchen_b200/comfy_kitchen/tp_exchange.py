@@ -47,7 +47,14 @@ class PeerExchange:
         self.world = dist.get_world_size(group) if live else 1
         self.rank = dist.get_rank(group) if live else 0
         lib = _native.load()
-        mat = _align(rows * cols * 2)
+        # the partial region holds either the whole [rows, cols] partial result (exchange / reduce_rows by peer loads)
+        # or, in the scattered layout, one slab per source rank with that rank's partial rows of MY row range
+        # (written by the peers' GEMM epilogues): world slabs of the largest range
+        tiles = (rows + 127) // 128
+        slab_rows = max(min(rows, 128 * (tiles * (r + 1) // self.world)) - min(rows, 128 * (tiles * r // self.world))
+                        for r in range(self.world)) if self.world > 1 else rows
+        self._slab_bytes = _align(max(slab_rows, 1) * cols * 2)
+        mat = _align(max(rows * cols * 2, self.world * self._slab_bytes))
         self._pad_bytes = _align(int(lib.ck_tp_pad_bytes()))
         # one block per rank: [partial | residual | NVFP4 codes of the activation | its tiled block scales | flag pad]
         rows_pad, sf_cols = (rows + 127) // 128 * 128, (cols // 16 + 3) // 4 * 4
@@ -86,6 +93,12 @@ class PeerExchange:
         self._residuals = arr(*[b + self._offsets[1] for b in bases])
         self._pads = arr(*[b + self._offsets[2] for b in bases])
         self._bases = arr(*bases)
+        # scattered layout: where MY partial rows of rank d's range go (d's slab number `rank`), the bounds as the
+        # GEMM launcher wants them, and this rank's slabs addressed so that "pointer + global vector index" lands in them
+        self._scatter_dests = arr(*[b + self._offsets[0] + self.rank * self._slab_bytes for b in bases])
+        self._scatter_bounds = (ctypes.c_int64 * (self.world + 1))(*self.row_bounds)
+        back = self.row_lo * cols * 2
+        self._slab_partials = arr(*[bases[self.rank] + self._offsets[0] + i * self._slab_bytes - back for i in range(self.world)])
         # NVLink-switch multicast address of the block, when the symmetric allocation has one (0 = none)
         mc = int(getattr(self, "_multicast_base", 0) or 0)
         # Off unless asked for (CK_TP_MULTIMEM=1): measured on 8 B200s the switch path takes the same 107 us per
@@ -133,13 +146,22 @@ class PeerExchange:
 
     # ---- sequence-parallel form: reduce my rows only, then distribute what I derived from them
 
-    def reduce_rows(self, gate0: torch.Tensor, gate1: torch.Tensor | None = None, split_row: int = 0, blocks: int = 0) -> None:
-        """residual[row_lo:row_hi] += gate * sum_over_ranks(partial[row_lo:row_hi]) in this rank's buffer only."""
+    def scatter_args(self, row_offset: int):
+        """The ``scatter=`` argument of ``scaled_mm_nvfp4`` for a row-parallel GEMM whose first output row is row
+        ``row_offset`` of the group's matrix: its tile rows go straight into the slabs of the ranks that sum them."""
+        return (self._scatter_dests, self._scatter_bounds, self.world, int(row_offset))
+
+    def reduce_rows(self, gate0: torch.Tensor, gate1: torch.Tensor | None = None, split_row: int = 0, blocks: int = 0,
+                    scattered: bool = False) -> None:
+        """residual[row_lo:row_hi] += gate * sum_over_ranks(partial[row_lo:row_hi]) in this rank's buffer only.
+        ``scattered``: the partial rows were delivered into this rank's slabs by the peers' GEMMs (scatter_args), so
+        the sum reads local memory only; otherwise they are read from the peers' partial buffers."""
         g0 = gate0.reshape(-1)
         g1 = None if gate1 is None else gate1.reshape(-1)
         assert g0.numel() == self.cols and g0.dtype == self.dtype and g0.is_contiguous()
         code = 2 if self.dtype == torch.bfloat16 else 1
-        _native.call("launch_tp_reduce_rows_kernel", self._partials, self._residuals, self._pads, self.world, self.rank,
+        _native.call("launch_tp_reduce_rows_kernel", self._slab_partials if scattered else self._partials, self._residuals,
+                     self._pads, self.world, self.rank,
                      ctypes.c_void_p(g0.data_ptr()), ctypes.c_void_p(0 if g1 is None else g1.data_ptr()), int(split_row),
                      self.rows, self.cols, self.row_lo, self.row_hi, code, int(blocks),
                      ctypes.c_void_p(torch.cuda.current_stream(self.device).cuda_stream))

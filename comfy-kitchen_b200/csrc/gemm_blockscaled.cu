@@ -297,6 +297,15 @@ struct GemmParams {
     const void* gate;     // [N] in the output dtype
 };
 
+// Scattered output (tensor-parallel reduce-scatter fused into the epilogue, kEpi = 2): output row r of this GEMM is
+// row row_offset + r of a matrix whose rows [bounds[d], bounds[d+1]) belong to rank d; its tile rows go to rank d's
+// buffer through m[d], rows counted from bounds[d].
+struct OutMaps {
+    CUtensorMap m[8];
+    int world, row_offset;
+    int bounds[9];
+};
+
 // Tile order: bands of kGroupM tile rows, walked column by column inside a band, so that the ~74 tiles in
 // flight at any time cover a compact block of the output (about kGroupM x 18 tiles) and re-use the same few A and
 // W tiles from L2 while the much larger output streams through it.  Band heights of 2 to 4 measured alike and
@@ -334,11 +343,12 @@ __device__ __forceinline__ uint32_t pack_pair<__half>(float a, float b) {
 //              multicast), and the MMA issuer itself moves the stage's scale tiles into TMEM with tcgen05.cp
 //              (.cta_group::2: one instruction copies in both CTAs, each from its own shared memory) right before
 //              the stage's MMAs; the scale buffer in TMEM is indexed by the stage, so it is free when the stage is.
-template <bool kFp4, bool kRes, bool kCp>
+template <bool kFp4, int kEpi, bool kCp>   // kEpi: 0 plain output, 1 fused residual update, 2 output scattered over ranks
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
 gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                         const __grid_constant__ CUtensorMap map_out, const __grid_constant__ CUtensorMap map_sfa,
-                        const __grid_constant__ CUtensorMap map_sfb, const GemmParams p) {
+                        const __grid_constant__ CUtensorMap map_sfb, const __grid_constant__ OutMaps omaps,
+                        const GemmParams p) {
     extern __shared__ uint8_t smem_raw[];
     // 1024-byte alignment for the swizzled tiles (the same offset in both CTAs of the pair)
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -622,7 +632,7 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
             }
             auto bias_at = [&](int col) { return __shfl_sync(0xffffffffu, bias_reg[col >> 5], col & 31); };
             // fused residual update: gate for these 64 columns, kept like the bias
-            constexpr bool fuse_res = kRes;
+            constexpr bool fuse_res = kEpi == 1;
             float gate_reg[2] = {0.0f, 0.0f};
             if (fuse_res) {
 #pragma unroll
@@ -709,7 +719,17 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
                     fence_async_smem();
                     __syncwarp();
                     const int col = n0 + ch * chunk_cols;
-                    if (lane == 0 && store_ok && col < p.N) tma_store_2d(&map_out, stg, col, row0);
+                    if (lane == 0 && store_ok && col < p.N) {
+                        if constexpr (kEpi == 2) {
+                            // the 32 rows of this chunk belong to one rank (bounds are multiples of 128): its buffer, its row count
+                            const int grow = omaps.row_offset + row0;
+                            int d = 0;
+                            while (d + 1 < omaps.world && grow >= omaps.bounds[d + 1]) ++d;
+                            tma_store_2d(&omaps.m[d], stg, col, grow - omaps.bounds[d]);
+                        } else {
+                            tma_store_2d(&map_out, stg, col, row0);
+                        }
+                    }
                 }
             }
         }
@@ -841,11 +861,18 @@ int sm_count() {
     return cached[dev];
 }
 
-template <bool kFp4, bool kRes = false>
+template <bool kFp4, int kEpi = 0>
 int launch_gemm(const void* a, const void* sfa, const void* b, const void* sfb, void* d, const void* bias,
                 int bias_code, int64_t M, int64_t N, int64_t K, const float* alpha, int out_code, cudaStream_t stream,
-                const void* residual = nullptr, const void* gate = nullptr) {
+                const void* residual = nullptr, const void* gate = nullptr, void* const* scatter_dests = nullptr,
+                const int64_t* scatter_bounds = nullptr, int scatter_world = 0, int64_t scatter_row_offset = 0) {
     const char* what = kFp4 ? "scaled_mm_nvfp4" : "scaled_mm_mxfp8";
+    if (scatter_world < 0 || scatter_world > 8) CK_FAIL(CK_ERR_SHAPE, "%s: scatter over %d ranks (at most 8)", what, scatter_world);
+    if (scatter_world > 0) {
+        if (!scatter_dests || !scatter_bounds) CK_FAIL(CK_ERR_NULL, "%s: scatter needs destinations and bounds", what);
+        if (out_code == CK_F32 || residual) CK_FAIL(CK_ERR_UNSUPPORTED, "%s: scattered output is 16-bit and without residual", what);
+        d = scatter_dests[0];   // (only checked for alignment below)
+    }
     if ((residual != nullptr) != (gate != nullptr)) CK_FAIL(CK_ERR_NULL, "%s: residual and gate go together", what);
     if (residual && out_code == CK_F32) CK_FAIL(CK_ERR_DTYPE, "%s: the fused residual update needs a 16-bit output", what);
     if (residual && (!aligned16(residual) || !aligned16(gate))) CK_FAIL(CK_ERR_ALIGN, "%s: residual and gate must be 16-byte aligned", what);
@@ -864,7 +891,7 @@ int launch_gemm(const void* a, const void* sfa, const void* b, const void* sfb, 
 
     // Which pipeline: 1 = scale movers, 2 = tcgen05.cp by the MMA issuer (ck_set_option("gemm_tile", ...); 0 = default).
     const bool use_cp = g_gemm_tile == 2 || (g_gemm_tile == 0 && kDefaultCp);
-    auto kern = use_cp ? gemm_blockscaled_kernel<kFp4, kRes, true> : gemm_blockscaled_kernel<kFp4, kRes, false>;
+    auto kern = use_cp ? gemm_blockscaled_kernel<kFp4, kEpi, true> : gemm_blockscaled_kernel<kFp4, kEpi, false>;
     // per device and variant: shared-memory opt-in, and how many CTA pairs can be resident at once
     static int max_pairs[2][64] = {};   // (one table per instantiation of this function)
     int dev = 0;
@@ -895,7 +922,27 @@ int launch_gemm(const void* a, const void* sfa, const void* b, const void* sfb, 
     CUtensorMap map_a, map_b, map_out;
     if (int rc = cached_map(&map_a, a, M, row_bytes, BM)) return rc;
     if (int rc = cached_map(&map_b, b, N, row_bytes, BN / 2)) return rc;
-    if (int rc = cached_map(&map_out, d, M, N, out_code == CK_F32 ? -4 : -2)) return rc;
+    if (scatter_world == 0)
+        if (int rc = cached_map(&map_out, d, M, N, out_code == CK_F32 ? -4 : -2)) return rc;
+    OutMaps omaps;
+    if (scatter_world > 0) {
+        map_out = map_a;   // (placeholder: the scattered epilogue does not read it)
+        for (int i = 0; i < scatter_world; ++i) {
+            const int64_t lo = scatter_bounds[i], hi = scatter_bounds[i + 1];
+            if (lo < 0 || hi < lo || lo % 128 != 0 || (hi % 128 != 0 && i + 1 < scatter_world) || lo > INT32_MAX || hi > INT32_MAX)
+                CK_FAIL(CK_ERR_SHAPE, "%s: scatter bounds must ascend in multiples of 128 rows", what);
+            if (!scatter_dests[i] || !aligned16(scatter_dests[i])) CK_FAIL(CK_ERR_ALIGN, "%s: scatter destination %d", what, i);
+            omaps.m[i] = map_a;
+            if (hi > lo)
+                if (int rc = cached_map(&omaps.m[i], scatter_dests[i], hi - lo, N, -2)) return rc;
+        }
+        for (int i = scatter_world; i < 8; ++i) omaps.m[i] = map_a;
+        if (M % 32 != 0) CK_FAIL(CK_ERR_SHAPE, "%s: scattered output needs M (%lld) to be a multiple of 32 rows", what, (long long)M);
+        if (scatter_row_offset < 0 || scatter_row_offset % 32 != 0 || scatter_row_offset + M > scatter_bounds[scatter_world])
+            CK_FAIL(CK_ERR_SHAPE, "%s: scatter row offset %lld (multiple of 32, rows within the bounds)", what, (long long)scatter_row_offset);
+    } else {
+        for (int i = 0; i < 8; ++i) omaps.m[i] = map_a;
+    }
 
     GemmParams p{};
     p.sfa = static_cast<const uint8_t*>(sfa);
@@ -913,6 +960,9 @@ int launch_gemm(const void* a, const void* sfa, const void* b, const void* sfb, 
     p.tiles_n = (int)ceil_div(N, BN);
     p.residual = residual;
     p.gate = gate;
+    omaps.world = scatter_world;
+    omaps.row_offset = (int)scatter_row_offset;
+    for (int i = 0; i < 9; ++i) omaps.bounds[i] = (scatter_world > 0 && i <= scatter_world) ? (int)scatter_bounds[i] : 0;
     const int64_t tiles = (int64_t)p.tiles_m * p.tiles_n;
     const int grid = 2 * (int)(tiles < pairs_cap ? tiles : pairs_cap);   // clusters of two CTAs
     CUtensorMap map_sfa = map_a, map_sfb = map_a;   // (placeholders for the mover variant, which does not read them)
@@ -921,7 +971,7 @@ int launch_gemm(const void* a, const void* sfa, const void* b, const void* sfb, 
         if (int rc = cached_map(&map_sfa, sfa, p.sf_row_tiles_a, p.sf_tiles_k, 1000 + 10 * box_tiles + 1)) return rc;
         if (int rc = cached_map(&map_sfb, sfb, p.sf_row_tiles_b, p.sf_tiles_k, 1000 + 10 * box_tiles + 2)) return rc;
     }
-    kern<<<grid, kThreads, kSmemBytes, stream>>>(map_a, map_b, map_out, map_sfa, map_sfb, p);
+    kern<<<grid, kThreads, kSmemBytes, stream>>>(map_a, map_b, map_out, map_sfa, map_sfb, omaps, p);
     return launch_status(what);
 }
 
@@ -946,8 +996,24 @@ extern "C" int launch_scaled_mm_nvfp4_residual_kernel(const void* A, const void*
                                                       const void* gate, int64_t M, int64_t N, int64_t K,
                                                       const float* alpha_device_ptr, int out_dtype_code, cudaStream_t stream) {
     if (!residual || !gate) CK_FAIL(CK_ERR_NULL, "scaled_mm_nvfp4_residual: null residual or gate");
-    return ck::launch_gemm<true, true>(A, A_scale, B, B_scale, D, bias, bias_dtype_code, M, N, K, alpha_device_ptr,
+    return ck::launch_gemm<true, 1>(A, A_scale, B, B_scale, D, bias, bias_dtype_code, M, N, K, alpha_device_ptr,
                                        out_dtype_code, stream, residual, gate);
+}
+
+// launch_scaled_mm_nvfp4_kernel with the output scattered by rows over the ranks of a tensor-parallel group (the
+// reduce-scatter of a row-parallel GEMM fused into its epilogue: each output tile row goes straight into the
+// buffer of the rank that will sum it, over NVLink, while the main loop carries on).  Output row r is row
+// row_offset + r of the group's [bounds[world], N] matrix; rows [bounds[d], bounds[d+1]) are written to dests[d]
+// (a [bounds[d+1] - bounds[d], N] buffer in rank d's memory, mapped into this process), counted from bounds[d].
+// dests, bounds: host arrays (world pointers, world + 1 row numbers in multiples of 128 except the last).
+// 16-bit outputs.  No counterpart in the reference (it has no multi-GPU code).
+extern "C" int launch_scaled_mm_nvfp4_scatter_kernel(const void* A, const void* A_scale, const void* B, const void* B_scale,
+                                                     void* const* dests, const int64_t* bounds, int world, int64_t row_offset,
+                                                     const void* bias, int bias_dtype_code, int64_t M, int64_t N, int64_t K,
+                                                     const float* alpha_device_ptr, int out_dtype_code, cudaStream_t stream) {
+    if (world < 1) CK_FAIL(CK_ERR_SHAPE, "scaled_mm_nvfp4_scatter: world must be at least 1");
+    return ck::launch_gemm<true, 2>(A, A_scale, B, B_scale, nullptr, bias, bias_dtype_code, M, N, K, alpha_device_ptr,
+                                    out_dtype_code, stream, nullptr, nullptr, dests, bounds, world, row_offset);
 }
 
 // Same contraction, MXFP8 operands: A: [M, K] E4M3, W: [N, K] E4M3, scales tiled E8M0.

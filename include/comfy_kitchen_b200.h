@@ -133,6 +133,17 @@ int launch_scaled_mm_nvfp4_residual_kernel(const void* A, const void* A_scale, c
                                            void* D, const void* bias, int bias_dtype_code, const void* residual,
                                            const void* gate, int64_t M, int64_t N, int64_t K,
                                            const float* alpha_device_ptr, int out_dtype_code, ck_stream_t stream);
+/* launch_scaled_mm_nvfp4_kernel with its output scattered by rows over the ranks of a tensor-parallel group: the
+ * reduce-scatter that follows a row-parallel GEMM, fused into the epilogue (tile rows go straight to the rank that
+ * will sum them, over NVLink, while the main loop carries on).  Output row r is row row_offset + r of the group's
+ * matrix; rows [bounds[d], bounds[d+1]) go to dests[d], a [bounds[d+1] - bounds[d], N] buffer in rank d's memory mapped
+ * into this process, counted from bounds[d].  dests / bounds: HOST arrays (world pointers; world + 1 ascending row
+ * numbers, multiples of 128 except the last); row_offset and M multiples of 32; 16-bit outputs.  No counterpart in the
+ * reference (no multi-GPU code). */
+int launch_scaled_mm_nvfp4_scatter_kernel(const void* A, const void* A_scale, const void* B, const void* B_scale,
+                                          void* const* dests, const int64_t* bounds, int world, int64_t row_offset,
+                                          const void* bias, int bias_dtype_code, int64_t M, int64_t N, int64_t K,
+                                          const float* alpha_device_ptr, int out_dtype_code, ck_stream_t stream);
 int launch_scaled_mm_mxfp8_kernel(const void* A, const void* A_scale, const void* B, const void* B_scale, void* D,
                                   const void* bias, int bias_dtype_code, int64_t M, int64_t N, int64_t K,
                                   int out_dtype_code, ck_stream_t stream);

@@ -243,3 +243,28 @@ def test_pipeline_variants_agree(ck, M, N, K):
         ck.set_option("gemm_tile", 0)
     assert torch.equal(outs[1][0], outs[2][0])
     assert (outs[1][1] - outs[2][1]).abs().max() <= 1e-6 * outs[1][1].abs().max()
+
+
+def test_scattered_output_single_gpu(ck):
+    """The GEMM whose epilogue scatters its tile rows over the ranks of a tensor-parallel group, exercised on one GPU
+    with three "ranks" whose buffers are separate local tensors: rows [bounds[d], bounds[d+1]) of the (offset) output
+    must land in buffer d, counted from bounds[d], with the bytes of the ordinary GEMM."""
+    import ctypes
+
+    M, N, K = 608, 520, 512
+    x, w, bias = _operands(M, N, K, 12)
+    gx = (x.float().abs().max() / (6 * 448)).float().cuda()
+    gw = (w.float().abs().max() / (6 * 448)).float().cuda()
+    qx, sx = ck.quantize_nvfp4(x.cuda(), gx)
+    qw, sw = ck.quantize_nvfp4(w.cuda(), gw)
+    want = ck.scaled_mm_nvfp4(qx, qw, gx, gw, sx, sw, bias=bias.cuda(), out_dtype=torch.bfloat16)
+    bounds = [0, 256, 768, 1000]          # the group's matrix has 1000 rows; this GEMM supplies rows 128 .. 735
+    row_offset = 128
+    bufs = [torch.full((bounds[d + 1] - bounds[d], N), 7.0, dtype=torch.bfloat16, device="cuda") for d in range(3)]
+    dests = (ctypes.c_void_p * 3)(*[b.data_ptr() for b in bufs])
+    cb = (ctypes.c_int64 * 4)(*bounds)
+    ck.scaled_mm_nvfp4(qx, qw, gx, gw, sx, sw, bias=bias.cuda(), out_dtype=torch.bfloat16, scatter=(dests, cb, 3, row_offset))
+    assert ck.gemm_device_status() == 0
+    whole = torch.cat(bufs)                # rows of the group's matrix
+    assert torch.equal(whole[row_offset:row_offset + M], want)
+    assert bool((whole[:row_offset] == 7.0).all()) and bool((whole[row_offset + M:] == 7.0).all())   # nothing else touched
