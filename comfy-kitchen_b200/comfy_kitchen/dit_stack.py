@@ -428,8 +428,23 @@ class DiTStack:
         from comfy_kitchen.tp_exchange import PeerExchange
 
         assert self.device.type == "cuda"
-        self.exchange = PeerExchange(self.tp.group, self.device, self.cfg.tokens, self.cfg.hidden, torch.bfloat16, mode)
+        n_mod = 0 if self.mod_w is None else self.mod_w.shape[0]
+        self.exchange = PeerExchange(self.tp.group, self.device, self.cfg.tokens, self.cfg.hidden, torch.bfloat16, mode,
+                                     extra_bytes=2 * n_mod)
         self._xbuf = self.exchange.residual
+        # The blocks' modulation vectors are one matrix-vector product over 6.5 GB of weights per forward (1 ms):
+        # with several ranks each keeps and multiplies only its share of the rows, and the shares are gathered.
+        self._mod_rows = None
+        if self.tp.world > 1 and n_mod and n_mod % (8 * self.tp.world) == 0:
+            per = n_mod // self.tp.world
+            lo = self.tp.rank * per
+            self._mod_rows = (lo, lo + per)
+            self._mod_w_shard = self.mod_w[lo:lo + per].clone()
+            self._mod_b_shard = self.mod_b[lo:lo + per].clone()
+            for p_ in [blk[s] for blk in self.double for s in ("img", "txt")] + list(self.single):
+                p_.pop("mod_w", None), p_.pop("mod_b", None)     # (views of the full matrix)
+            self.mod_w = self.mod_b = None
+            self._n_mod = n_mod
 
     def enable_sequence_parallel(self) -> None:
         """From now on every rank updates and normalises only its rows of the residual stream (whole 128-row scale
@@ -547,7 +562,14 @@ class DiTStack:
     def forward(self, img: torch.Tensor, txt: torch.Tensor, vec: torch.Tensor) -> torch.Tensor:
         """img [img_tokens, hidden], txt [txt_tokens, hidden], vec [1, hidden] (bf16) -> [tokens, hidden],
         text tokens first.  Every rank receives the same inputs and returns the same (replicated) output."""
-        self._mods = F.linear(F.silu(vec), self.mod_w, self.mod_b) if self.mod_w is not None else None
+        if getattr(self, "_mod_rows", None) is not None:
+            lo, hi = self._mod_rows
+            mods = self.exchange.extra[:2 * self._n_mod].view(torch.bfloat16)
+            mods[lo:hi].copy_(F.linear(F.silu(vec), self._mod_w_shard, self._mod_b_shard)[0])
+            self.exchange.gather_extra(2 * lo, 2 * hi)
+            self._mods = mods[None]
+        else:
+            self._mods = F.linear(F.silu(vec), self.mod_w, self.mod_b) if self.mod_w is not None else None
         tt = self._tt = txt.shape[0]
         x = self._residual(tt + img.shape[0])
         x[:tt].copy_(txt)

@@ -36,7 +36,8 @@ class PeerExchange:
     all-reduce + residual kernel.  World size 1 works too (the kernel then only applies the residual update),
     which is what the single-GPU tests exercise."""
 
-    def __init__(self, group, device, rows: int, cols: int, dtype: torch.dtype = torch.bfloat16, mode: str | None = None):
+    def __init__(self, group, device, rows: int, cols: int, dtype: torch.dtype = torch.bfloat16, mode: str | None = None,
+                 extra_bytes: int = 0):
         import torch.distributed as dist
 
         assert dtype in (torch.bfloat16, torch.float16) and cols % 8 == 0
@@ -59,8 +60,10 @@ class PeerExchange:
         # one block per rank: [partial | residual | NVFP4 codes of the activation | its tiled block scales | flag pad]
         rows_pad, sf_cols = (rows + 127) // 128 * 128, (cols // 16 + 3) // 4 * 4
         q_bytes, sf_bytes = _align(rows * (cols // 2)), _align(rows_pad * sf_cols)
-        self._offsets = (0, mat, 2 * mat + q_bytes + sf_bytes)
+        extra_bytes = _align(extra_bytes)     # a caller-defined region every rank can push slices of (gather_extra)
+        self._offsets = (0, mat, 2 * mat + q_bytes + sf_bytes + extra_bytes)
         self._q_off, self._sf_off = 2 * mat, 2 * mat + q_bytes
+        self._extra_off, self._extra_bytes = 2 * mat + q_bytes + sf_bytes, extra_bytes
         total = self._offsets[2] + self._pad_bytes
         mode = mode or os.environ.get("CK_TP_PEER_MEMORY", "auto")
         self._keep = []          # objects that own the mappings
@@ -84,6 +87,7 @@ class PeerExchange:
         self.qx = self._block[self._q_off:self._q_off + rows * (cols // 2)].view(rows, cols // 2)
         self.sx = self._block[self._sf_off:self._sf_off + rows_pad * sf_cols].view(rows_pad, sf_cols)
         self._sf_cols = sf_cols
+        self.extra = self._block[self._extra_off:self._extra_off + extra_bytes]
         tiles = rows_pad // 128
         cuts = [min(rows, 128 * (tiles * r // self.world)) for r in range(self.world)] + [rows]
         self.row_bounds = cuts
@@ -178,6 +182,11 @@ class PeerExchange:
         tile_lo, tile_hi = lo // 128, (hi + 127) // 128
         self._gather((self._q_off + lo * half, self._q_off + hi * half),
                      (self._sf_off + tile_lo * 128 * self._sf_cols, self._sf_off + tile_hi * 128 * self._sf_cols))
+
+    def gather_extra(self, lo: int, hi: int) -> None:
+        """Bytes [lo, hi) (multiples of 16) of this rank's ``extra`` region reach every rank's copy."""
+        assert 0 <= lo <= hi <= self._extra_bytes and lo % 16 == 0 and hi % 16 == 0
+        self._gather((self._extra_off + lo, self._extra_off + hi), (0, 0))
 
     def gather_residual(self) -> None:
         """Every rank's rows of the residual stream reach every rank's copy (end of a sequence-parallel forward)."""
