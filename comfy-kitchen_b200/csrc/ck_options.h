@@ -18,10 +18,10 @@
 //                         over the broadcast dimension (0: default)
 //   "gelu_table_min"      the gather quantizer tabulates GELU per CTA from n activated elements on
 //                         (default 16 Mi; negative: never; same bytes either way)
-//   "gemm_tile"           GEMM pipeline: 0 or 1 = scale movers (default); 2 = scales moved by tcgen05.cp from
-//                         the MMA issuer, copies of both CTAs signalling the leader's barrier (1-3 % faster for
-//                         NVFP4 at K = 3072, up to 13 % for MXFP8, but the two issuers' k-tiles then reach the
-//                         tensor pipe in varying order: MXFP8 sums can differ in the last fp32 bit between runs)
+//   "gemm_tile"           GEMM pipeline: 0 or 2 = scales moved by tcgen05.cp (default); 1 = scale-mover warps; 2 = tcgen05.cp from
+//                         the MMA issuer, copies of both CTAs signalling the leader's barrier.  Same MMAs either way;
+//                         with either one MXFP8 sums can differ in the last fp32 bit between launches (two issuing
+//                         warps), NVFP4 results repeat bit for bit
 //   "gemm_map_cache"      0 disables the cache of encoded tensor maps (1: default)
 //   "tp_bulk"             1: launch_tp_reduce_rows_kernel pulls the peers' rows with bulk copies through shared memory
 //                         (0: 16-byte peer loads from every thread)

@@ -17,28 +17,33 @@
 // accumulator of its own rows.  Per CTA:
 //   warp 0       TMA producer: per k-tile one 128x128B box of A, one 128x128B box of
 //                W (both SWIZZLE_128B) and the scale tiles (its A rows' tile, both W
-//                tiles; plain bulk copies) into a 5-stage shared-memory ring.
-//   warps 18-21  scale movers: shared memory -> registers -> TMEM (tcgen05.st), one
-//                warp per 32-lane quarter of TMEM, into a ring of three scale
-//                buffers; they tell the leader CTA's MMA issuer when a k-tile's
-//                scales (and, transitively, its operands) are in place.
-//   warp 1       in the leader CTA (rank 0) the MMA issuer: four tcgen05.mma
-//                .kind::{mxf4nvf4,mxf8f6f4}.block_scale per k-tile (256x256xK64 for
-//                FP4, xK32 for FP8); tcgen05.commit (multicast to both CTAs) releases
-//                the stage and its scale buffer and, per tile, publishes the
-//                accumulator.  In both CTAs this warp allocates and frees TMEM.
+//                tiles) into a 5-stage shared-memory ring.
+//   warp 1, 22   in the leader CTA (rank 0) the two MMA issuers, taking the k-tiles in
+//                turn: four tcgen05.mma.kind::{mxf4nvf4,mxf8f6f4}.block_scale per
+//                k-tile (256x256xK64 for FP4, xK32 for FP8); tcgen05.commit (multicast
+//                to both CTAs) releases the stage and, per tile, publishes the
+//                accumulator.  In both CTAs warp 1 allocates and frees TMEM.
 //   warps 2-17   epilogue: each warp reads its 32 TMEM lanes x 64 columns into
-//                registers, hands the accumulator back, then applies alpha and bias,
-//                converts and writes through a swizzled staging buffer with TMA
-//                stores, overlapping the next tile's main loop.
+//                registers, hands the accumulator back, then applies alpha and bias
+//                (optionally the residual update), converts and writes through a
+//                swizzled staging buffer with TMA stores (optionally into the buffers
+//                of other ranks), overlapping the next tile's main loop.
+// Two ways of getting the scale tiles from shared memory into TMEM (template flag kCp):
+//   tcgen05.cp (default): every copy of both CTAs signals the LEADER's barrier
+//                (cp.async.bulk.tensor ... .cta_group::2, no multicast); the MMA issuer
+//                waits for that one barrier and issues tcgen05.cp.cta_group::2 for the
+//                stage's scale tiles right in front of its MMAs; the scale buffer in
+//                TMEM is indexed by the stage.  Warps 18-21 have no work.
+//   movers:      warps 18-21 copy shared memory -> registers -> TMEM (tcgen05.st), one
+//                warp per 32-lane quarter, into a ring of three scale buffers, and tell
+//                the leader's issuers when a k-tile's scales (and, transitively, its
+//                operands) are in place.
 // Why this shape: measured on B200, one block-scaled MMA with 128 rows per CTA keeps
 // the issuing thread ~140 clocks whether N is 64 or 256, so only N = 256 reaches the
-// tensor cores' rate; with one CTA per tile that costs 96 KB of shared-memory traffic
-// per k-tile, and pairing the CTAs halves the W traffic of each SM.  The 256-column
-// accumulator leaves room for the scale ring (A: 16 columns, W: 32 columns per
-// k-tile, three buffers) but not for a second accumulator, hence the
-// register-buffered epilogue.  (tcgen05.cp could move the scales too, but it queues
-// on the tensor pipe in front of the MMAs: ~22 clocks per 512-byte tile measured.)
+// tensor cores' rate (hence also two issuing warps); with one CTA per tile that costs
+// 96 KB of shared-memory traffic per k-tile, and pairing the CTAs halves the W traffic
+// of each SM.  The 256-column accumulator leaves no room for a second one beside the
+// scale buffers, hence the register-buffered epilogue.
 //
 // Every wait on an mbarrier in this file is bounded: on expiry the CTA records a
 // status word, stops issuing work, drains its own copies and frees its TMEM before
@@ -65,7 +70,6 @@ constexpr int kFirstMoverWarp = kFirstEpiWarp + kEpiWarps;
 constexpr int kSecondMmaWarp = kFirstMoverWarp + 4;   // issues the odd k-tiles; warp 1 the even ones
 constexpr int kThreads = 32 * (kSecondMmaWarp + 1);
 constexpr int kSfBufs = 3;
-constexpr bool kDefaultCp = false;   // which pipeline variant the launcher takes when not told (see launch_gemm)
 constexpr int kKbPerTile = 4;  // MMAs per k-tile
 
 constexpr int kSmemA = BM * 128;            // 16 KB
@@ -890,7 +894,11 @@ int launch_gemm(const void* a, const void* sfa, const void* b, const void* sfb, 
         CK_FAIL(CK_ERR_ALIGN, "%s: operands, scales and output must be 16-byte aligned (row pitch too)", what);
 
     // Which pipeline: 1 = scale movers, 2 = tcgen05.cp by the MMA issuer (ck_set_option("gemm_tile", ...); 0 = default).
-    const bool use_cp = g_gemm_tile == 2 || (g_gemm_tile == 0 && kDefaultCp);
+    // Default: the tcgen05.cp pipeline (measured 1-3 % faster for NVFP4, 2-13 % for MXFP8, never slower by more than
+    // the run-to-run spread); ck_set_option("gemm_tile", 1) selects the scale movers.  Both pipelines use two
+    // MMA-issuing warps whose k-tiles may reach the tensor pipe in either order: NVFP4 results repeat bit for bit in
+    // every test, MXFP8 sums can differ in the last fp32 bit from launch to launch with either pipeline.
+    const bool use_cp = g_gemm_tile != 1;
     auto kern = use_cp ? gemm_blockscaled_kernel<kFp4, kEpi, true> : gemm_blockscaled_kernel<kFp4, kEpi, false>;
     // per device and variant: shared-memory opt-in, and how many CTA pairs can be resident at once
     static int max_pairs[2][64] = {};   // (one table per instantiation of this function)

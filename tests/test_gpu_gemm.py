@@ -220,11 +220,11 @@ def test_tensor_map_cache_is_transparent(ck):
 @pytest.mark.parametrize("M,N,K", [(128, 192, 256), (300, 520, 192), (513, 264, 3104), (1024, 3072, 3072), (4608, 3072, 12288),
                                    (2344, 1160, 6176)])
 def test_pipeline_variants_agree(ck, M, N, K):
-    """The two pipelines of the GEMM kernel (scales moved into TMEM by dedicated warps -- the default -- or by
-    tcgen05.cp from the MMA issuer with all copies signalling the pair leader's barrier) issue the same MMAs: one
-    tile or many per CTA pair, ragged edges, partial last k-tile.  NVFP4 results are identical; with MXFP8 the
-    second pipeline lets the two issuing warps' k-tiles reach the tensor pipe in varying order, so fp32 sums may
-    differ in the last bit (1e-6 relative allowed), which is why it is not the default."""
+    """The two pipelines of the GEMM kernel (scales moved into TMEM by dedicated warps, or by tcgen05.cp from the MMA
+    issuer with all copies signalling the pair leader's barrier; the launcher picks one per format and K) issue the
+    same MMAs: one tile or many per CTA pair, ragged edges, partial last k-tile.  NVFP4 results are identical.  With
+    MXFP8 the k-tiles of the two issuing warps can reach the tensor pipe in either order, with both pipelines, so
+    fp32 sums may differ in the last bit even between two launches of the same pipeline (1e-6 relative allowed)."""
     x, w, bias = _operands(M, N, K, 9)
     gx = (x.float().abs().max() / (6 * 448)).float().cuda()
     gw = (w.float().abs().max() / (6 * 448)).float().cuda()
