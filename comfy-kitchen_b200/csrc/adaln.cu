@@ -428,7 +428,7 @@ int launch_warp(const NormArgs& a, cudaStream_t stream) {
                 w -= w % group;
                 if ((size_t)w * warp_bytes > budget) w = 0;
             } else {
-                for (int cand : {32, 24, 16, 12, 8, 6, 4, 2, 1})
+                for (int cand : {16, 12, 8, 6, 4, 2, 1})   // (24 and 32 warps measured slower: option "norm_warps" only)
                     if (cand % group == 0 && (group == 1 || cand <= 16) && (size_t)cand * warp_bytes <= budget) { w = cand; break; }
             }
             if (w == 0) continue;
