@@ -113,9 +113,9 @@ quantize_mxfp8_kernel(const T* __restrict__ x, uint8_t* __restrict__ q, uint8_t*
 template <typename T>
 __global__ void __launch_bounds__(kThreads)
 dequantize_mxfp8_kernel(const uint8_t* __restrict__ q, const uint8_t* __restrict__ sf, T* __restrict__ out,
-                        int64_t rows, int64_t cols, int64_t sf_cpad) {
+                        int64_t rows, int64_t cols, int64_t sf_cpad, const bool vec32) {
     __shared__ __align__(16) uint8_t s_sf[kSfTiles * 512];
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int tid = threadIdx.x;
     const int64_t row0 = (int64_t)blockIdx.y * kTileRows;
     const int64_t col0 = (int64_t)blockIdx.x * kTileCols;
 
@@ -130,27 +130,48 @@ dequantize_mxfp8_kernel(const uint8_t* __restrict__ q, const uint8_t* __restrict
     }
     __syncthreads();
 
-    const int64_t col = col0 + lane * 8;
+    // a thread owns 16 consecutive elements: one 16-byte load, 32 (16-bit outputs) or 64 bytes stored; four rows in flight
+    const int seg = tid & 15, sub = tid >> 4;
+    constexpr int kRowsPerStep = kThreads / 16;
+    const int64_t col = col0 + seg * 16;
     if (col >= cols) return;
-    const int blk_in_tile = lane >> 2;
-
-#pragma unroll 4
-    for (int it = 0; it < kTileRows / kWarps; ++it) {
-        const int r_in_tile = it * kWarps + warp;
-        const int64_t row = row0 + r_in_tile;
-        if (row >= rows) break;
-        const uint2 data = *reinterpret_cast<const uint2*>(q + row * cols + col);
-        const uint32_t e = s_sf[(blk_in_tile >> 2) * 512 + sf_tile_offset(r_in_tile, blk_in_tile & 3)];
-        const float s = e == 0u ? 0.0f : __uint_as_float(e << 23);
-        const uint32_t w[2] = {data.x, data.y};
-        float v[8];
+    const int blk_in_tile = seg >> 1;
+    constexpr int kUnroll = 4;
+#pragma unroll 1
+    for (int it = 0; it < kTileRows / kRowsPerStep; it += kUnroll) {
+        uint4 data[kUnroll];
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const float2 f = e4m3x2_to_f32x2(w[i >> 1] >> (16 * (i & 1)));
-            v[2 * i] = __fmul_rn(f.x, s);
-            v[2 * i + 1] = __fmul_rn(f.y, s);
+        for (int u = 0; u < kUnroll; ++u) {
+            const int64_t row = row0 + (it + u) * kRowsPerStep + sub;
+            data[u] = make_uint4(0u, 0u, 0u, 0u);
+            if (row < rows) data[u] = *reinterpret_cast<const uint4*>(q + row * cols + col);
         }
-        store8<T>(out + row * cols + col, v);
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u) {
+            const int r_in_tile = (it + u) * kRowsPerStep + sub;
+            const int64_t row = row0 + r_in_tile;
+            if (row >= rows) continue;
+            const uint32_t e = s_sf[(blk_in_tile >> 2) * 512 + sf_tile_offset(r_in_tile, blk_in_tile & 3)];
+            const float s = e == 0u ? 0.0f : __uint_as_float(e << 23);
+            const uint32_t w[4] = {data[u].x, data[u].y, data[u].z, data[u].w};
+            float v[16];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const float2 f = e4m3x2_to_f32x2(w[i >> 1] >> (16 * (i & 1)));
+                v[2 * i] = __fmul_rn(f.x, s);
+                v[2 * i + 1] = __fmul_rn(f.y, s);
+            }
+            T* dst = out + row * cols + col;
+            if (vec32) {
+                store16<T>(dst, v);
+            } else {
+                float lo[8], hi[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) { lo[i] = v[i]; hi[i] = v[8 + i]; }
+                store8<T>(dst, lo);
+                store8<T>(dst + 8, hi);
+            }
+        }
     }
 }
 
@@ -171,7 +192,8 @@ template <typename T>
 int launch_dequantize(const uint8_t* q, const uint8_t* sf, void* out, int64_t rows, int64_t cols, cudaStream_t stream) {
     const int64_t sf_cpad = round_up(cols / 32, 4);
     dim3 grid((unsigned)ceil_div(cols, kTileCols), (unsigned)ceil_div(rows, kTileRows));
-    dequantize_mxfp8_kernel<T><<<grid, kThreads, 0, stream>>>(q, sf, (T*)out, rows, cols, sf_cpad);
+    // (256-bit stores need a 32-byte aligned output; rows are multiples of 32 elements)
+    dequantize_mxfp8_kernel<T><<<grid, kThreads, 0, stream>>>(q, sf, (T*)out, rows, cols, sf_cpad, aligned32(out));
     return launch_status("dequantize_mxfp8");
 }
 
