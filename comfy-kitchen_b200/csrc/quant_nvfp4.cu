@@ -330,31 +330,42 @@ dequantize_nvfp4_kernel(const uint8_t* __restrict__ q, const float* __restrict__
     const int64_t col = col0 + blk * 16;
     if (col >= cols) return;
 
-#pragma unroll 4
-    for (int it = 0; it < kTileRows / kRowsPerStep; ++it) {
-        const int r_in_tile = it * kRowsPerStep + sub;
-        const int64_t row = row0 + r_in_tile;
-        if (row >= rows) break;
-        const uint2 codes = *reinterpret_cast<const uint2*>(q + row * (cols >> 1) + (col >> 1));
-        const uint32_t s8 = s_sf[(blk >> 2) * 512 + sf_tile_offset(r_in_tile, blk & 3)];
-        const float tot = Elem<T>::round(__fmul_rn(g, e4m3_to_f32(s8)));
-        float lo[8], hi[8], v[16];
-        e2m1x8_to_f32(codes.x, hi_first, lo);
-        e2m1x8_to_f32(codes.y, hi_first, hi);
+    // four rows per thread in flight: the code loads of a batch are issued before any of them is expanded
+    constexpr int kUnroll = 4;
+#pragma unroll 1
+    for (int it = 0; it < kTileRows / kRowsPerStep; it += kUnroll) {
+        uint2 codes[kUnroll];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            v[i] = __fmul_rn(lo[i], tot);
-            v[8 + i] = __fmul_rn(hi[i], tot);
+        for (int u = 0; u < kUnroll; ++u) {
+            const int64_t row = row0 + (it + u) * kRowsPerStep + sub;
+            codes[u] = make_uint2(0u, 0u);
+            if (row < rows) codes[u] = *reinterpret_cast<const uint2*>(q + row * (cols >> 1) + (col >> 1));
         }
-        T* dst = out + row * cols + col;
-        if (kVec) {
-            store16<T>(dst, v);
-        } else {
-            float a[8], b[8];
 #pragma unroll
-            for (int i = 0; i < 8; ++i) { a[i] = v[i]; b[i] = v[8 + i]; }
-            store8<T>(dst, a);
-            store8<T>(dst + 8, b);
+        for (int u = 0; u < kUnroll; ++u) {
+            const int r_in_tile = (it + u) * kRowsPerStep + sub;
+            const int64_t row = row0 + r_in_tile;
+            if (row >= rows) continue;
+            const uint32_t s8 = s_sf[(blk >> 2) * 512 + sf_tile_offset(r_in_tile, blk & 3)];
+            const float tot = Elem<T>::round(__fmul_rn(g, e4m3_to_f32(s8)));
+            float lo[8], hi[8], v[16];
+            e2m1x8_to_f32(codes[u].x, hi_first, lo);
+            e2m1x8_to_f32(codes[u].y, hi_first, hi);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                v[i] = __fmul_rn(lo[i], tot);
+                v[8 + i] = __fmul_rn(hi[i], tot);
+            }
+            T* dst = out + row * cols + col;
+            if (kVec) {
+                store16<T>(dst, v);
+            } else {
+                float a[8], b[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) { a[i] = v[i]; b[i] = v[8 + i]; }
+                store8<T>(dst, a);
+                store8<T>(dst + 8, b);
+            }
         }
     }
 }
