@@ -955,7 +955,10 @@ def main() -> None:
         del wl.host_in, wl.host_out
     # ---- N > 1: the tensor-parallel DiT stack of configs[4] over all ranks (strong scaling), while the group is alive
     if dist is not None and not args.no_dit and not args.no_extras:
-        line["dit_stack"] = dit_tp_leg(args, dist, device, rank, world)
+        try:
+            line["dit_stack"] = dit_tp_leg(args, dist, device, rank, world)
+        except Exception as e:  # noqa: BLE001 - the contract line must still be printed; the failure is reported in it
+            line["dit_stack"] = {"tp": world, "error": f"{type(e).__name__}: {str(e)[:300]}"}
     # The legs below are single-GPU measurements that rank 0 makes alone: the process group goes first, so that
     # nothing in them can wait for a rank that has already left.
     if dist is not None:

@@ -106,6 +106,22 @@ def main() -> None:
     assert fused.exchange.status() == 0
     assert fused.ops.gemm_device_status() == 0
     assert fused.ops.norm_device_status() == 0
+    # a split in which one rank's rows are exactly the text tokens (what eight ranks give on the full model): that rank
+    # has no image rows to normalise and receives no image tile rows from the scattered GEMMs
+    cfg2 = DiTConfig(n_double=2, n_single=1, txt_tokens=128 * (world - 1) if world > 1 else 128, img_grid=(8, 16 * max(world - 1, 1)))
+    img2 = torch.randn(cfg2.img_tokens, cfg2.hidden, generator=g).bfloat16().to(dev)
+    txt2 = torch.randn(cfg2.txt_tokens, cfg2.hidden, generator=g).bfloat16().to(dev)
+    st2 = DiTStack(cfg2, dev, tp=TensorParallel())
+    assert st2.try_enable_peer_exchange() is None
+    if world == 2:
+        assert st2.exchange.row_bounds == [0, cfg2.txt_tokens, cfg2.tokens], st2.exchange.row_bounds
+    st2.calibrate(img2, txt2, vec)
+    y_rep = st2.forward(img2, txt2, vec)
+    st2.enable_sequence_parallel()
+    y_sp2 = st2.forward(img2, txt2, vec)
+    rel2 = ((y_sp2.float() - y_rep.float()).norm() / y_rep.float().norm()).item()
+    assert rel2 < 1e-2, rel2
+    assert st2.exchange.status() == 0 and st2.ops.gemm_device_status() == 0
     dist.barrier()
     if rank == 0:
         print(f"stack: fused vs NCCL relative difference {rel:.2e}; {how}")
