@@ -19,6 +19,17 @@
 // for NVFP4).
 #include "ck_common.cuh"
 
+// Unroll factor of the two per-row loops in the builds for rows of a known length.  Timed with builds of the same
+// source on 18432 rows (fused NVFP4): 2 -> 48.6 us (rows of 3072) / 63.1 us (4096); 1 -> 50.4 / 66.5; full (6 / 8) ->
+// 49.5 / 69.2: the fully unrolled loop is long enough for the warps of an SM, which sit at different places in it,
+// to wait on instruction fetches.
+#ifndef CK_NORM_U1
+#define CK_NORM_U1 2
+#endif
+#ifndef CK_NORM_U2
+#define CK_NORM_U2 2
+#endif
+
 namespace ck {
 namespace {
 
@@ -44,6 +55,41 @@ __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
     return v;
+}
+
+// Row statistics of 16-bit rows on the tensor cores.  The 4 words (8 values) a lane read from its row are its
+// fragment of a 16 x 16 matrix A in mma.m16n8k16's layout — which of the warp's 256 values lands where does not
+// matter for sums.  A x ones gives the row sums of A (every one eight times); A x A[0:8]^T and A x A[8:16]^T hold on
+// their diagonals the sums of squares of A's rows (for the B operand "A[n][k]" a lane needs exactly its own A
+// words).  Products of two 16-bit values are exact in fp32 and the accumulators are fp32, so this replaces the
+// unpack + add + fma per element of a scalar pass by three instructions per 8 values of a lane.
+template <typename T>
+__device__ __forceinline__ void mma_16816(float (&d)[4], const uint4& a, uint32_t b0, uint32_t b1) {
+    if (sizeof(T) == 2 && Elem<T>::code == CK_F16)
+        asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                     : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3]) : "r"(a.x), "r"(a.y), "r"(a.z), "r"(a.w), "r"(b0), "r"(b1));
+    else
+        asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                     : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3]) : "r"(a.x), "r"(a.y), "r"(a.z), "r"(a.w), "r"(b0), "r"(b1));
+}
+struct MmaStats {
+    float ones[4], lo[4], hi[4];   // A x ones; A x A[0:8]^T (rows 0-7 on its diagonal: ones[0..1]); A x A[8:16]^T (rows 8-15: [2..3])
+};
+template <typename T>
+__device__ __forceinline__ void mma_stats_add(MmaStats& st, const uint4& u, bool want_sum) {
+    // fragment words: x = (row g, k 2t..), y = (row g+8, k 2t..), z = (row g, k 2t+8..), w = (row g+8, k 2t+8..)
+    const uint32_t one2 = Elem<T>::code == CK_F16 ? 0x3c003c00u : 0x3f803f80u;
+    if (want_sum) mma_16816<T>(st.ones, u, one2, one2);
+    mma_16816<T>(st.lo, u, u.x, u.z);
+    mma_16816<T>(st.hi, u, u.y, u.w);
+}
+// Sum and sum of squares of everything the warp fed in (every lane gets both).
+__device__ __forceinline__ void mma_stats_finish(const MmaStats& st, int lane, float& sum1, float& sum2) {
+    const int g = lane >> 2, t = lane & 3;
+    // diagonal entries: row g of `lo` sits in column g = 2t or 2t+1, i.e. in the lanes with t == g / 2
+    const float diag = (g & 1) ? st.lo[1] + st.hi[3] : st.lo[0] + st.hi[2];
+    sum2 = warp_sum(t == (g >> 1) ? diag : 0.0f);
+    sum1 = warp_sum((st.ones[0] + st.ones[1]) + (st.ones[2] + st.ones[3])) * 0.125f;
 }
 
 __device__ int g_norm_status = 0;  // non-zero when a bounded wait on a row copy ran out
@@ -95,6 +141,7 @@ __global__ void __launch_bounds__(kMaxThreads)
 norm_stream_kernel(const NormArgs a, const int ring, const int64_t rows_per_cta, const int cache_mod,
                    const uint32_t poll_limit) {
     extern __shared__ __align__(128) uint8_t smem[];
+    constexpr int kUnrollStats = kIters > 0 ? (CK_NORM_U1) : 2, kUnrollOut = kIters > 0 ? (CK_NORM_U2) : 2;
     const int warps = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int grp = warp / kGroup, member = warp % kGroup, n_groups = warps / kGroup;
     const int64_t D = a.D;
@@ -197,24 +244,49 @@ norm_stream_kernel(const NormArgs a, const int ring, const int64_t rows_per_cta,
             }
             const T* xs = reinterpret_cast<const T*>(my_rows + (size_t)slot * row_bytes);
 
-            // statistics in one pass, shifted by the row's first element (a group's other members fetch it from
-            // global memory: it sits in the first member's buffer)
-            const float shift0 = a.rms ? 0.0f : Elem<T>::to_f32((kGroup == 1 || member == 0) ? xs[0] : xg[row * D]);
-            // two accumulator pairs, updated with sm_100's packed fp32 instructions (two IEEE operations each)
-            float2 s1 = make_float2(0.0f, 0.0f), s2 = s1;
-            const float2 nshift = make_float2(-shift0, -shift0);
-#pragma unroll(kIters > 0 ? kIters : 2)
-            for (int c = lane; c < nchunk; c += 32) {
-                float f[16];
-                lds16<T, false>(xs + c * 16, lane, f);
+            // Statistics in one pass.  fp32 rows: shifted by the row's first element, so that a large common offset
+            // does not cancel (a group's other members fetch it from global memory: it sits in the first member's
+            // buffer).  16-bit rows: unshifted sums on the tensor cores; a row whose mean dwarfs its spread is
+            // then summed again the shifted way (below).  Rows shared by a group of warps keep the shifted sums.
+            float shift0 = 0.0f, sum1, sum2;
+            auto shifted_sums = [&]() {
+                shift0 = a.rms ? 0.0f : Elem<T>::to_f32((kGroup == 1 || member == 0) ? xs[0] : xg[row * D]);
+                // two accumulator pairs, updated with sm_100's packed fp32 instructions (two IEEE operations each)
+                float2 s1 = make_float2(0.0f, 0.0f), s2 = s1;
+                const float2 nshift = make_float2(-shift0, -shift0);
+#pragma unroll((sizeof(T) == 2 && kGroup == 1) ? 1 : (kIters > 0 ? kIters : 2))
+                for (int c = lane; c < nchunk; c += 32) {
+                    float f[16];
+                    lds16<T, false>(xs + c * 16, lane, f);
 #pragma unroll
-                for (int j = 0; j < 16; j += 2) {
-                    const float2 d = __fadd2_rn(make_float2(f[j], f[j + 1]), nshift);
-                    s1 = __fadd2_rn(s1, d);
-                    s2 = __ffma2_rn(d, d, s2);
+                    for (int j = 0; j < 16; j += 2) {
+                        const float2 d = __fadd2_rn(make_float2(f[j], f[j + 1]), nshift);
+                        s1 = __fadd2_rn(s1, d);
+                        s2 = __ffma2_rn(d, d, s2);
+                    }
                 }
+                sum1 = warp_sum(s1.x + s1.y);
+                sum2 = warp_sum(s2.x + s2.y);
+            };
+            if constexpr (sizeof(T) == 2 && kGroup == 1) {
+                MmaStats st = {};
+                const int rot = (lane >> 2) & 1;   // the order of a lane's two 16-byte reads (bank conflicts, see lds16)
+#pragma unroll(kUnrollStats)
+                for (int c0 = 0; c0 < nchunk; c0 += 32) {
+                    const int c = c0 + lane;
+                    uint4 u0 = make_uint4(0u, 0u, 0u, 0u), u1 = u0;   // (every lane takes part in the MMAs)
+                    if (kIters > 0 || c < nchunk) {
+                        const uint4* q = reinterpret_cast<const uint4*>(xs + c * 16);
+                        u0 = q[rot];
+                        u1 = q[rot ^ 1];
+                    }
+                    mma_stats_add<T>(st, u0, !a.rms);
+                    mma_stats_add<T>(st, u1, !a.rms);
+                }
+                mma_stats_finish(st, lane, sum1, sum2);
+            } else {
+                shifted_sums();
             }
-            float sum1 = warp_sum(s1.x + s1.y), sum2 = warp_sum(s2.x + s2.y);
             if (kGroup > 1) {
                 float2* part = s_part + (grp * 2 + (int)(i & 1)) * kGroup;
                 if (lane == 0) part[member] = make_float2(sum1, sum2);
@@ -228,8 +300,14 @@ norm_stream_kernel(const NormArgs a, const int ring, const int64_t rows_per_cta,
 #pragma unroll
                 for (int k = 0; k < kGroup; ++k) { const float2 v = part[k]; sum1 += v.x; sum2 += v.y; }
             }
-            const float m1 = sum1 * inv_d;   // mean - shift0
-            const float m2 = sum2 * inv_d;   // E[(x - shift0)^2]
+            float m1 = sum1 * inv_d;   // mean - shift0
+            float m2 = sum2 * inv_d;   // E[(x - shift0)^2]
+            if (sizeof(T) == 2 && kGroup == 1 && !a.rms && (m2 - m1 * m1) * 256.0f < m2) {
+                // |mean| > 16 standard deviations: E[x^2] - mean^2 has lost bits to cancellation
+                shifted_sums();
+                m1 = sum1 * inv_d;
+                m2 = sum2 * inv_d;
+            }
             const float mean = a.rms ? 0.0f : shift0 + m1;
             const float var = a.rms ? m2 : fmaxf(m2 - m1 * m1, 0.0f);
             const float rstd = rsqrtf(var + a.eps);
@@ -240,7 +318,7 @@ norm_stream_kernel(const NormArgs a, const int ring, const int64_t rows_per_cta,
             const T* __restrict__ sh = (!cache_mod && shift_g) ? shift_g + (row / a.shift_group) * D : nullptr;
 
             // whole-warp steps: the MXFP8 block encoder shuffles between lane pairs
-#pragma unroll(kIters > 0 ? kIters : 2)
+#pragma unroll(kUnrollOut)
             for (int c0 = 0; c0 < nchunk; c0 += 32) {
                 const int c = c0 + lane;          // chunk within this warp's share
                 const int cg = cbase + c;         // chunk within the row
@@ -256,14 +334,23 @@ norm_stream_kernel(const NormArgs a, const int ring, const int64_t rows_per_cta,
                     if (kMode == kOutNvfp4 && row_tail && cg < a.sf_cpad) a.sf[sf_offset(row, cg, a.sf_cpad)] = 0;
                     continue;
                 }
+                // NVFP4 with cached modulation: lanes that read their high half first (lds16) keep that order
+                // through the modulation and the block encoder (the block maximum does not care, the modulation is
+                // read in the same order) and exchange the two words of codes at the end, instead of putting the
+                // sixteen values back in order.
+                const bool halves_swapped = kMode == kOutNvfp4 && sizeof(T) == 2 && cache_mod && ((lane >> 2) & 1);
                 if (ok) {
                     float f[16];
-                    lds16<T, true>(xs + c * 16, lane, f);
+                    lds16<T, kMode != kOutNvfp4>(xs + c * 16, lane, f);
                     if (cache_mod) {
+                        const int mbase = mod_pos(cg, 0);
+                        const int off_first = mbase + (halves_swapped ? 256 : 0);    // quads of f[0..7]
+                        const int off_second = mbase + (halves_swapped ? 0 : 256);   // quads of f[8..15]
 #pragma unroll
                         for (int j4 = 0; j4 < 4; ++j4) {
-                            const float4 mu = *reinterpret_cast<const float4*>(s_mul + mod_pos(cg, j4 * 4));
-                            const float4 ad = *reinterpret_cast<const float4*>(s_add + mod_pos(cg, j4 * 4));
+                            const int mo = (j4 < 2 ? off_first : off_second) + (j4 & 1) * 128;
+                            const float4 mu = *reinterpret_cast<const float4*>(s_mul + mo);
+                            const float4 ad = *reinterpret_cast<const float4*>(s_add + mo);
                             const float2 ya = __ffma2_rn(__ffma2_rn(make_float2(f[4 * j4 + 0], f[4 * j4 + 1]), rstd2, nmr2),
                                                          make_float2(mu.x, mu.y), make_float2(ad.x, ad.y));
                             const float2 yb = __ffma2_rn(__ffma2_rn(make_float2(f[4 * j4 + 2], f[4 * j4 + 3]), rstd2, nmr2),
@@ -271,6 +358,11 @@ norm_stream_kernel(const NormArgs a, const int ring, const int64_t rows_per_cta,
                             y[4 * j4 + 0] = ya.x; y[4 * j4 + 1] = ya.y; y[4 * j4 + 2] = yb.x; y[4 * j4 + 3] = yb.y;
                         }
                     } else {
+                        if (kMode == kOutNvfp4 && sizeof(T) == 2 && ((lane >> 2) & 1)) {
+                            // (the modulation comes from global memory in element order: put the halves back)
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) { const float t = f[j]; f[j] = f[8 + j]; f[8 + j] = t; }
+                        }
                         float m[16], b[16];
 #pragma unroll
                         for (int j = 0; j < 16; ++j) { m[j] = a.rms ? 1.0f : 0.0f; b[j] = 0.0f; }
@@ -289,7 +381,8 @@ norm_stream_kernel(const NormArgs a, const int ring, const int64_t rows_per_cta,
                     for (int j = 0; j < 16; j += 2) Elem<T>::round2(y[j], y[j + 1]);
                     if (kMode == kOutNvfp4) {
                         uint32_t s8;
-                        const uint2 packed = nvfp4_encode_block_lean(y, ctx, a.hi_first != 0, s8);
+                        uint2 packed = nvfp4_encode_block_straight(y, ctx, a.hi_first != 0, s8);
+                        if (halves_swapped) packed = make_uint2(packed.y, packed.x);
                         *reinterpret_cast<uint2*>(static_cast<uint8_t*>(a.out) + row * (D >> 1) + (int64_t)cg * 8) = packed;
                         a.sf[sf_offset(row, cg, a.sf_cpad)] = (uint8_t)s8;
                     } else {

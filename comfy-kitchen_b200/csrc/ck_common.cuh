@@ -447,6 +447,66 @@ __device__ __forceinline__ uint2 nvfp4_encode_block_lean(const float (&v)[16], c
     return nvfp4_codes16(v, b, hi_first);
 }
 
+// nvfp4_encode_block_lean with the scale byte, too, on a straight-line common path; same bytes.
+__device__ __forceinline__ uint2 nvfp4_encode_block_straight(const float (&v)[16], const Nvfp4Ctx& c, bool hi_first, uint32_t& s8) {
+    float amax = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(v[i]));
+    // Common path, straight-line: scale byte and divisor through the reciprocal sequence, whether or not it
+    // applies; one test at the end sends the rare blocks (and tensors) where it does not through the IEEE
+    // divisions instead (the same conditions as nvfp4_block_scale).
+    const float bs = div_by_reciprocal(amax, 6.0f, 0.16666667163372040f /* RN(1/6) */);
+    const float sbs = fminf(div_by_reciprocal(bs, c.g, c.rg), 448.0f);
+    s8 = cvt_e4m3x2(0.0f, sbs) & 0xffu;
+    const float tot = __fmul_rn(c.g, e4m3_to_f32(s8));
+    const uint32_t u = __float_as_uint(tot);
+    const float r = __frcp_rn(tot);
+    // 2^-64 <= tot < 2^65 (one unsigned comparison on the bits), significand not all ones, amax < 2^60
+    const bool fast = c.fast && (u - (63u << 23)) < (129u << 23) && (u & 0x7fffffu) != 0x7fffffu && amax < 1152921504606846976.0f;
+    float q[16];
+    const float2 r2 = make_float2(r, r), b2 = make_float2(tot, tot);
+#pragma unroll
+    for (int i = 0; i < 16; i += 2) {   // div_by_reciprocal on pairs
+        const float2 a2 = make_float2(v[i], v[i + 1]);
+        const float2 q0 = __fmul2_rn(a2, r2);
+        const float2 e = __ffma2_rn(b2, q0, make_float2(-a2.x, -a2.y));
+        const float2 qq = __ffma2_rn(make_float2(-e.x, -e.y), r2, q0);
+        q[i] = qq.x; q[i + 1] = qq.y;
+    }
+    if (!fast) {
+        const Nvfp4Block b = nvfp4_block_scale<true>(amax, c);
+        s8 = b.s8;
+        if (b.tot == 0.0f) return make_uint2(0u, 0u);
+#pragma unroll
+        for (int i = 0; i < 16; ++i) q[i] = __fdiv_rn(v[i], b.tot);
+    }
+    uint2 out;
+    if (hi_first) {
+        asm("{ .reg .b8 t0, t1, t2, t3;\n"
+            "cvt.rn.satfinite.e2m1x2.f32 t0, %1, %2; cvt.rn.satfinite.e2m1x2.f32 t1, %3, %4;\n"
+            "cvt.rn.satfinite.e2m1x2.f32 t2, %5, %6; cvt.rn.satfinite.e2m1x2.f32 t3, %7, %8;\n"
+            "mov.b32 %0, {t0, t1, t2, t3}; }"
+            : "=r"(out.x) : "f"(q[0]), "f"(q[1]), "f"(q[2]), "f"(q[3]), "f"(q[4]), "f"(q[5]), "f"(q[6]), "f"(q[7]));
+        asm("{ .reg .b8 t0, t1, t2, t3;\n"
+            "cvt.rn.satfinite.e2m1x2.f32 t0, %1, %2; cvt.rn.satfinite.e2m1x2.f32 t1, %3, %4;\n"
+            "cvt.rn.satfinite.e2m1x2.f32 t2, %5, %6; cvt.rn.satfinite.e2m1x2.f32 t3, %7, %8;\n"
+            "mov.b32 %0, {t0, t1, t2, t3}; }"
+            : "=r"(out.y) : "f"(q[8]), "f"(q[9]), "f"(q[10]), "f"(q[11]), "f"(q[12]), "f"(q[13]), "f"(q[14]), "f"(q[15]));
+    } else {
+        asm("{ .reg .b8 t0, t1, t2, t3;\n"
+            "cvt.rn.satfinite.e2m1x2.f32 t0, %2, %1; cvt.rn.satfinite.e2m1x2.f32 t1, %4, %3;\n"
+            "cvt.rn.satfinite.e2m1x2.f32 t2, %6, %5; cvt.rn.satfinite.e2m1x2.f32 t3, %8, %7;\n"
+            "mov.b32 %0, {t0, t1, t2, t3}; }"
+            : "=r"(out.x) : "f"(q[0]), "f"(q[1]), "f"(q[2]), "f"(q[3]), "f"(q[4]), "f"(q[5]), "f"(q[6]), "f"(q[7]));
+        asm("{ .reg .b8 t0, t1, t2, t3;\n"
+            "cvt.rn.satfinite.e2m1x2.f32 t0, %2, %1; cvt.rn.satfinite.e2m1x2.f32 t1, %4, %3;\n"
+            "cvt.rn.satfinite.e2m1x2.f32 t2, %6, %5; cvt.rn.satfinite.e2m1x2.f32 t3, %8, %7;\n"
+            "mov.b32 %0, {t0, t1, t2, t3}; }"
+            : "=r"(out.y) : "f"(q[8]), "f"(q[9]), "f"(q[10]), "f"(q[11]), "f"(q[12]), "f"(q[13]), "f"(q[14]), "f"(q[15]));
+    }
+    return out;
+}
+
 // ---- 256-bit global accesses (sm_100) -------------------------------------------------------
 __device__ __forceinline__ void ldg256(const void* p, uint32_t (&r)[8]) {
     asm volatile("ld.global.nc.L1::no_allocate.v8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"

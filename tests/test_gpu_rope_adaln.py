@@ -131,6 +131,34 @@ def test_adaln_vs_oracle(ck, orc, xshape, mshape, dt):
         assert (y.cpu().view(torch.int16) != ref.view(torch.int16)).float().mean().item() < 0.02
 
 
+@pytest.mark.parametrize("D", [3072, 4096, 1008])
+@pytest.mark.parametrize("dt", [torch.bfloat16, torch.float16])
+def test_adaln_rows_with_a_large_mean(ck, orc, D, dt):
+    """16-bit rows get their statistics from unshifted sums (tensor cores); a row whose mean is many standard
+    deviations away from zero must come out as accurately as one centred on zero (the kernel then sums again,
+    shifted).  Offsets on both sides of that switch, and constant rows."""
+    g = torch.Generator().manual_seed(12)
+    offsets = torch.tensor([0.0, 3.0, -8.0, 12.0, 20.0, -50.0, 100.0, 7.5])
+    N = 8 * 40
+    spread = torch.tensor([1.0, 0.5, 2.0, 0.25, 1.0])
+    x = torch.randn(N, D, generator=g) * spread[torch.arange(N) % 5, None] + offsets[torch.arange(N) % 8, None]
+    x[5] = 3.25      # constant rows
+    x[6] = -100.0
+    x = x.to(dt).reshape(1, N, D)
+    sc = (0.1 * torch.randn(1, 1, D, generator=g)).to(dt)
+    sh = (0.1 * torch.randn(1, 1, D, generator=g)).to(dt)
+    y = ck.adaln(x.cuda(), sc.cuda(), sh.cuda(), 1e-6)
+    ref = orc.adaln(x, sc, sh, 1e-6, single_rounding=True)
+    torch.testing.assert_close(y.float().cpu(), ref.float(), rtol=1e-2, atol=1e-2)
+    assert (y.cpu().view(torch.int16) != ref.view(torch.int16)).float().mean().item() < 0.02
+    # the fused kernel sees the same statistics
+    yy = y.reshape(N, D)
+    gs = (yy.float().abs().max() / (6 * 448)).float()
+    q, sf = ck.adaln_quantize_nvfp4(x.cuda(), sc.cuda(), sh.cuda(), gs, 1e-6)
+    q2, sf2 = ck.quantize_nvfp4(yy, gs)
+    assert torch.equal(q, q2) and torch.equal(sf.view(torch.uint8), sf2.view(torch.uint8))
+
+
 def test_rmsnorm_vs_torch(ck):
     g = torch.Generator().manual_seed(6)
     x = torch.randn(64, 24, 128, generator=g).bfloat16().cuda()
