@@ -24,7 +24,7 @@ extern "C" int ck_abi_version(void) { return 1; }
 
 namespace ck {
 int g_nvfp4_exact_div = 0, g_norm_warps = 0, g_norm_cache = -1, g_norm_group = 0, g_norm_poll_limit = 0;
-int g_rope_threads_per_sm = 0, g_gelu_table_min = 16 << 20, g_gemm_tile = 0, g_gemm_map_cache = 1, g_tp_bulk = 0;
+int g_rope_threads_per_sm = 0, g_gelu_table_min = 16 << 20, g_gemm_tile = 0, g_gemm_map_cache = 1, g_tp_bulk = 0, g_qk_heads_per_warp = 0;
 }
 
 // Library options: the public one is described in the C header, the tuning knobs in ck_options.h.
@@ -34,7 +34,7 @@ extern "C" int ck_set_option(const char* name, int value) {
         {"norm_group", &ck::g_norm_group},   {"norm_poll_limit", &ck::g_norm_poll_limit},
         {"rope_threads_per_sm", &ck::g_rope_threads_per_sm}, {"gelu_table_min", &ck::g_gelu_table_min},
         {"gemm_tile", &ck::g_gemm_tile},     {"gemm_map_cache", &ck::g_gemm_map_cache},
-        {"tp_bulk", &ck::g_tp_bulk},
+        {"tp_bulk", &ck::g_tp_bulk},         {"qk_heads_per_warp", &ck::g_qk_heads_per_warp},
     };
     if (name && !strcmp(name, "nvfp4_exact_div")) { ck::g_nvfp4_exact_div = value ? 1 : 0; return CK_OK; }
     if (name)

@@ -16,6 +16,7 @@
 //                         row, deterministically and without any fault.
 //   "rope_threads_per_sm" n > 0: threads per SM the RoPE launcher aims for when it splits the walk
 //                         over the broadcast dimension (0: default)
+//   "qk_heads_per_warp"   n > 0: heads of a token that one warp of the QK-norm + RoPE kernel walks (0: default, one)
 //   "gelu_table_min"      the gather quantizer tabulates GELU per CTA from n activated elements on
 //                         (default 16 Mi; negative: never; same bytes either way)
 //   "gemm_tile"           GEMM pipeline: 0 or 2 = scales moved by tcgen05.cp (default); 1 = scale-mover warps; 2 = tcgen05.cp from
@@ -38,4 +39,5 @@ extern int g_gelu_table_min;
 extern int g_gemm_tile;
 extern int g_gemm_map_cache;
 extern int g_tp_bulk;
+extern int g_qk_heads_per_warp;
 }  // namespace ck
