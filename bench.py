@@ -681,25 +681,38 @@ def dit_tp_leg(args, dist, device, rank: int, world: int) -> dict:
     vec = torch.randn(1, cfg.hidden, generator=g).bfloat16().to(device)
     why_not = None if args.nccl else stack.try_enable_peer_exchange()
     stack.calibrate(img, txt, vec)
+    steps = max(3, min(args.steps, 10))
+
+    def timed_forward():
+        run, how = stack.capture_best(img, txt, vec)
+        for _ in range(3):
+            y = run(img, txt, vec)
+        torch.cuda.synchronize()
+        dist.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            y = run(img, txt, vec)
+        e1.record()
+        torch.cuda.synchronize()
+        dist.barrier()
+        return max_over_ranks(e0.elapsed_time(e1), dist, device) / steps, how, y
+
+    # The form with the replicated front end first (every rank normalises and quantizes the whole sequence), then,
+    # where the peer exchange is available, the sequence-parallel form; the line carries both and the faster one
+    # as ms_per_forward.
+    ms, launch, out = timed_forward()
+    forms = {"replicated_front_end_ms": round(ms, 2)}
+    front_end = "replicated"
     if stack.exchange is not None and not args.no_sp:
         stack.enable_sequence_parallel()
-    run, launch = stack.capture_best(img, txt, vec)
-    for _ in range(3):
-        out = run(img, txt, vec)
-    torch.cuda.synchronize()
-    dist.barrier()
-    steps = max(3, min(args.steps, 10))
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(steps):
-        out = run(img, txt, vec)
-    e1.record()
-    torch.cuda.synchronize()
-    dist.barrier()
-    ms = max_over_ranks(e0.elapsed_time(e1), dist, device) / steps
+        ms_sp, launch_sp, out_sp = timed_forward()
+        forms["sequence_parallel_ms"] = round(ms_sp, 2)
+        if ms_sp <= ms:
+            ms, launch, out, front_end = ms_sp, launch_sp, out_sp, "sequence parallel"
     assert stack.ops.gemm_device_status() == 0, "GEMM kernel reported a device-side timeout"
     assert torch.isfinite(out.float()).all(), "non-finite output"
-    res = {"tp": world, "ms_per_forward": round(ms, 2), "launch": launch, "steps": steps,
+    res = {"tp": world, "ms_per_forward": round(ms, 2), "front_end": front_end, **forms, "launch": launch, "steps": steps,
            "blocks": [cfg.n_double, cfg.n_single], "tokens": cfg.tokens,
            "all_reduces_per_forward": stack.expected_all_reduces(),
            "linear_tflops": round(gemm_flops_per_forward(cfg) / (ms * 1e-3) / 1e12, 1)}

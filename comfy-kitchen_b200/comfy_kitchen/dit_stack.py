@@ -149,9 +149,25 @@ class QuantLinear:
         self.bias = bias
         return self
 
+    def _alpha_for(self, act_scale: torch.Tensor) -> torch.Tensor:
+        """act_scale * weight scale as a device scalar.  Static activation scales are the same tensor objects call
+        after call, so the product is kept per scale tensor (a one-element multiply per GEMM was 228 launches and
+        0.4 ms of a forward); a tensor that was modified in place since, or a new one, is multiplied again."""
+        cache = self.__dict__.setdefault("_alphas", {})
+        hit = cache.get(id(act_scale))
+        if hit is not None and hit[0] is act_scale and hit[2] == act_scale._version:
+            return hit[1]
+        alpha = (act_scale * self.tensor_scale).reshape(1)
+        capturing = act_scale.is_cuda and torch.cuda.is_current_stream_capturing()
+        # (a tensor made during capture belongs to that graph; entries are never dropped, because a captured graph
+        # may hold the address of a kept product: past a handful, further scales are simply not kept)
+        if not capturing and (id(act_scale) in cache or len(cache) < 8):
+            cache[id(act_scale)] = (act_scale, alpha, act_scale._version)
+        return alpha
+
     def __call__(self, qx: torch.Tensor, sx: torch.Tensor, act_scale: torch.Tensor, out=None, residual=None, gate=None,
                  scatter=None) -> torch.Tensor:
-        alpha = (act_scale * self.tensor_scale).reshape(1)
+        alpha = self._alpha_for(act_scale)
         extra = {} if residual is None else {"residual": residual, "gate": gate}
         if scatter is not None:
             extra["scatter"] = scatter

@@ -224,6 +224,13 @@ __device__ __forceinline__ uint32_t gelu_bits<__half>(uint32_t bits) {
 }
 
 template <typename T>
+__device__ __forceinline__ float lut_bits_to_f32(uint16_t b);
+template <>
+__device__ __forceinline__ float lut_bits_to_f32<__nv_bfloat16>(uint16_t b) { return __uint_as_float((uint32_t)b << 16); }
+template <>
+__device__ __forceinline__ float lut_bits_to_f32<__half>(uint16_t b) { return __half2float(__ushort_as_half(b)); }
+
+template <typename T>
 __global__ void __launch_bounds__(kLutThreads, 1)
 quantize_nvfp4_gather_lut_kernel(const QuantSegment s0, const QuantSegment s1, const float* __restrict__ global_scale,
                                  uint8_t* __restrict__ q, uint8_t* __restrict__ sf, int64_t rows, int64_t cols,
@@ -271,15 +278,18 @@ quantize_nvfp4_gather_lut_kernel(const QuantSegment s0, const QuantSegment s1, c
             for (int u = 0; u < kUnroll; ++u) {
                 const int r_in_tile = (it + u) * kRowsPerStep + sub;
                 const int64_t row = row0 + r_in_tile;
+                float v[16];
                 if (act == 1) {
+                    // looked-up bits go straight to fp32 (no repacking of the pair in between)
 #pragma unroll
                     for (int k = 0; k < 8; ++k) {
                         const uint32_t w = raw[u].w[k];
-                        raw[u].w[k] = (uint32_t)lut[w & 0xffffu] | ((uint32_t)lut[w >> 16] << 16);
+                        v[2 * k] = lut_bits_to_f32<T>(lut[w & 0xffffu]);
+                        v[2 * k + 1] = lut_bits_to_f32<T>(lut[w >> 16]);
                     }
+                } else {
+                    unpack16(raw[u], v);
                 }
-                float v[16];
-                unpack16(raw[u], v);
                 uint32_t s8;
                 const uint2 packed = nvfp4_encode_block<false>(v, ctx, hi_first, s8);
                 if (col_ok && row < rows) {

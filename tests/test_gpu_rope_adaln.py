@@ -328,3 +328,25 @@ def test_qk_norm_rope_matches_composition(ck, dtype):
     for a, b in zip(got[:2], want[:2]):
         # the norm's rounding to the 16-bit dtype can differ by one ulp between summation orders and is then rotated
         torch.testing.assert_close(a.float().cpu(), b.float(), rtol=2e-2, atol=2e-2)
+
+
+@pytest.mark.parametrize("heads", [24, 7])
+def test_qk_norm_rope_heads_per_warp_setting_changes_no_byte(ck, heads):
+    """One head per warp (the default), compile-time counts that divide the heads, a count that does not (the
+    run-time walk) and all heads in one warp: the same bytes, the arithmetic per (token, head) is the same."""
+    g = torch.Generator().manual_seed(9)
+    tokens = 333
+    ang = torch.rand(tokens, 64, generator=g) * 6.28
+    f = torch.stack([torch.stack([ang.cos(), -ang.sin()], -1), torch.stack([ang.sin(), ang.cos()], -1)], -2)[None, None].contiguous().cuda()
+    qkv = (2 * torch.randn(tokens, 3 * heads * 128, generator=g)).bfloat16().cuda()
+    qw = (1 + 0.1 * torch.randn(128, generator=g)).bfloat16().cuda()
+    kw = (1 + 0.1 * torch.randn(128, generator=g)).bfloat16().cuda()
+    try:
+        base = ck.qk_norm_rope(qkv, qw, kw, f, heads)
+        for hpw in (2, 3, 4, 5, 6, heads):
+            ck.set_option("qk_heads_per_warp", hpw)
+            got = ck.qk_norm_rope(qkv, qw, kw, f, heads)
+            for a, b in zip(got, base):
+                assert torch.equal(a, b), f"heads per warp {hpw}"
+    finally:
+        ck.set_option("qk_heads_per_warp", 0)
