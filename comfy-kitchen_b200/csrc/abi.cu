@@ -24,7 +24,7 @@ extern "C" int ck_abi_version(void) { return 1; }
 
 namespace ck {
 int g_nvfp4_exact_div = 0, g_norm_warps = 0, g_norm_cache = -1, g_norm_group = 0, g_norm_poll_limit = 0;
-int g_rope_threads_per_sm = 0, g_gelu_table_min = 16 << 20, g_gemm_tile = 0, g_gemm_map_cache = 1, g_tp_bulk = 0, g_qk_heads_per_warp = 0;
+int g_rope_threads_per_sm = 0, g_gelu_table_min = 8 << 20, g_gemm_tile = 0, g_gemm_map_cache = 1, g_tp_bulk = 0, g_qk_heads_per_warp = 0;
 }
 
 // Library options: the public one is described in the C header, the tuning knobs in ck_options.h.

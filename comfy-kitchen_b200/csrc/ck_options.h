@@ -18,7 +18,7 @@
 //                         over the broadcast dimension (0: default)
 //   "qk_heads_per_warp"   n > 0: heads of a token that one warp of the QK-norm + RoPE kernel walks (0: default, one)
 //   "gelu_table_min"      the gather quantizer tabulates GELU per CTA from n activated elements on
-//                         (default 16 Mi; negative: never; same bytes either way)
+//                         (default 8 Mi; negative: never; same bytes either way)
 //   "gemm_tile"           GEMM pipeline: 0 or 2 = scales moved by tcgen05.cp (default); 1 = scale-mover warps; 2 = tcgen05.cp from
 //                         the MMA issuer, copies of both CTAs signalling the leader's barrier.  Same MMAs either way;
 //                         with either one MXFP8 sums can differ in the last fp32 bit between launches (two issuing

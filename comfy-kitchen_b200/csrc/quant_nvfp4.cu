@@ -195,7 +195,8 @@ quantize_nvfp4_gather_kernel(const QuantSegment s0, const QuantSegment s1, const
 // function the kernel above applies, hence the same bits) and then looks elements up: two 16-bit loads per
 // pair instead of the arithmetic.  One persistent CTA of 1024 threads per SM; each quarter of it walks tiles
 // of the kernel above with its own staging area and named barrier.  The fill costs 64 evaluations per thread,
-// so the launcher takes this path only when the activated part is large (>= 16 M elements).
+// so the launcher takes this path only when the activated part is large (>= 8 Mi elements: with 14 M activated
+// elements the table path measured 20.9 us against 26.6 us for the arithmetic).
 constexpr int kLutThreads = 1024;
 constexpr int kLutGroups = kLutThreads / kThreads;
 constexpr int kLutSmem = 65536 * 2 + kLutGroups * kSfTiles * 512;
