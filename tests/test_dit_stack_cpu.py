@@ -193,3 +193,27 @@ def test_stack_from_checkpoint_equals_stack_built_directly(world):
         if world == 1:
             img, txt, vec = _inputs(cfg)
             assert torch.equal(direct.forward(img, txt, vec), loaded.forward(img, txt, vec))
+
+
+def test_alpha_scalar_is_kept_per_scale_tensor_and_follows_in_place_changes():
+    """QuantLinear keeps activation-scale x weight-scale per scale tensor (static scales are the same objects call
+    after call); a scale modified in place, or another tensor, must give a fresh product."""
+    from comfy_kitchen.dit_stack import QuantLinear
+    from tests import dit_oracle_ops as ops
+
+    g = torch.Generator().manual_seed(2)
+    w = (0.05 * torch.randn(128, 64, generator=g)).bfloat16()
+    lin = QuantLinear(ops, w, (w.float().abs().max() / (6 * 448)).reshape(()), None)
+    s = torch.tensor(0.5)
+    a1 = lin._alpha_for(s)
+    assert lin._alpha_for(s) is a1                       # same tensor, unchanged: kept
+    assert torch.equal(a1, (s * lin.tensor_scale).reshape(1))
+    s.mul_(2.0)                                          # in place: the kept product is stale
+    a2 = lin._alpha_for(s)
+    assert torch.equal(a2, (s * lin.tensor_scale).reshape(1)) and not torch.equal(a2, a1)
+    t = torch.tensor(0.25)                               # another tensor
+    assert torch.equal(lin._alpha_for(t), (t * lin.tensor_scale).reshape(1))
+    assert lin._alpha_for(s) is a2
+    for k in range(20):                                  # many one-off scales do not push the kept ones out
+        lin._alpha_for(torch.tensor(0.1 + k))
+    assert lin._alpha_for(s) is a2

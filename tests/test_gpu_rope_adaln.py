@@ -159,6 +159,30 @@ def test_adaln_rows_with_a_large_mean(ck, orc, D, dt):
     assert torch.equal(q, q2) and torch.equal(sf.view(torch.uint8), sf2.view(torch.uint8))
 
 
+@pytest.mark.parametrize("B,T,D", [(5, 130, 1024), (3, 1000, 3072), (7, 64, 512)])
+def test_norm_with_several_modulation_groups(ck, orc, B, T, D):
+    """Each modulation group (batch entry) gets its own share of the CTAs; group sizes that are no multiple of the
+    128-row scale tiles, so the last CTA also owns the scale buffer's padding rows.  Plain output against the oracle,
+    fused outputs against norm kernel -> quantizer (padding bytes of the scale buffer included)."""
+    g = torch.Generator().manual_seed(21)
+    x = torch.randn(B, T, D, generator=g).bfloat16()
+    sc = (0.2 * torch.randn(B, 1, D, generator=g)).bfloat16()
+    sh = (0.2 * torch.randn(B, 1, D, generator=g)).bfloat16()
+    y = ck.adaln(x.cuda(), sc.cuda(), sh.cuda(), 1e-6)
+    ref = orc.adaln(x, sc, sh, 1e-6, single_rounding=True)
+    torch.testing.assert_close(y.float().cpu(), ref.float(), rtol=1e-2, atol=1e-2)
+    assert (y.cpu().view(torch.int16) != ref.view(torch.int16)).float().mean().item() < 0.02
+    yy = y.reshape(B * T, D)
+    gs = (yy.float().abs().max() / (6 * 448)).float()
+    q, sf = ck.adaln_quantize_nvfp4(x.cuda(), sc.cuda(), sh.cuda(), gs, 1e-6)
+    q2, sf2 = ck.quantize_nvfp4(yy, gs)
+    assert torch.equal(q, q2) and torch.equal(sf.view(torch.uint8), sf2.view(torch.uint8))
+    q8, sf8 = ck.adaln_quantize_mxfp8(x.cuda(), sc.cuda(), sh.cuda(), 1e-6)
+    q8b, sf8b = ck.quantize_mxfp8(yy)
+    assert torch.equal(q8.view(torch.uint8), q8b.view(torch.uint8))
+    assert torch.equal(sf8.view(torch.uint8), sf8b.view(torch.uint8))
+
+
 def test_rmsnorm_vs_torch(ck):
     g = torch.Generator().manual_seed(6)
     x = torch.randn(64, 24, 128, generator=g).bfloat16().cuda()
