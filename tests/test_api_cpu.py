@@ -64,6 +64,19 @@ def test_argument_errors_come_back_as_status_and_message():
         _native.call("ck_set_option", b"no_such_option", 1)
 
 
+def test_every_documented_option_is_accepted():
+    """The option names listed in csrc/ck_options.h (and the public one) are the ones ck_set_option knows."""
+    import re
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    text = open(os.path.join(root, "comfy-kitchen_b200", "csrc", "ck_options.h")).read()
+    names = re.findall(r'^//   "([a-z_]+)"', text, flags=re.M)
+    assert len(names) >= 8 and "qk_heads_per_warp" in names
+    defaults = {"norm_cache": -1, "gelu_table_min": 8 << 20, "gemm_map_cache": 1}
+    for name in names + ["nvfp4_exact_div"]:
+        _native.call("ck_set_option", name.encode(), defaults.get(name, 0))   # (sets the default back)
+
+
 # ------------------------------------------------------------------ registry
 
 
